@@ -1,0 +1,83 @@
+// Shared helpers of the sm_100a kernels: element types, loads/stores that widen to float,
+// warp and block reductions, and the launch-status convention of the exported C functions.
+//
+// Every exported function is `extern "C"`, takes raw device pointers, sizes and a stream, launches
+// on that stream and returns 0 or a non-zero code (see LLM_ERR_*); the text of the last error is
+// kept for llm_last_error(). Nothing here allocates device memory.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+
+#define LLM_OK 0
+#define LLM_ERR_ARG 1     // a size or option this kernel does not take
+#define LLM_ERR_LAUNCH 2  // the CUDA runtime refused the launch
+
+// element type codes shared with the Python side
+#define LLM_F32 0
+#define LLM_BF16 1
+
+typedef __nv_bfloat16 bf16;
+
+extern "C" const char* llm_last_error();
+void llm_set_error(const char* fmt, ...);
+
+#define LLM_REQUIRE(cond, ...)            \
+  do {                                    \
+    if (!(cond)) {                        \
+      llm_set_error(__VA_ARGS__);         \
+      return LLM_ERR_ARG;                 \
+    }                                     \
+  } while (0)
+
+#define LLM_CHECK_LAUNCH(name)                                            \
+  do {                                                                    \
+    cudaError_t e__ = cudaGetLastError();                                 \
+    if (e__ != cudaSuccess) {                                             \
+      llm_set_error("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+      return LLM_ERR_LAUNCH;                                              \
+    }                                                                     \
+  } while (0)
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. `red` holds 33 floats.
+// The order of additions depends only on blockDim, never on the batch.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }

@@ -1,0 +1,152 @@
+// Embedding gather, RMSNorm (with the residual sum fused in), SiLU*up, residual add.
+// The residual stream is float32 in both engine precisions; sums of squares, the reciprocal root
+// and the activation are computed in float32.
+//
+// Formulas follow the reference CPU ops: rmsnorm_f32 (src/kernels.cpp:18-24: out = w*x*inv_rms,
+// inv_rms = 1/sqrt(sum(x^2)/dim + eps)), silu_f32 (src/kernels.cpp:26-31: v/(1+exp(-v))) with the
+// product by `up` as a separate multiply (src/engine.cpp:388-389), embed_lookup_f32
+// (src/kernels.cpp:59-66).
+#include "common.cuh"
+
+#include <cstdarg>
+#include <cstring>
+
+static thread_local char g_last_error[512] = "";
+
+extern "C" const char* llm_last_error() { return g_last_error; }
+
+void llm_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+}
+
+// ------------------------------------------------------------------------------------ embedding
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ out, int dim, int vocab) {
+  const int row = blockIdx.x;
+  int id = ids[row];
+  if (id < 0 || id >= vocab) id = 0;  // ids are validated on the host; never read out of range
+  const T* src = table + (size_t)id * dim;
+  float* dst = out + (size_t)row * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = to_f32(src[i]);
+}
+
+extern "C" int llm_embed(const void* table, int table_dtype, const int* ids, float* out, int n_rows,
+                         int dim, int vocab, cudaStream_t stream) {
+  if (n_rows == 0) return LLM_OK;
+  LLM_REQUIRE(n_rows > 0 && dim > 0 && vocab > 0, "embed: bad sizes rows=%d dim=%d vocab=%d", n_rows, dim, vocab);
+  const int threads = dim >= 1024 ? 256 : 128;
+  if (table_dtype == LLM_F32)
+    embed_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)table, ids, out, dim, vocab);
+  else if (table_dtype == LLM_BF16)
+    embed_kernel<bf16><<<n_rows, threads, 0, stream>>>((const bf16*)table, ids, out, dim, vocab);
+  else
+    LLM_REQUIRE(false, "embed: unknown table dtype %d", table_dtype);
+  LLM_CHECK_LAUNCH("embed");
+  return LLM_OK;
+}
+
+// ------------------------------------------------------------------------------------ RMSNorm
+// One block per output row. Source row r = rows ? rows[blockIdx.x] : blockIdx.x.
+// x = h[r] + sum_p delta[p][r] (partials added in index order); if write_back, h[r] = x.
+// out[blockIdx.x] = (w * x) * inv_rms.
+template <typename TOut>
+__global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int n_partials,
+                               size_t partial_stride, const float* __restrict__ w,
+                               const int* __restrict__ rows, TOut* __restrict__ out, int dim, float eps,
+                               int write_back) {
+  __shared__ float red[33];
+  const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+  float* hr = h + (size_t)r * dim;
+  const float* dr = delta ? delta + (size_t)r * dim : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float x = hr[i];
+    if (dr) {
+      for (int p = 0; p < n_partials; ++p) x += dr[(size_t)p * partial_stride + i];
+      if (write_back) hr[i] = x;
+    }
+    ss += x * x;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+  TOut* o = out + (size_t)blockIdx.x * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float x = hr[i];
+    if (dr && !write_back)
+      for (int p = 0; p < n_partials; ++p) x += dr[(size_t)p * partial_stride + i];
+    o[i] = from_f32<TOut>((w[i] * x) * inv);
+  }
+}
+
+extern "C" int llm_rmsnorm(float* h, const float* delta, int n_partials, long long partial_stride,
+                           const float* w, const int* rows, void* out, int out_dtype, int n_out_rows,
+                           int dim, float eps, int write_back, cudaStream_t stream) {
+  if (n_out_rows == 0) return LLM_OK;
+  LLM_REQUIRE(n_out_rows > 0 && dim > 0, "rmsnorm: bad sizes rows=%d dim=%d", n_out_rows, dim);
+  LLM_REQUIRE(!(rows && write_back), "rmsnorm: write_back with a row list is not allowed");
+  LLM_REQUIRE(!delta || n_partials >= 1, "rmsnorm: delta needs n_partials >= 1");
+  int threads = 128;
+  while (threads < 1024 && threads * 4 < dim) threads *= 2;
+  if (out_dtype == LLM_F32)
+    rmsnorm_kernel<float><<<n_out_rows, threads, 0, stream>>>(h, delta, n_partials, (size_t)partial_stride, w, rows,
+                                                              (float*)out, dim, eps, write_back);
+  else if (out_dtype == LLM_BF16)
+    rmsnorm_kernel<bf16><<<n_out_rows, threads, 0, stream>>>(h, delta, n_partials, (size_t)partial_stride, w, rows,
+                                                             (bf16*)out, dim, eps, write_back);
+  else
+    LLM_REQUIRE(false, "rmsnorm: unknown out dtype %d", out_dtype);
+  LLM_CHECK_LAUNCH("rmsnorm");
+  return LLM_OK;
+}
+
+// ------------------------------------------------------------------------------------ residual add
+__global__ void residual_add_kernel(float* __restrict__ h, const float* __restrict__ delta, int n_partials,
+                                    size_t partial_stride, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float x = h[i];
+  for (int p = 0; p < n_partials; ++p) x += delta[(size_t)p * partial_stride + i];
+  h[i] = x;
+}
+
+extern "C" int llm_residual_add(float* h, const float* delta, int n_partials, long long partial_stride,
+                                long long n, cudaStream_t stream) {
+  if (n == 0) return LLM_OK;
+  LLM_REQUIRE(n > 0 && n_partials >= 1, "residual_add: bad sizes");
+  residual_add_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(h, delta, n_partials, (size_t)partial_stride, (size_t)n);
+  LLM_CHECK_LAUNCH("residual_add");
+  return LLM_OK;
+}
+
+// ------------------------------------------------------------------------------------ SiLU(gate) * up
+// in: [rows, 2*ff] with gate in columns [0,ff) and up in [ff,2ff); out: [rows, ff].
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int ff, size_t total) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t r = i / ff;
+  const int c = (int)(i - r * ff);
+  const float g = to_f32(in[r * 2 * ff + c]);
+  const float u = to_f32(in[r * 2 * ff + ff + c]);
+  float s = g / (1.0f + expf(-g));
+  out[i] = from_f32<T>(s * u);
+}
+
+extern "C" int llm_silu_mul(const void* in, void* out, int dtype, int n_rows, int ff, cudaStream_t stream) {
+  if (n_rows == 0) return LLM_OK;
+  LLM_REQUIRE(n_rows > 0 && ff > 0, "silu_mul: bad sizes rows=%d ff=%d", n_rows, ff);
+  const size_t total = (size_t)n_rows * ff;
+  const int blocks = ceil_div((long long)total, 256);
+  if (dtype == LLM_F32)
+    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)in, (float*)out, ff, total);
+  else if (dtype == LLM_BF16)
+    silu_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)in, (bf16*)out, ff, total);
+  else
+    LLM_REQUIRE(false, "silu_mul: unknown dtype %d", dtype);
+  LLM_CHECK_LAUNCH("silu_mul");
+  return LLM_OK;
+}

@@ -1,0 +1,92 @@
+"""A model built from its description: embedding, the layers in their run order, final norm, head.
+
+`Model.forward(ctx)` is the device half of the step function: it runs exactly the tokens of the
+step's flat batch, reading and writing the paged cache through the block tables in `ctx`, and
+returns float32 logits for the wanted rows only (the reference skips the final norm and the head
+for positions whose logits are not asked for, src/engine.cpp:415-433).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache.storage import allocate_run_caches, bytes_per_token, plan_groups
+from ..parts.base import BuildEnv, LayerCache, Residual
+from ..parts.registry import build_part
+from ..parts.spec import ModelSpec
+from ..weights.loader import Checkpoint, load_tensors
+from ..weights.random_init import model_tensor_needs
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, env: BuildEnv):
+        self.spec, self.env = spec, env
+        self.blocks = [build_part("block", b, env) for b in spec.layers]
+        self.final_norm = build_part("norm", spec.final_norm, env)
+        self.embedding: Optional[torch.Tensor] = None
+        self.head: Optional[torch.Tensor] = None
+        n_runs = len(spec.order)
+        for r, run in enumerate(spec.order):
+            if not (0 <= run.layer < len(self.blocks)):
+                raise ValueError(f"layer order entry {r} names layer {run.layer}, which does not exist")
+            if run.cache_from is not None:
+                if not (0 <= run.cache_from < r):
+                    raise ValueError(f"layer order entry {r} reads the cache of entry {run.cache_from}, which must come before it")
+                if spec.order[run.cache_from].cache_from is not None:
+                    raise ValueError(f"layer order entry {r} reads the cache of entry {run.cache_from}, which owns none")
+        # cache needs per run: a run that borrows another run's cache needs nothing of its own
+        self.run_needs: List[Sequence[object]] = [
+            () if run.cache_from is not None else tuple(self.blocks[run.layer].cache_needs()) for run in spec.order]
+        self.windows, self.run_group = plan_groups(self.run_needs)
+        self.caches: List[LayerCache] = [LayerCache() for _ in range(n_runs)]
+        self.weight_bytes = 0
+
+    # ------------------------------------------------------------------ weights
+    def load(self, model_dir: str) -> None:
+        needs = model_tensor_needs(self.spec)
+        tensors = load_tensors(Checkpoint(model_dir), needs, self.spec.duplicates, self.env.device, self.env.dtype)
+        self.embedding = tensors[self.spec.embedding.weight]
+        self.head = tensors[self.spec.head.weight]
+        for b in self.blocks:
+            b.load(tensors)
+        self.final_norm.load(tensors)
+        self.weight_bytes = sum(t.numel() * t.element_size() for t in tensors.values())
+        self.tensor_names = sorted(tensors)
+
+    # ------------------------------------------------------------------ cache
+    def kv_bytes_per_token(self) -> int:
+        return bytes_per_token(self.run_needs, self.env.dtype)
+
+    def allocate_cache(self, group_pages: Sequence[int], num_slots: int) -> None:
+        own = allocate_run_caches(self.run_needs, self.run_group, group_pages, self.windows, self.env.page_size,
+                                  num_slots, self.env.dtype, self.env.device)
+        for r, run in enumerate(self.spec.order):
+            if run.cache_from is None:
+                self.caches[r] = own[r]
+            else:
+                src = own[run.cache_from]
+                self.caches[r] = LayerCache(group=src.group, k=src.k, v=src.v, writes=False, window=src.window,
+                                            states=src.states)
+
+    def reset_slot(self, slot: int) -> None:
+        """A request starts in this slot: its fixed-size state begins at zero."""
+        for c in self.caches:
+            if c.writes:
+                for t in c.states.values():
+                    t[slot].zero_()
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, ctx) -> torch.Tensor:
+        ops, n = self.env.ops, ctx.n_tokens
+        H, V = self.spec.hidden_size, self.spec.vocab_size
+        h = ctx.ws.get("model.residual", (n, H), torch.float32)
+        ops.embed(self.embedding, ctx.token_ids, h)
+        res = Residual(h)
+        for r, run in enumerate(self.spec.order):
+            res = self.blocks[run.layer].forward(res, ctx, self.caches[r])
+        logits = ctx.ws.get("model.logits", (max(ctx.n_rows, 1), V), torch.float32)[:ctx.n_rows]
+        if ctx.n_rows > 0:
+            x = self.final_norm.forward(res, ctx, rows=ctx.logit_rows, n_rows=ctx.n_rows)
+            ops.gemm(x, self.head, logits)
+        return logits

@@ -1,0 +1,61 @@
+"""Causal grouped-query attention over the paged cache.
+
+q, k, v projections without bias (src/engine.cpp:319-341) as one product against the row-wise
+concatenation [Wq; Wk; Wv] (each output element is the same dot as with three products), position
+encoding on q and k, k (encoded) and v written to the cache (src/engine.cpp:343-353), attention of
+every token over cache positions lo..pos of its request (src/kernels.cpp:413-474), output
+projection (src/engine.cpp:364-379). The residual sum is left to the caller.
+"""
+from __future__ import annotations
+
+import math
+from typing import List
+
+import torch
+
+from .base import KVNeed, LayerCache, Mixer
+from .registry import build_part, register_part
+from .spec import AttentionSpec, TensorNeed
+
+
+class PagedAttention(Mixer):
+    def __init__(self, spec: AttentionSpec, env):
+        super().__init__(spec, env)
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError(f"attention: {spec.num_heads} heads cannot share {spec.num_kv_heads} key/value heads")
+        if spec.window < 0:
+            raise ValueError("attention: window must be >= 0")
+        self.position = build_part("position", spec.position, env)
+        self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(spec.head_dim)
+        self.w_qkv = None
+        self.w_o = None
+
+    @staticmethod
+    def tensor_needs(spec: AttentionSpec) -> List[TensorNeed]:
+        dq, dkv = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
+        return [TensorNeed(spec.q_weight, (dq, spec.hidden)), TensorNeed(spec.k_weight, (dkv, spec.hidden)),
+                TensorNeed(spec.v_weight, (dkv, spec.hidden)), TensorNeed(spec.o_weight, (spec.hidden, dq))]
+
+    def cache_needs(self):
+        return (KVNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window),)
+
+    def load(self, tensors) -> None:
+        s = self.spec
+        self.w_qkv = torch.cat([tensors[s.q_weight], tensors[s.k_weight], tensors[s.v_weight]], dim=0).contiguous()
+        self.w_o = tensors[s.o_weight]
+
+    def forward(self, x: torch.Tensor, ctx, cache: LayerCache) -> torch.Tensor:
+        s, ops, n = self.spec, self.env.ops, ctx.n_tokens
+        dq, dkv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        qkv = ctx.ws.get("attention.qkv", (n, dq + 2 * dkv), self.env.dtype)
+        ops.gemm(x[:n], self.w_qkv, qkv)
+        self.position.rotate_and_store(qkv, ctx, cache, s.num_heads, s.num_kv_heads, s.head_dim)
+        att = ctx.ws.get("attention.out", (n, dq), self.env.dtype)
+        ops.paged_attention(qkv[:, :dq], cache.k, cache.v, ctx.positions, ctx.token_seq, ctx.block_tables[cache.group],
+                            att, n, s.num_heads, s.num_kv_heads, s.head_dim, self.scale, s.window)
+        delta = ctx.ws.get("attention.delta", (n, s.hidden), torch.float32)
+        ops.gemm(att, self.w_o, delta)
+        return delta
+
+
+register_part("mixer", "attention", PagedAttention)

@@ -1,0 +1,128 @@
+"""Interfaces of the parts a layer is put together from, and the objects they are handed.
+
+No part knows which model it is in: it sees its own spec (sizes and constants), the build
+environment (device, dtype, kernels), the tensors it asked for by name, and at each step the step
+context (the flat batch) and, for mixers, its own layer's cache.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Mapping, Optional, Sequence, Tuple
+
+import torch
+
+from .spec import TensorNeed
+
+
+@dataclass
+class BuildEnv:
+    device: torch.device
+    dtype: torch.dtype  # engine precision: torch.float32 (true 32-bit path) or torch.bfloat16
+    ops: object         # the kernel interface (llmengine.ops.CudaOps)
+    page_size: int
+
+
+# ---------------------------------------------------------------------------- cache needs
+@dataclass(frozen=True)
+class KVNeed:
+    """Keys and values per token, kept in pages. window 0: all of them; W: the last W."""
+    num_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """Per-request state of fixed size, kept in the request's slot; zeroed when a request starts."""
+    name: str
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class LayerCache:
+    """What one run of a layer owns (or borrows) of the cache.
+    k, v: [pages + 1, kv_heads, page_size, head_dim]; the last page is the null page that padded
+    batch rows point at. group: which block table applies. writes: False when this run reads
+    another run's cache. states: name -> [slots + 1, *shape]; the last slot is the null slot."""
+    group: int = -1
+    k: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None
+    writes: bool = True
+    window: int = 0
+    states: Dict[str, torch.Tensor] = field(default_factory=dict)
+
+
+class Residual:
+    """The float32 residual stream h [tokens, hidden] and a float32 delta that has not been added
+    yet ([tokens, hidden], or [parts, tokens, hidden] to be summed in index order). The next norm
+    adds it while it reads h, which saves one pass over the stream."""
+
+    def __init__(self, h: torch.Tensor):
+        self.h = h
+        self.pending: Optional[torch.Tensor] = None
+
+
+class Part:
+    category = ""
+
+    def __init__(self, spec, env: BuildEnv):
+        self.spec = spec
+        self.env = env
+
+    @staticmethod
+    def tensor_needs(spec) -> List[TensorNeed]:
+        return []
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        """Receives every tensor it asked for, on the device, in the asked precision."""
+
+
+class Norm(Part):
+    category = "norm"
+
+    def forward(self, res: Residual, ctx, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> torch.Tensor:
+        """Adds res.pending into res.h (when `rows` is None) and returns the normalised rows in the
+        engine dtype. With `rows`, only those source rows are normalised and res is left alone."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    category = "position"
+
+    def rotate_and_store(self, qkv: torch.Tensor, ctx, cache: LayerCache, num_heads: int, num_kv_heads: int,
+                         head_dim: int) -> None:
+        """Encodes positions into q and k of qkv [tokens, (heads + 2 kv_heads) * head_dim] in place
+        and writes k, v of every token into its page of `cache` (if cache.writes)."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    category = "mixer"
+
+    def cache_needs(self) -> Sequence[object]:
+        """KVNeed / StateNeed objects; empty if the mixer keeps nothing between steps."""
+        return ()
+
+    def forward(self, x: torch.Tensor, ctx, cache: LayerCache) -> torch.Tensor:
+        """x: normalised activations [tokens, hidden] (engine dtype). Returns the float32 delta
+        [tokens, hidden] to be added to the residual stream."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    category = "feed_forward"
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        """As Mixer.forward, without a cache."""
+        raise NotImplementedError
+
+
+class Block(Part):
+    category = "block"
+
+    def cache_needs(self) -> Sequence[object]:
+        return ()
+
+    def forward(self, res: Residual, ctx, cache: LayerCache) -> Residual:
+        raise NotImplementedError

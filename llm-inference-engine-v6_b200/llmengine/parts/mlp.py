@@ -1,0 +1,44 @@
+"""Dense gated feed-forward: down( silu(gate(x)) * up(x) ), no bias (src/engine.cpp:383-412;
+silu as v/(1+exp(-v)), src/kernels.cpp:26-31). gate and up run as one product against [Wg; Wu]."""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from .base import FeedForward
+from .registry import register_part
+from .spec import GatedMLPSpec, TensorNeed
+
+
+class GatedMLP(FeedForward):
+    def __init__(self, spec: GatedMLPSpec, env):
+        super().__init__(spec, env)
+        if spec.activation != "silu":
+            raise ValueError(f"gated feed-forward: activation '{spec.activation}' is not implemented (silu is)")
+        self.w_gate_up = None
+        self.w_down = None
+
+    @staticmethod
+    def tensor_needs(spec: GatedMLPSpec) -> List[TensorNeed]:
+        return [TensorNeed(spec.gate_weight, (spec.intermediate, spec.hidden)),
+                TensorNeed(spec.up_weight, (spec.intermediate, spec.hidden)),
+                TensorNeed(spec.down_weight, (spec.hidden, spec.intermediate))]
+
+    def load(self, tensors) -> None:
+        s = self.spec
+        self.w_gate_up = torch.cat([tensors[s.gate_weight], tensors[s.up_weight]], dim=0).contiguous()
+        self.w_down = tensors[s.down_weight]
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        s, ops, n = self.spec, self.env.ops, ctx.n_tokens
+        gate_up = ctx.ws.get("mlp.gate_up", (n, 2 * s.intermediate), self.env.dtype)
+        ops.gemm(x[:n], self.w_gate_up, gate_up)
+        act = ctx.ws.get("mlp.act", (n, s.intermediate), self.env.dtype)
+        ops.silu_mul(gate_up, act)
+        delta = ctx.ws.get("mlp.delta", (n, s.hidden), torch.float32)
+        ops.gemm(act, self.w_down, delta)
+        return delta
+
+
+register_part("feed_forward", "gated_mlp", GatedMLP)

@@ -1,0 +1,4 @@
+"""Greedy and temperature sampling."""
+from .sampler import Sampler
+
+__all__ = ["Sampler"]
