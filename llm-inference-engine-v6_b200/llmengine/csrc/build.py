@@ -130,6 +130,17 @@ def _compile_and_link(compiler: List[str], srcs: List[str], obj_flags: List[str]
                 os.remove(o)
 
 
+def _drop_stale(build_dir: str, prefix: str, keep: str) -> None:
+    """Removes earlier builds of the same library (other hashes)."""
+    for f in os.listdir(build_dir):
+        full = os.path.join(build_dir, f)
+        if f.startswith(prefix) and full != keep and ".tmp" not in f:
+            try:
+                shutil.rmtree(full) if os.path.isdir(full) else os.remove(full)
+            except OSError:
+                pass
+
+
 def kernel_library_path(name: str, build: bool = True) -> str:
     """Path of the built kernel library `name`; compiles it first if needed and allowed."""
     if name not in KERNEL_LIBRARIES:
@@ -145,6 +156,7 @@ def kernel_library_path(name: str, build: bool = True) -> str:
     nvcc = _find_nvcc()
     _compile_and_link([nvcc], srcs, NVCC_FLAGS + ["-I", KERNEL_DIR], ["-shared"] + NVCC_FLAGS + ["-lcuda"],
                       out, f"CUDA kernels '{name}' for sm_100a")
+    _drop_stale(os.path.dirname(out), f"libllmengine_{name}_", out)
     return out
 
 
@@ -154,7 +166,7 @@ def host_module_path(build: bool = True) -> str:
     headers = [os.path.join(HOST_DIR, f) for f in os.listdir(HOST_DIR) if f.endswith((".hpp", ".h"))]
     ext = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
     flags = CXX_FLAGS + ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], "-I", HOST_DIR]
-    digest = _hash(srcs, flags + [ext, pybind11.__version__], headers)
+    digest = _hash(srcs, CXX_FLAGS + [ext, pybind11.__version__], headers)  # no absolute paths in the hash
     d = os.path.join(_build_dir(), f"host_{digest}")
     out = os.path.join(d, "_llmengine_host" + ext)
     if os.path.isfile(out):
@@ -166,6 +178,7 @@ def host_module_path(build: bool = True) -> str:
     if not cxx:
         raise BuildError("no C++ compiler found (g++)")
     _compile_and_link([cxx], srcs, flags, ["-shared"], out, "host runtime (C++)")
+    _drop_stale(os.path.dirname(d), "host_", d)
     return out
 
 
