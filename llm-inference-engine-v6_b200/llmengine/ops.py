@@ -53,6 +53,7 @@ class CudaOps:
 
     def __init__(self):
         self._libs = {}
+        self.launches = 0  # kernels launched through this object (a counter for measurements)
 
     # ------------------------------------------------------------------ loading
     def lib(self, name: str = "core"):
@@ -67,6 +68,7 @@ class CudaOps:
         return lib
 
     def _check(self, rc: int, lib) -> None:
+        self.launches += 1
         if rc != 0:
             raise KernelError(lib.llm_last_error().decode())
 

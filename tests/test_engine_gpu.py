@@ -1,0 +1,266 @@
+"""The engine on the GPU through its Python entry point: greedy and sampled generation, long
+decoding, the first tokens of a sequence, the scheduler against each request alone, and a toy mixer
+with state of its own that is registered, built and stepped without touching the framework."""
+import json
+import os
+from dataclasses import dataclass
+from typing import Tuple
+
+import numpy as np
+import pytest
+import torch
+
+import llmengine
+import plain_llama as P
+from tiny import TINY_A, TINY_B, make_model_dir, random_ids
+
+pytestmark = pytest.mark.gpu
+TOL = {"fp32": 2e-4, "bf16": 6e-2}
+
+
+@pytest.fixture(scope="module", params=[("a", "fp32"), ("a", "bf16"), ("b", "fp32"), ("b", "bf16")], ids=lambda p: f"{p[0]}-{p[1]}")
+def setup(request, tmp_path_factory):
+    name, dtype = request.param
+    cfg = {"a": TINY_A, "b": TINY_B}[name]
+    d = str(tmp_path_factory.mktemp(f"eng_{name}_{dtype}"))
+    make_model_dir(d, cfg, torch.float32 if dtype == "fp32" else torch.bfloat16)
+    pc, pw = P.read_model(d)
+    eng = llmengine.Engine(d, dtype, block_size=4 if name == "a" else 16, num_blocks=96, max_concurrent=8)
+    return cfg, eng, pc, pw, dtype
+
+
+def check_stream(pc, pw, prompt, tokens, tol, temperature=0.0, seed=0):
+    """Every generated token must be the plain implementation's choice, or differ from it only where
+    the plain scores of the two are closer than the tolerance (a near tie that rounding may flip)."""
+    logits = P.forward_logits(pc, pw, tokens[:-1]) if len(tokens) > len(prompt) else None
+    for k in range(len(prompt), len(tokens)):
+        row = logits[k - 1].astype(np.float32)
+        if temperature > 0:
+            row = row * (np.float32(1.0) / np.float32(temperature)) + P.gumbel_noise(seed, k - len(prompt), row.shape[0])
+        best = int(np.argmax(row))
+        assert tokens[k] == best or row[best] - row[tokens[k]] < 2 * tol / max(temperature, 1.0) + 2 * tol, \
+            f"token {k}: engine chose {tokens[k]}, plain chooses {best} by {row[best] - row[tokens[k]]:.4f}"
+
+
+def test_forward_logits_and_first_tokens(setup):
+    cfg, eng, pc, pw, dtype = setup
+    for n in (1, 2, 3, 21):  # the first tokens of a sequence, alone
+        ids = random_ids(n, cfg["vocab_size"], 7 + n)
+        np.testing.assert_allclose(eng.forward_logits(ids), P.forward_logits(pc, pw, ids), atol=TOL[dtype], rtol=0)
+    assert eng.cm.free_pages(0) == 96
+    assert eng.dtype == dtype and eng.max_pos == cfg["max_position_embeddings"] and eng.cfg.vocab_size == cfg["vocab_size"]
+    assert eng.has_weight("model.norm.weight") and eng.has_weight("lm_head.weight")
+
+
+def test_greedy_generation_and_long_decoding(setup):
+    cfg, eng, pc, pw, dtype = setup
+    prompt = random_ids(9, cfg["vocab_size"], 3)
+    n_new = cfg["max_position_embeddings"] - 9  # decode up to the position limit
+    out, reason = eng.generate(prompt, n_new)
+    assert reason == "length" and len(out) == cfg["max_position_embeddings"] and out[:9] == prompt
+    check_stream(pc, pw, prompt, out, TOL[dtype])
+    if dtype == "fp32":
+        assert out[:21] == P.generate(pc, pw, prompt, 12)[0]
+    assert eng.generate(prompt, 0) == (prompt, "length")
+    with pytest.raises(RuntimeError, match="position limit"):
+        eng.generate(prompt, n_new + 1)
+    with pytest.raises(ValueError, match="out of range"):
+        eng.forward_logits([cfg["vocab_size"]])
+
+
+def test_eos_stops_generation(setup, tmp_path):
+    cfg, eng, pc, pw, dtype = setup
+    prompt = random_ids(5, cfg["vocab_size"], 11)
+    out, _ = eng.generate(prompt, 6)
+    stop_at = out[7]
+    d = str(tmp_path / "eos")
+    os.makedirs(d)
+    with open(os.path.join(eng.model_dir, "config.json")) as f:
+        c = json.load(f)
+    c["eos_token_id"] = [stop_at]
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(c, f)
+    os.symlink(os.path.join(eng.model_dir, "model.safetensors"), os.path.join(d, "model.safetensors"))
+    eng2 = llmengine.Engine(d, dtype, block_size=4, num_blocks=32)
+    out2, reason2 = eng2.generate(prompt, 6)
+    assert reason2 == "stop" and out2 == out[:out.index(stop_at, 5)]
+
+
+def test_scheduler_equals_each_request_alone(setup):
+    cfg, eng, pc, pw, dtype = setup
+    lens = [5, 11, 17, 2, 30]
+    news = [8, 0, 1, 5, 12]
+    prompts = [random_ids(n, cfg["vocab_size"], 60 + n) for n in lens]
+    alone = [eng.generate(p, k) for p, k in zip(prompts, news)]
+    bm = llmengine.BlockManager(64, eng.cm.page_size)
+    sch = llmengine.ContinuousBatchScheduler(eng, bm, max_concurrent=3, max_prefill_tokens_per_step=8)
+    for p, k in zip(prompts, news):
+        sch.enqueue(p, k)
+    sch.run_until_idle()
+    assert bm.free_blocks == 64 and sch.idle
+    for r, (toks, reason), p in zip(sch.results, alone, prompts):
+        assert r.finish_reason == reason and r.prompt_len == len(p)
+        if dtype == "fp32":
+            assert list(r.token_ids) == toks
+        else:  # batching changes bf16 rounding: allow a near tie to flip, then the streams part ways
+            check_stream(pc, pw, p, list(r.token_ids), TOL[dtype])
+    eng.configure_cache(num_blocks=96, block_size=eng.cm.page_size, num_slots=8)
+
+
+def test_temperature_sampling(setup):
+    cfg, eng, pc, pw, dtype = setup
+    prompt = random_ids(6, cfg["vocab_size"], 21)
+    a, _ = eng.generate(prompt, 10, temperature=1.0, seed=42)
+    b, _ = eng.generate(prompt, 10, temperature=1.0, seed=42)
+    c, _ = eng.generate(prompt, 10, temperature=1.0, seed=43)
+    assert a == b and a != c
+    check_stream(pc, pw, prompt, a, TOL[dtype], temperature=1.0, seed=42)
+    if dtype == "fp32":
+        assert a == P.generate(pc, pw, prompt, 10, temperature=1.0, seed=42)[0]
+
+
+# ------------------------------------------------------------------------------------ a toy mixer
+@dataclass(frozen=True)
+class RunningMeanSpec:
+    kind: str
+    hidden: int
+    weight: str
+
+
+def _register_toy():
+    """A mixer with fixed-size state of its own: out_t = W * mean(x_0..x_t). Its state (the running
+    sum, one vector per request) lives in the request's slot. Defined here, in the test; the
+    framework's files are not touched."""
+    from llmengine.config.registry import Architecture, register_architecture
+    from llmengine.config.llama import LlamaConfig
+    from llmengine.models.llama import describe_llama
+    from llmengine.parts import Mixer, StateNeed, TensorNeed, register_part
+    from dataclasses import replace
+
+    class RunningMean(Mixer):
+        @staticmethod
+        def tensor_needs(spec):
+            return [TensorNeed(spec.weight, (spec.hidden, spec.hidden))]
+
+        def cache_needs(self):
+            return (StateNeed("sum", (self.spec.hidden,), torch.float32),)
+
+        def load(self, tensors):
+            self.w = tensors[self.spec.weight]
+
+        def forward(self, x, ctx, cache):
+            state = cache.states["sum"]
+            out = torch.empty(ctx.n_tokens, self.spec.hidden, dtype=torch.float32, device=x.device)
+            qoff, start, slot = ctx.seq_qoff.tolist(), ctx.seq_start.tolist(), ctx.seq_slot.tolist()
+            for s in range(ctx.n_seqs):
+                xs = x[qoff[s]:qoff[s + 1]].float()
+                run = state[slot[s]] + torch.cumsum(xs, 0)
+                state[slot[s]] = run[-1]
+                counts = torch.arange(start[s] + 1, start[s] + 1 + xs.shape[0], device=x.device).unsqueeze(1)
+                out[qoff[s]:qoff[s + 1]] = (run / counts) @ self.w.float().t()
+            return out
+
+    register_part("mixer", "running_mean", RunningMean, replace=True)
+
+    def describe(cfg):
+        spec = describe_llama(cfg)
+        layers = list(spec.layers)  # layer 1 keeps attention, layer 0 gets the toy mixer
+        layers[0] = replace(layers[0], mixer=RunningMeanSpec("running_mean", cfg.hidden_size, "model.layers.0.toy.weight"))
+        return replace(spec, architecture="ToyStateModel", layers=tuple(layers))
+
+    register_architecture(Architecture("ToyStateModel", LlamaConfig.from_dict, describe,
+                                       lambda c: dict(c.to_dict(), architectures=["ToyStateModel"])), replace=True)
+
+
+def _toy_plain(pc, w, ids):
+    T = len(ids)
+    inv = P.llama3_inv_freq(pc["head_dim"], pc["rope_theta"], False, 1, 1, 1, 0)
+    cos, sin = P.rope_tables(inv, T, pc["head_dim"])
+    h = P.embed(w["model.embed_tokens.weight"], ids)
+    x = P.rmsnorm(h, w["model.layers.0.input_layernorm.weight"], pc["rms_norm_eps"])
+    mean = np.cumsum(x, axis=0) / np.arange(1, T + 1, dtype=np.float32)[:, None]
+    h = h + P.linear(mean.astype(np.float32), w["model.layers.0.toy.weight"])
+    x = P.rmsnorm(h, w["model.layers.0.post_attention_layernorm.weight"], pc["rms_norm_eps"])
+    h = h + P.swiglu_mlp(x, w["model.layers.0.mlp.gate_proj.weight"], w["model.layers.0.mlp.up_proj.weight"], w["model.layers.0.mlp.down_proj.weight"])
+    x = P.rmsnorm(h, w["model.layers.1.input_layernorm.weight"], pc["rms_norm_eps"])
+    h = h + P.attention_block(x, pc, w, 1, cos, sin)
+    x = P.rmsnorm(h, w["model.layers.1.post_attention_layernorm.weight"], pc["rms_norm_eps"])
+    h = h + P.swiglu_mlp(x, w["model.layers.1.mlp.gate_proj.weight"], w["model.layers.1.mlp.up_proj.weight"], w["model.layers.1.mlp.down_proj.weight"])
+    return P.linear(P.rmsnorm(h, w["model.norm.weight"], pc["rms_norm_eps"]), w["lm_head.weight"])
+
+
+def test_toy_mixer_with_state_can_be_registered_built_and_stepped(tmp_path):
+    _register_toy()
+    cfg = dict(TINY_A, architectures=["ToyStateModel"])
+    d = str(tmp_path / "toy")
+    llmengine.write_random_model(d, cfg, seed=5, dtype=torch.float32, std=0.05)
+    pc, pw = P.read_model(d)
+    assert "model.layers.0.toy.weight" in pw and "model.layers.0.self_attn.q_proj.weight" not in pw
+    eng = llmengine.Engine(d, "fp32", block_size=4, num_blocks=24, max_concurrent=2)
+    ids_a, ids_b = random_ids(23, 256, 1), random_ids(14, 256, 2)
+    ref_a, ref_b = _toy_plain(pc, pw, ids_a), _toy_plain(pc, pw, ids_b)
+    np.testing.assert_allclose(eng.forward_logits(ids_a), ref_a, atol=2e-4, rtol=0)
+    # two requests interleaved in portions: each one's state stays in its own slot; a slot that is
+    # used again starts from zero
+    got_a, got_b = [], []
+    got_a.append(eng.run_step([(1, ids_a[:5], range(5))]).clone())
+    lg = eng.run_step([(1, ids_a[5:7], range(2)), (2, ids_b[:9], range(9))])
+    got_a.append(lg[:2].clone()); got_b.append(lg[2:].clone())
+    lg = eng.run_step([(2, ids_b[9:], range(5)), (1, ids_a[7:], range(16))], end=[1, 2])
+    got_b.append(lg[:5].clone()); got_a.append(lg[5:].clone())
+    np.testing.assert_allclose(torch.cat(got_a).cpu().numpy(), ref_a, atol=2e-4, rtol=0)
+    np.testing.assert_allclose(torch.cat(got_b).cpu().numpy(), ref_b, atol=2e-4, rtol=0)
+    np.testing.assert_allclose(eng.run_step([(3, ids_b, range(14))], end=[3]).cpu().numpy(), ref_b, atol=2e-4, rtol=0)
+    out, reason = eng.generate(ids_b[:4], 5)
+    assert len(out) == 9 and reason == "length" and eng.cm.free_slots == 2
+
+
+def test_layer_order_is_data(tmp_path):
+    """The order in which layers run is a list: it may name a layer twice, and a run may read an
+    earlier run's cache instead of keeping its own."""
+    from dataclasses import replace
+    from llmengine.config.registry import Architecture, register_architecture
+    from llmengine.config.llama import LlamaConfig
+    from llmengine.models.llama import describe_llama
+    from llmengine.parts import LayerRun
+
+    def describe(cfg):
+        spec = describe_llama(cfg)
+        return replace(spec, architecture="LoopedModel", order=(LayerRun(0), LayerRun(1), LayerRun(0), LayerRun(1, cache_from=1)))
+
+    register_architecture(Architecture("LoopedModel", LlamaConfig.from_dict, describe,
+                                       lambda c: dict(c.to_dict(), architectures=["LoopedModel"])), replace=True)
+    cfg = dict(TINY_A, architectures=["LoopedModel"])
+    d = str(tmp_path / "looped")
+    llmengine.write_random_model(d, cfg, seed=6, dtype=torch.float32, std=0.05)
+    pc, w = P.read_model(d)
+    ids = random_ids(19, 256, 4)
+    T, hd, nq, nkv = 19, 16, 4, 2
+    cos, sin = P.rope_tables(P.llama3_inv_freq(hd, pc["rope_theta"], False, 1, 1, 1, 0), T, hd)
+
+    def mlp(h, l):
+        p = f"model.layers.{l}."
+        x = P.rmsnorm(h, w[p + "post_attention_layernorm.weight"], pc["rms_norm_eps"])
+        return h + P.swiglu_mlp(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+
+    h = P.embed(w["model.embed_tokens.weight"], ids)
+    kv1 = None
+    for run, (l, borrow) in enumerate([(0, False), (1, False), (0, False), (1, True)]):
+        p = f"model.layers.{l}."
+        x = P.rmsnorm(h, w[p + "input_layernorm.weight"], pc["rms_norm_eps"])
+        q = P.apply_rope(P.linear(x, w[p + "self_attn.q_proj.weight"]).reshape(T, nq, hd), cos, sin)
+        if borrow:
+            k, v = kv1  # keys and values that run 1 wrote
+        else:
+            k = P.apply_rope(P.linear(x, w[p + "self_attn.k_proj.weight"]).reshape(T, nkv, hd), cos, sin)
+            v = P.linear(x, w[p + "self_attn.v_proj.weight"]).reshape(T, nkv, hd)
+            if run == 1:
+                kv1 = (k, v)
+        h = h + P.linear(P.causal_gqa_attention(q, k, v), w[p + "self_attn.o_proj.weight"])
+        h = mlp(h, l)
+    ref = P.linear(P.rmsnorm(h, w["model.norm.weight"], pc["rms_norm_eps"]), w["lm_head.weight"])
+    eng = llmengine.Engine(d, "fp32", block_size=4, num_blocks=24)
+    np.testing.assert_allclose(eng.forward_logits(ids), ref, atol=2e-4, rtol=0)
+    first = eng.run_step([(9, ids[:11], range(11))]).clone()  # the logits tensor is scratch of the next step
+    second = eng.run_step([(9, ids[11:], range(8))], end=[9])
+    np.testing.assert_allclose(torch.cat([first, second]).cpu().numpy(), ref, atol=2e-4, rtol=0)

@@ -1,0 +1,277 @@
+"""Each CUDA kernel alone against a plain float32 reference of the same op, at sizes other than
+the engine's tiny models use (non powers of two, tails, strided views)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from llmengine.ops import get_ops
+    return get_ops()
+
+
+def tol(dt, scale=1.0):
+    return dict(atol=2e-5 * scale, rtol=2e-5) if dt == torch.float32 else dict(atol=1.6e-2 * scale, rtol=1.6e-2)
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * std).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_embed(ops, dt):
+    table = rnd(301, 200, dtype=dt)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 200, dtype=torch.float32, device=DEV)
+    ops.embed(table, ids, out)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("dim", [16, 257, 2048, 5000])
+def test_rmsnorm_variants(ops, dt, dim):
+    n, eps = 7, 1e-5
+    h = rnd(n, dim, seed=1)
+    w = rnd(dim, seed=2) * 0.1 + 1.0
+    ref = torch.from_numpy(P.rmsnorm(h.cpu().numpy(), w.cpu().numpy(), eps)).to(DEV)
+    out = torch.empty(n, dim, dtype=dt, device=DEV)
+    ops.rmsnorm(h, w, eps, out)
+    torch.testing.assert_close(out.float(), ref, **tol(dt, 4))
+    # fused residual sum: h += delta, then norm; also a stack of partial sums added in order
+    for delta in (rnd(n, dim, seed=3), rnd(3, n, dim, seed=4)):
+        h2 = h.clone()
+        dsum = delta if delta.dim() == 2 else delta[0] + delta[1] + delta[2]
+        ops.rmsnorm(h2, w, eps, out, delta=delta)
+        torch.testing.assert_close(h2, h + dsum, atol=1e-6, rtol=1e-6)
+        ref2 = torch.from_numpy(P.rmsnorm((h + dsum).cpu().numpy(), w.cpu().numpy(), eps)).to(DEV)
+        torch.testing.assert_close(out.float(), ref2, **tol(dt, 4))
+    # chosen rows only (the logits rows): h stays as it is
+    rows = torch.tensor([6, 0, 6], dtype=torch.int32, device=DEV)
+    h3, d3 = h.clone(), rnd(n, dim, seed=5)
+    out3 = torch.empty(3, dim, dtype=dt, device=DEV)
+    ops.rmsnorm(h3, w, eps, out3, delta=d3, rows=rows)
+    assert torch.equal(h3, h)
+    ref3 = torch.from_numpy(P.rmsnorm((h + d3)[rows.long()].cpu().numpy(), w.cpu().numpy(), eps)).to(DEV)
+    torch.testing.assert_close(out3.float(), ref3, **tol(dt, 4))
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_silu_mul_and_residual_add(ops, dt):
+    n, ff = 5, 1000
+    gu = rnd(n, 2 * ff, dtype=dt, seed=6, std=2.0)
+    out = torch.empty(n, ff, dtype=dt, device=DEV)
+    ops.silu_mul(gu, out)
+    g, u = gu[:, :ff].float().cpu().numpy(), gu[:, ff:].float().cpu().numpy()
+    torch.testing.assert_close(out.float().cpu(), torch.from_numpy(P.silu(g) * u), **tol(dt, 4))
+    h, d = rnd(n, 333, seed=7), rnd(2, n, 333, seed=8)
+    want = h + d[0] + d[1]
+    ops.residual_add(h, d)
+    torch.testing.assert_close(h, want, atol=1e-6, rtol=1e-6)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 130, 257), (65, 64, 64), (128, 509, 192), (200, 176, 1000), (9, 2048, 96)])
+def test_gemm(ops, dt, M, N, K):
+    a, w = rnd(M, K, dtype=dt, seed=9), rnd(N, K, dtype=dt, seed=10, std=0.1)
+    ref = a.double() @ w.double().t()
+    for out_dt in {dt, torch.float32}:
+        out = torch.empty(M, N, dtype=out_dt, device=DEV)
+        ops.gemm(a, w, out)
+        t = tol(out_dt, math.sqrt(K) * 0.1)
+        torch.testing.assert_close(out.double(), ref, **t)
+    # strided rows (views into wider buffers), as the engine passes the q part of qkv
+    wide_a = rnd(M, K + 13, dtype=dt, seed=11)
+    wide_out = torch.zeros(M, N + 5, dtype=torch.float32, device=DEV)
+    ops.gemm(wide_a[:, 3:3 + K], w, wide_out[:, 2:2 + N])
+    torch.testing.assert_close(wide_out[:, 2:2 + N].double(), wide_a[:, 3:3 + K].double() @ w.double().t(),
+                               **tol(torch.float32 if dt == torch.float32 else dt, math.sqrt(K) * 0.1))
+    assert float(wide_out[:, :2].abs().max()) == 0 and float(wide_out[:, 2 + N:].abs().max()) == 0
+
+
+def test_gemm_float32_rows_do_not_depend_on_the_batch(ops):
+    """A row's result is bit-identical whether it is computed alone or among others."""
+    a, w = rnd(77, 300, seed=12), rnd(190, 300, seed=13)
+    full = torch.empty(77, 190, device=DEV)
+    ops.gemm(a, w, full)
+    for r in (0, 40, 76):
+        one = torch.empty(1, 190, device=DEV)
+        ops.gemm(a[r:r + 1], w, one)
+        assert torch.equal(one[0], full[r])
+
+
+def _paged_setup(dt, nkv, hd, page, seq_lens, n_pages, seed=0):
+    """Random K,V for each request, scattered into shuffled pages. -> caches, tables, dense K/V."""
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    kc = torch.zeros(n_pages + 1, nkv, page, hd, dtype=dt, device=DEV)
+    vc = torch.zeros_like(kc)
+    max_blocks = max((L + page - 1) // page for L in seq_lens)
+    table = torch.full((len(seq_lens), max_blocks), -1, dtype=torch.int32)
+    dense = []
+    for s, L in enumerate(seq_lens):
+        K = (torch.randn(L, nkv, hd, generator=g)).to(dt)
+        V = (torch.randn(L, nkv, hd, generator=g)).to(dt)
+        dense.append((K, V))
+        for b in range((L + page - 1) // page):
+            pg = perm.pop()
+            table[s, b] = pg
+            n = min(page, L - b * page)
+            kc[pg, :, :n] = K[b * page:b * page + n].transpose(0, 1).to(DEV)
+            vc[pg, :, :n] = V[b * page:b * page + n].transpose(0, 1).to(DEV)
+    return kc, vc, table.to(DEV), dense
+
+
+def _attention_ref(q, K, V, pos, nq, nkv, hd, scale, window):
+    lo = max(0, pos - window + 1) if window > 0 else 0
+    K, V = K[lo:pos + 1].float(), V[lo:pos + 1].float()
+    out = torch.empty(nq, hd)
+    for h in range(nq):
+        s = (K[:, h // (nq // nkv)] @ q[h].float()) * scale
+        out[h] = torch.softmax(s, 0) @ V[:, h // (nq // nkv)]
+    return out.reshape(-1)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,page,window", [(8, 2, 64, 16, 0), (6, 1, 32, 4, 0), (5, 5, 48, 8, 0), (4, 2, 16, 4, 9),
+                                                   (8, 4, 128, 16, 40), (2, 1, 256, 16, 0), (3, 3, 80, 64, 0)])
+def test_paged_attention(ops, dt, nq, nkv, hd, page, window):
+    seq_lens = [1, 37, 130, 64]
+    kc, vc, table, dense = _paged_setup(dt, nkv, hd, page, seq_lens, 40 if page >= 8 else 80)
+    # tokens: a portion of request 2 (positions 100..129), one decoded token of each other request
+    toks = [(0, 0), (1, 36), (3, 63), (3, 15), (3, 16)] + [(2, p) for p in range(100, 130)]
+    q = rnd(len(toks), nq * hd, dtype=dt, seed=20)
+    positions = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    token_seq = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    out = torch.empty(len(toks), nq * hd, dtype=dt, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ops.paged_attention(q, kc, vc, positions, token_seq, table, out, len(toks), nq, nkv, hd, scale, window)
+    for i, (s, p) in enumerate(toks):
+        ref = _attention_ref(q[i].cpu().view(nq, hd), dense[s][0], dense[s][1], p, nq, nkv, hd, scale, window)
+        torch.testing.assert_close(out[i].float().cpu(), ref, **tol(dt, 2))
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("special", [0, 15, 16, 31, 32, 255, 256, 499])
+def test_attention_finds_one_far_key_among_hundreds(ops, dt, special):
+    """Random values hide a skipped key (its weight is ~1/500). Here one key is made to match the
+    query, so that the output must be that key's value: a key lost at a page's edge, at the start or
+    at the end of the range shows as an error of order one."""
+    nq, nkv, hd, page, L = 4, 2, 64, 16, 500
+    kc, vc, table, dense = _paged_setup(dt, nkv, hd, page, [L], 40, seed=special)
+    q = rnd(1, nq * hd, dtype=dt, seed=21)
+    K, V = dense[0]
+    pg, off = int(table[0, special // page]), special % page
+    for h in range(nkv):  # both kv heads: key `special` := 4 * (a query of that group), others stay random
+        K[special, h] = (q[0].cpu().view(nq, hd)[h * 2].float() * 4).to(dt)
+        kc[pg, h, off] = K[special, h].to(DEV)
+    positions = torch.tensor([L - 1], dtype=torch.int32, device=DEV)
+    out = torch.empty(1, nq * hd, dtype=dt, device=DEV)
+    ops.paged_attention(q, kc, vc, positions, torch.zeros(1, dtype=torch.int32, device=DEV), table, out, 1, nq, nkv, hd, 1.0, 0)
+    ref = _attention_ref(q[0].cpu().view(nq, hd), K, V, L - 1, nq, nkv, hd, 1.0, 0)
+    o = out[0].float().cpu().view(nq, hd)
+    torch.testing.assert_close(o.reshape(-1), ref, **tol(dt, 2))
+    for h in (0, 2):  # the matching heads return (almost exactly) the special key's value
+        assert (o[h] - V[special, h // 2].float()).abs().max() < 0.05
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_attention_window_edge(ops, dt):
+    """The key just outside the window must not count, the one just inside must."""
+    nq, nkv, hd, page, L, W = 2, 1, 32, 8, 100, 24
+    for special, inside in ((L - W, True), (L - W - 1, False)):
+        kc, vc, table, dense = _paged_setup(dt, nkv, hd, page, [L], 20, seed=3)
+        q = rnd(1, nq * hd, dtype=dt, seed=22)
+        K, V = dense[0]
+        K[special, 0] = (q[0].cpu().view(nq, hd)[0].float() * 4).to(dt)
+        kc[int(table[0, special // page]), 0, special % page] = K[special, 0].to(DEV)
+        out = torch.empty(1, nq * hd, dtype=dt, device=DEV)
+        ops.paged_attention(q, kc, vc, torch.tensor([L - 1], dtype=torch.int32, device=DEV),
+                            torch.zeros(1, dtype=torch.int32, device=DEV), table, out, 1, nq, nkv, hd, 1.0, W)
+        ref = _attention_ref(q[0].cpu().view(nq, hd), K, V, L - 1, nq, nkv, hd, 1.0, W)
+        torch.testing.assert_close(out[0].float().cpu(), ref, **tol(dt, 2))
+        hit = (out[0].float().cpu()[:hd] - V[special, 0].float()).abs().max() < 0.05
+        assert bool(hit) == inside
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,page", [(4, 2, 16, 4), (6, 1, 32, 16), (3, 3, 80, 8)])
+def test_rope_and_cache_write(ops, dt, nq, nkv, hd, page):
+    inv = P.llama3_inv_freq(hd, 500000.0, True, 8.0, 1.0, 4.0, 64)
+    cos, sin = P.rope_tables(inv, 300, hd)
+    cos_d = torch.from_numpy(cos[:, :hd // 2].copy()).to(DEV)
+    sin_d = torch.from_numpy(sin[:, :hd // 2].copy()).to(DEV)
+    toks = [(0, 0), (0, 1), (1, 163), (1, 150), (2, 17)]
+    n = len(toks)
+    qkv = rnd(n, (nq + 2 * nkv) * hd, dtype=dt, seed=30)
+    orig = qkv.clone()
+    table = torch.tensor([[3, 1] + [-1] * 40, [(5 + i) for i in range(42)], [50, 51, 52, 53, 54] + [-1] * 37], dtype=torch.int32, device=DEV)
+    kc = torch.zeros(60, nkv, page, hd, dtype=dt, device=DEV)
+    vc = torch.zeros_like(kc)
+    positions = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    token_seq = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    ops.rope_kv_write(qkv, positions, token_seq, table, cos_d, sin_d, kc, vc, n, nq, nkv, hd)
+    o = orig.float().cpu().numpy()
+    pos = positions.cpu().numpy()
+    q_ref = P.apply_rope(o[:, :nq * hd].reshape(n, nq, hd), cos[pos], sin[pos])
+    k_ref = P.apply_rope(o[:, nq * hd:(nq + nkv) * hd].reshape(n, nkv, hd), cos[pos], sin[pos])
+    v_ref = o[:, (nq + nkv) * hd:].reshape(n, nkv, hd)
+    torch.testing.assert_close(qkv[:, :nq * hd].float().cpu(), torch.from_numpy(q_ref.reshape(n, -1)), **tol(dt, 4))
+    written = torch.zeros(60, page, dtype=torch.bool)
+    for i, (s, p) in enumerate(toks):
+        pg = int(table[s, p // page])
+        written[pg, p % page] = True
+        torch.testing.assert_close(kc[pg, :, p % page].float().cpu(), torch.from_numpy(k_ref[i]), **tol(dt, 4))
+        assert torch.equal(vc[pg, :, p % page].float().cpu(), torch.from_numpy(v_ref[i]))
+    # nothing else was touched
+    assert float(kc.float().abs().sum(dim=(1, 3)).cpu()[~written].sum()) == 0
+    # no tables: q, k stay as they are, k and v are only stored
+    qkv2 = orig.clone()
+    ops.rope_kv_write(qkv2, positions, token_seq, table, None, None, kc, vc, n, nq, nkv, hd)
+    assert torch.equal(qkv2[:, :nq * hd], orig[:, :nq * hd])
+    assert torch.equal(kc[int(table[1, 163 // page]), :, 163 % page].reshape(-1), orig[2, nq * hd:(nq + nkv) * hd])
+
+
+def test_sampling_greedy_and_temperature(ops):
+    V = 5003
+    logits = rnd(6, V, seed=40)
+    logits[0, 100] = logits[0, 4000] = 50.0  # tie: the first index wins
+    logits[1, V - 1] = 60.0
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    ops.sample(logits, out)
+    assert out.tolist() == [100, V - 1] + logits[2:].argmax(-1).tolist()
+    temps = torch.tensor([0.0, 1.0, 0.7, 1.5, 1.0, 1.0], device=DEV)
+    seeds = torch.tensor([1, 2, 3, 4, 5, 5], dtype=torch.int32, device=DEV)
+    draws = torch.tensor([0, 0, 7, 3, 1, 2], dtype=torch.int32, device=DEV)
+    ops.sample(logits, out, temps, seeds, draws)
+    host = logits.cpu().numpy()
+    want = [P.sample_token(host[r], float(temps[r]), int(seeds[r]), int(draws[r])) for r in range(6)]
+    assert out.tolist() == want and out[4] != out[5] or want[4] == want[5]
+    # a draw follows softmax(logits / T)
+    small = torch.tensor([[0.0, 1.0, 2.0, -1.0]], device=DEV).repeat(4000, 1).contiguous()
+    o = torch.empty(4000, dtype=torch.int32, device=DEV)
+    ops.sample(small, o, torch.ones(4000, device=DEV), torch.full((4000,), 77, dtype=torch.int32, device=DEV),
+               torch.arange(4000, dtype=torch.int32, device=DEV))
+    freq = torch.bincount(o.long(), minlength=4).float().cpu() / 4000
+    assert (freq - torch.softmax(small[0].cpu(), 0)).abs().max() < 0.03
+
+
+def test_kernels_refuse_what_they_cannot_take(ops):
+    from llmengine.ops import KernelError
+    with pytest.raises(KernelError, match="head_dim"):
+        ops.paged_attention(rnd(1, 2 * 512), torch.zeros(2, 1, 4, 512, device=DEV), torch.zeros(2, 1, 4, 512, device=DEV),
+                            torch.zeros(1, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                            torch.zeros(1, 1, dtype=torch.int32, device=DEV), torch.empty(1, 1024, device=DEV), 1, 2, 1, 512, 1.0)
+    with pytest.raises(KernelError, match="CUDA tensor"):
+        ops.gemm(torch.zeros(2, 2), torch.zeros(2, 2), torch.zeros(2, 2))
+    with pytest.raises(KernelError):
+        ops.gemm(rnd(2, 2).half(), rnd(2, 2).half(), torch.empty(2, 2, device=DEV))

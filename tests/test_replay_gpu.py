@@ -1,0 +1,80 @@
+"""Trace replay through bin/trace_run (a subprocess, as a user runs it) against the plain
+implementation: each request alone and whole; most of it in one step and the last 32 tokens one by
+one; in portions of changing size down to two tokens; mixed, up to four live requests with so few
+pages that they are used again. In true 32-bit and in bfloat16, for both tiny configurations."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+from tiny import (TINY, make_model_dir, random_ids, round64, run_trace, trace_mixed, trace_portions, trace_tail,
+                  trace_whole, Trace)
+
+pytestmark = pytest.mark.gpu
+
+LENS = {"a": [5, 64, 33, 97, 128], "b": [2, 23, 64, 150, 255, 201]}  # short ones first: four are live at once
+# float32: the engine's own arithmetic is float32 throughout; the plain implementation differs by
+# summation order only. bfloat16: weights are the same bf16 values on both sides; the difference is
+# the rounding of activations to bf16 between kernels.
+TOL = {"float32": 2e-4, "bfloat16": 6e-2}
+
+
+@pytest.fixture(scope="module", params=[("a", "float32"), ("a", "bfloat16"), ("b", "float32"), ("b", "bfloat16")],
+                ids=lambda p: f"{p[0]}-{p[1]}")
+def replayed(request, tmp_path_factory):
+    name, dtype = request.param
+    cfg, page = TINY[name]
+    d = str(tmp_path_factory.mktemp(f"model_{name}_{dtype}"))
+    make_model_dir(d, cfg, torch.float32 if dtype == "float32" else torch.bfloat16)
+    pc, pw = P.read_model(d)
+    reqs = {f"r{i}": random_ids(n, cfg["vocab_size"], 100 + i) for i, n in enumerate(LENS[name])}
+    plain = {k: P.forward_logits(pc, pw, ids) for k, ids in reqs.items()}
+    # one process replays the four cuts one after another; request names are made distinct per cut
+    cuts = {"whole": trace_whole, "tail": trace_tail, "portions": trace_portions}
+    full, spans = Trace(), {}
+    for cut, fn in cuts.items():
+        t = fn({f"{cut}.{k}": v for k, v in reqs.items()})
+        spans[cut] = (len(full.steps), len(full.steps) + len(t.steps))
+        full.extend(t)
+    longest = max(round64(len(v)) for v in reqs.values())
+    max_tokens = longest + 3 * 64  # room for the longest request and three short ones: pages are reused
+    t = trace_mixed({f"mixed.{k}": v for k, v in reqs.items()}, max_tokens, seed=5)
+    spans["mixed"] = (len(full.steps), len(full.steps) + len(t.steps))
+    full.extend(t)
+    out = str(tmp_path_factory.mktemp(f"out_{name}_{dtype}"))
+    rows = run_trace(d, dtype, full, out, max_tokens, page, cfg["vocab_size"])
+    return dtype, reqs, plain, rows, t
+
+
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
+def test_cut_matches_plain(replayed, cut):
+    dtype, reqs, plain, rows, _ = replayed
+    worst = (0.0, None)
+    for k, ids in reqs.items():
+        for p in range(len(ids)):
+            row = rows[(f"{cut}.{k}", p)]
+            err = float(np.abs(row - plain[k][p]).max())
+            if err > worst[0]:
+                worst = (err, (k, p))
+    assert worst[0] < TOL[dtype], f"{cut}: first look at request/position {worst[1]} (max error {worst[0]:.3e})"
+
+
+def test_cuts_agree_with_one_another(replayed):
+    """The logits at a position do not depend on how the tokens were cut into steps, on what else
+    was in the batch, or on which pages were used, beyond rounding."""
+    dtype, reqs, plain, rows, _ = replayed
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    for k, ids in reqs.items():
+        for p in range(len(ids)):
+            base = rows[(f"whole.{k}", p)]
+            for cut in ("tail", "portions", "mixed"):
+                err = float(np.abs(rows[(f"{cut}.{k}", p)] - base).max())
+                assert err < tol, f"{cut} vs whole differ at request {k} position {p}: {err:.3e}"
+
+
+def test_mixed_trace_is_really_mixed(replayed):
+    """The trace used above has steps with four live requests, prompt portions beside single tokens."""
+    *_, t = replayed
+    assert max(len(s["entries"]) for s in t.steps) == 4
+    assert any(len({len(e["tokens"]) == 1 for e in s["entries"]}) == 2 for s in t.steps)
+    assert any(len(e["tokens"]) == 2 for s in t.steps for e in s["entries"])
