@@ -36,7 +36,8 @@ CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wex
 # name -> CUDA sources. "core" is what every model and precision needs; "tensorcore" holds the
 # tcgen05/TMA kernels that only the bfloat16 path uses.
 KERNEL_LIBRARIES: Dict[str, List[str]] = {
-    "core": ["elementwise.cu", "gemm_simt.cu", "rope_kv.cu", "attention_simt.cu", "sampling.cu"],
+    "core": ["status.cu", "elementwise.cu", "gemm_simt.cu", "rope_kv.cu", "attention_simt.cu", "sampling.cu"],
+    "tensorcore": ["status.cu", "gemm_tc.cu"],
 }
 HOST_SOURCES = ["cache_manager.cpp", "scheduler.cpp", "bindings.cpp"]
 
@@ -154,7 +155,7 @@ def kernel_library_path(name: str, build: bool = True) -> str:
     if not build:
         raise BuildError(f"kernel library '{name}' is not built")
     nvcc = _find_nvcc()
-    _compile_and_link([nvcc], srcs, NVCC_FLAGS + ["-I", KERNEL_DIR], ["-shared"] + NVCC_FLAGS + ["-lcuda"],
+    _compile_and_link([nvcc], srcs, NVCC_FLAGS + ["-I", KERNEL_DIR], ["-shared"] + NVCC_FLAGS,
                       out, f"CUDA kernels '{name}' for sm_100a")
     _drop_stale(os.path.dirname(out), f"libllmengine_{name}_", out)
     return out

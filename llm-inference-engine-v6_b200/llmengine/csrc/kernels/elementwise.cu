@@ -8,20 +8,6 @@
 // (src/kernels.cpp:59-66).
 #include "common.cuh"
 
-#include <cstdarg>
-#include <cstring>
-
-static thread_local char g_last_error[512] = "";
-
-extern "C" const char* llm_last_error() { return g_last_error; }
-
-void llm_set_error(const char* fmt, ...) {
-  va_list ap;
-  va_start(ap, fmt);
-  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
-  va_end(ap);
-}
-
 // ------------------------------------------------------------------------------------ embedding
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
@@ -148,5 +134,67 @@ extern "C" int llm_silu_mul(const void* in, void* out, int dtype, int n_rows, in
   else
     LLM_REQUIRE(false, "silu_mul: unknown dtype %d", dtype);
   LLM_CHECK_LAUNCH("silu_mul");
+  return LLM_OK;
+}
+
+// ------------------------------------------------------------------------------------ partial sums
+// K-split matrix products leave float32 partials [parts, rows, width]; these kernels add them in
+// index order (a fixed order: the result does not depend on timing) while doing their own work.
+template <typename T>
+__global__ void reduce_partials_kernel(const float* __restrict__ partials, int n_partials, size_t stride,
+                                       T* __restrict__ out, size_t total) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  float x = partials[i];
+  for (int p = 1; p < n_partials; ++p) x += partials[(size_t)p * stride + i];
+  out[i] = from_f32<T>(x);
+}
+
+extern "C" int llm_reduce_partials(const float* partials, int n_partials, long long stride, void* out, int out_dtype,
+                                   long long total, cudaStream_t stream) {
+  if (total == 0) return LLM_OK;
+  LLM_REQUIRE(total > 0 && n_partials >= 1, "reduce_partials: bad sizes");
+  const int blocks = ceil_div(total, 256);
+  if (out_dtype == LLM_F32)
+    reduce_partials_kernel<float><<<blocks, 256, 0, stream>>>(partials, n_partials, (size_t)stride, (float*)out, (size_t)total);
+  else if (out_dtype == LLM_BF16)
+    reduce_partials_kernel<bf16><<<blocks, 256, 0, stream>>>(partials, n_partials, (size_t)stride, (bf16*)out, (size_t)total);
+  else
+    LLM_REQUIRE(false, "reduce_partials: unknown dtype %d", out_dtype);
+  LLM_CHECK_LAUNCH("reduce_partials");
+  return LLM_OK;
+}
+
+// partials: [parts, rows, 2*ff] float32 (gate | up); out [rows, ff] = silu(sum gate) * (sum up).
+template <typename T>
+__global__ void silu_mul_partials_kernel(const float* __restrict__ partials, int n_partials, size_t stride,
+                                         T* __restrict__ out, int ff, size_t total) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t r = i / ff;
+  const int c = (int)(i - r * ff);
+  const size_t gi = r * 2 * ff + c, ui = gi + ff;
+  float g = partials[gi], u = partials[ui];
+  for (int p = 1; p < n_partials; ++p) {
+    g += partials[(size_t)p * stride + gi];
+    u += partials[(size_t)p * stride + ui];
+  }
+  const float s = g / (1.0f + expf(-g));
+  out[i] = from_f32<T>(s * u);
+}
+
+extern "C" int llm_silu_mul_partials(const float* partials, int n_partials, long long stride, void* out, int out_dtype,
+                                     int n_rows, int ff, cudaStream_t stream) {
+  if (n_rows == 0) return LLM_OK;
+  LLM_REQUIRE(n_rows > 0 && ff > 0 && n_partials >= 1, "silu_mul_partials: bad sizes");
+  const size_t total = (size_t)n_rows * ff;
+  const int blocks = ceil_div((long long)total, 256);
+  if (out_dtype == LLM_F32)
+    silu_mul_partials_kernel<float><<<blocks, 256, 0, stream>>>(partials, n_partials, (size_t)stride, (float*)out, ff, total);
+  else if (out_dtype == LLM_BF16)
+    silu_mul_partials_kernel<bf16><<<blocks, 256, 0, stream>>>(partials, n_partials, (size_t)stride, (bf16*)out, ff, total);
+  else
+    LLM_REQUIRE(false, "silu_mul_partials: unknown dtype %d", out_dtype);
+  LLM_CHECK_LAUNCH("silu_mul_partials");
   return LLM_OK;
 }

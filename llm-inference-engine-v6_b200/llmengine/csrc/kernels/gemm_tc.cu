@@ -1,0 +1,454 @@
+// bfloat16 matrix product on the 5th-generation tensor cores (tcgen05), operands brought to shared
+// memory by TMA, float32 accumulator in tensor memory.
+//
+//   D[ra, rb] = sum_k A[ra, k] * B[rb, k]        A: [RA, K], B: [RB, K], both with k contiguous
+//
+// Both uses of the engine are this one kernel:
+//   * many tokens (prompt portions): A = activations [tokens, K], B = weights [N, K],
+//     out[token, n] = D[token, n]; tiles of 128 tokens x BN outputs;
+//   * few tokens (decoding): A = weights [N, K] (128 weight rows fill the 128 accumulator lanes),
+//     B = activations [tokens <= BN, K], out[token, n] = D[n, token] ("swapped"); the K range can be
+//     cut into splits, each writing its own float32 partial [split, tokens, N]; the consumer adds
+//     the partials in index order, so the result does not depend on timing.
+//
+// One CTA computes one output tile: warp 0 lane 0 issues the TMA loads into a ring of stages,
+// warp 1 lane 0 issues tcgen05.mma (one instruction covers 128 x BN x 16) and commits each
+// stage back to the producer, all four warps read the accumulator with tcgen05.ld and store it.
+// Every wait on an mbarrier is bounded: after about a second it records an error code, the
+// other roles see the abort flag, outstanding copies are waited for (bounded too), tensor memory is
+// freed and the kernel returns; the host reports the code.
+//
+// The reference computes the same products with a scalar loop (matmul_f32, src/kernels.cpp:33-57).
+#include <cuda.h>
+
+#include <algorithm>
+#include <mutex>
+#include <tuple>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;  // accumulator lanes = rows of A per tile
+constexpr int BK = 64;   // 64 bf16 = 128 bytes = one row of the 128-byte swizzle
+constexpr int A_BYTES = BM * BK * 2;
+constexpr long long WAIT_CYCLES = 2000000000LL;  // about one second
+
+enum : int { ERR_PRODUCER = 1, ERR_MMA = 2, ERR_EPILOGUE = 3, ERR_DRAIN = 4 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait. Returns false if the phase did not complete in time or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* error_out, int code) {
+  const long long t0 = clock64();
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > WAIT_CYCLES) {
+        *abort_flag = code;
+        atomicCAS(error_out, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile with 128-byte swizzle; rows are 128 bytes apart,
+// groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);  // start address, bits [0,14)
+  d |= (uint64_t)1 << 16;                   // leading byte offset (unused with swizzle), bits [16,30)
+  d |= (uint64_t)(1024 >> 4) << 32;         // stride byte offset, bits [32,46)
+  d |= (uint64_t)1 << 46;                   // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                   // 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor of kind::f16: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <typename TO>
+__device__ __forceinline__ void store_row16(TO* dst, const float* v, int valid, bool aligned);
+
+template <>
+__device__ __forceinline__ void store_row16<float>(float* dst, const float* v, int valid, bool aligned) {
+  if (valid == 16 && aligned) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else {
+    for (int i = 0; i < valid; ++i) dst[i] = v[i];
+  }
+}
+
+template <>
+__device__ __forceinline__ void store_row16<bf16>(bf16* dst, const float* v, int valid, bool aligned) {
+  if (valid == 16 && aligned) {
+    uint32_t p[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      p[i] = *reinterpret_cast<uint32_t*>(&t);
+    }
+    reinterpret_cast<uint4*>(dst)[0] = make_uint4(p[0], p[1], p[2], p[3]);
+    reinterpret_cast<uint4*>(dst)[1] = make_uint4(p[4], p[5], p[6], p[7]);
+  } else {
+    for (int i = 0; i < valid; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+  }
+}
+
+// grid: (tiles of A rows, tiles of B rows, K splits); block: 128 threads.
+template <int BN, bool SWAP, typename TO>
+__global__ void __launch_bounds__(128)
+    gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TO* __restrict__ out,
+                   int RA, int RB, int k_tiles, int k_tiles_per_split, long long ldo, long long split_stride, int stages,
+                   int* __restrict__ error_out) {
+  constexpr int B_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)stages * STAGE_BYTES);
+  uint64_t* empty = full + stages;
+  uint64_t* acc_ready = empty + stages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int a_row0 = blockIdx.x * BM, b_row0 = blockIdx.y * BN;
+  const int kt_begin = blockIdx.z * k_tiles_per_split;
+  const int kt_end = min(k_tiles, kt_begin + k_tiles_per_split);
+  const int n_iter = kt_end - kt_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_ready, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------------------------------------------------------- producer: TMA loads
+    int issued = 0;
+    bool ok = true;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int s = it % stages;
+      const uint32_t ph = (uint32_t)(it / stages) & 1u;
+      ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag, error_out, ERR_PRODUCER);
+      if (!ok) break;
+      uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
+      mbar_expect_tx(&full[s], STAGE_BYTES);
+      tma_load_2d(sa, &map_a, (kt_begin + it) * BK, a_row0, &full[s]);
+      tma_load_2d(sa + A_BYTES, &map_b, (kt_begin + it) * BK, b_row0, &full[s]);
+      issued = it + 1;
+    }
+    if (!ok || *abort_flag) {
+      // wait (bounded) for the copies already issued, so that none lands after the CTA has left
+      const int first = issued > stages ? issued - stages : 0;
+      for (int it = first; it < issued; ++it) {
+        const long long t0 = clock64();
+        while (!mbar_try_wait(&full[it % stages], (uint32_t)(it / stages) & 1u)) {
+          if (clock64() - t0 > WAIT_CYCLES) {
+            atomicCAS(error_out, 0, ERR_DRAIN);
+            break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------------------------------------------------------- tensor-core issue
+    constexpr uint32_t idesc = instr_desc(BN);
+    bool ok = true;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int s = it % stages;
+      const uint32_t ph = (uint32_t)(it / stages) & 1u;
+      ok = mbar_wait(&full[s], ph, abort_flag, error_out, ERR_MMA);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
+      const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_BYTES);
+#pragma unroll
+      for (int k = 0; k < BK / 16; ++k)  // 16 bf16 = 32 bytes further along the swizzled row: +2 in the address field
+        mma_f16(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (it > 0 || k > 0) ? 1u : 0u);
+      mma_commit(&empty[s]);  // arrives when the MMAs above have read the stage
+    }
+    if (ok) mma_commit(acc_ready);
+  }
+  __syncwarp();
+
+  // ------------------------------------------------------------------ epilogue: all four warps
+  bool ready = n_iter > 0;
+  if (ready) ready = mbar_wait(acc_ready, 0, abort_flag, error_out, ERR_EPILOGUE);
+  ready = __all_sync(0xffffffffu, ready);  // a warp reads tensor memory together or not at all
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  TO* o = out + (size_t)blockIdx.z * split_stride;
+  const int ra = a_row0 + warp * 32 + lane;
+  if (ready || n_iter == 0) {
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 16) {
+      float v[16];
+      if (n_iter > 0) {
+        tmem_load16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+      }
+      const int rb0 = b_row0 + c0;
+      if (!SWAP) {
+        if (ra < RA && rb0 < RB) {
+          TO* dst = o + (size_t)ra * ldo + rb0;
+          const bool aligned = (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
+          store_row16<TO>(dst, v, min(16, RB - rb0), aligned);
+        }
+      } else {
+        if (ra < RA) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (rb0 + i < RB) o[(size_t)(rb0 + i) * ldo + ra] = from_f32<TO>(v[i]);  // lanes write consecutive addresses
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  long long rows, cols, ld;
+  int box_rows;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    for (long long v : {k.rows, k.cols, k.ld, (long long)k.box_rows}) h = h * 1000003u ^ (size_t)v;
+    return h;
+  }
+};
+
+// Tensor map of a row-major bf16 matrix [rows, cols] with row stride ld (elements): boxes of
+// box_rows x 64 elements, 128-byte swizzle, zeros outside the matrix. Encoding is host-only work;
+// maps are kept by (pointer, shape) since weights and workspaces keep their addresses.
+bool tensor_map_for(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{ptr, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return true;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return true;
+}
+
+int* error_word() {
+  // One int of device memory per process for the kernels' error codes, made at first use.
+  static int* word = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    if (cudaMalloc(&word, sizeof(int)) == cudaSuccess) cudaMemset(word, 0, sizeof(int));
+    else word = nullptr;
+  });
+  return word;
+}
+
+template <int BN, bool SWAP, typename TO>
+int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, int splits, long long ldo,
+              long long split_stride, int stages, cudaStream_t stream) {
+  constexpr int STAGE_BYTES = A_BYTES + BN * BK * 2;
+  const int k_tiles = (K + BK - 1) / BK;
+  int per_split = (k_tiles + splits - 1) / splits;
+  splits = (k_tiles + per_split - 1) / per_split;
+  stages = std::min(stages, (227 * 1024 - 2048) / STAGE_BYTES);
+  if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
+  const size_t smem = (size_t)stages * STAGE_BYTES + (2 * stages + 1) * sizeof(uint64_t) + 16 + 1024;
+  auto kernel = gemm_tc_kernel<BN, SWAP, TO>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+      llm_set_error("gemm_tc: cannot raise the shared memory limit");
+      return LLM_ERR_LAUNCH;
+    }
+    attr_set = true;
+  }
+  dim3 grid((RA + BM - 1) / BM, (RB + BN - 1) / BN, splits);
+  kernel<<<grid, 128, smem, stream>>>(ma, mb, (TO*)out, RA, RB, k_tiles, per_split, ldo, split_stride, stages, error_word());
+  return LLM_OK;
+}
+
+}  // namespace
+
+// Number of K splits llm_gemm_tc will really use for (K, wanted splits).
+extern "C" int llm_gemm_tc_splits(int K, int splits) {
+  const int k_tiles = (K + BK - 1) / BK;
+  if (splits < 1) splits = 1;
+  const int per_split = (k_tiles + splits - 1) / splits;
+  return (k_tiles + per_split - 1) / per_split;
+}
+
+// Whether the tensor-core kernel takes these operands (else the caller uses the CUDA-core one).
+extern "C" int llm_gemm_tc_supported(const void* a, const void* w, int M, int N, int K, long long lda, long long ldw) {
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  return M > 0 && N > 0 && K > 0 && (K % 8) == 0 && (lda % 8) == 0 && (ldw % 8) == 0 && al(a) && al(w) && encode_fn() != nullptr;
+}
+
+// out[m, n] = sum_k a[m, k] * w[n, k], a [M, K] and w [N, K] bfloat16.
+// swap = 0: tiles of 128 tokens; out dtype bf16 or f32; splits must be 1.
+// swap = 1: M <= 256 tokens; weights fill the accumulator lanes; with splits > 1, out is float32
+//           [splits, M, ldo] partials (split_stride elements apart) to be added by the consumer.
+extern "C" int llm_gemm_tc(const void* a, const void* w, void* out, int M, int N, int K, long long lda, long long ldw,
+                           long long ldo, int out_dtype, int swap, int splits, long long split_stride, int stages,
+                           cudaStream_t stream) {
+  if (M == 0 || N == 0) return LLM_OK;
+  LLM_REQUIRE(llm_gemm_tc_supported(a, w, M, N, K, lda, ldw), "gemm_tc: operands must be 16-byte aligned with K and row strides multiples of 8");
+  LLM_REQUIRE(out_dtype == LLM_F32 || out_dtype == LLM_BF16, "gemm_tc: unknown out dtype %d", out_dtype);
+  LLM_REQUIRE(splits >= 1 && (splits == 1 || (swap && out_dtype == LLM_F32)), "gemm_tc: K splits need the swapped form and float32 partials");
+  LLM_REQUIRE(stages >= 2 && stages <= 12, "gemm_tc: stages %d not in 2..12", stages);
+  LLM_REQUIRE(error_word() != nullptr, "gemm_tc: cannot allocate the error word");
+  CUtensorMap ma, mb;
+  int rc = LLM_OK;
+  if (!swap) {
+    const int bn = N >= 256 ? 256 : (N > 64 ? 128 : (N > 32 ? 64 : (N > 16 ? 32 : 16)));
+    LLM_REQUIRE(tensor_map_for(a, M, K, lda, BM, &ma) && tensor_map_for(w, N, K, ldw, bn, &mb), "gemm_tc: cuTensorMapEncodeTiled failed");
+#define LLM_TC_CASE(BN_)                                                                                                   \
+  rc = (out_dtype == LLM_F32) ? launch_tc<BN_, false, float>(ma, mb, out, M, N, K, 1, ldo, 0, std::min(stages, BN_ == 256 ? 4 : 6), stream) \
+                              : launch_tc<BN_, false, bf16>(ma, mb, out, M, N, K, 1, ldo, 0, std::min(stages, BN_ == 256 ? 4 : 6), stream)
+    if (bn == 256) LLM_TC_CASE(256);
+    else if (bn == 128) LLM_TC_CASE(128);
+    else if (bn == 64) LLM_TC_CASE(64);
+    else if (bn == 32) LLM_TC_CASE(32);
+    else LLM_TC_CASE(16);
+#undef LLM_TC_CASE
+  } else {
+    LLM_REQUIRE(M <= 256, "gemm_tc: the swapped form takes at most 256 tokens, got %d", M);
+    const int bn = M > 128 ? 256 : (M > 64 ? 128 : (M > 32 ? 64 : (M > 16 ? 32 : 16)));
+    LLM_REQUIRE(tensor_map_for(w, N, K, ldw, BM, &ma) && tensor_map_for(a, M, K, lda, bn, &mb), "gemm_tc: cuTensorMapEncodeTiled failed");
+#define LLM_TC_CASE(BN_)                                                                                                        \
+  rc = (out_dtype == LLM_F32) ? launch_tc<BN_, true, float>(ma, mb, out, N, M, K, splits, ldo, split_stride, std::min(stages, BN_ == 256 ? 4 : 8), stream) \
+                              : launch_tc<BN_, true, bf16>(ma, mb, out, N, M, K, 1, ldo, 0, std::min(stages, BN_ == 256 ? 4 : 8), stream)
+    if (bn == 256) LLM_TC_CASE(256);
+    else if (bn == 128) LLM_TC_CASE(128);
+    else if (bn == 64) LLM_TC_CASE(64);
+    else if (bn == 32) LLM_TC_CASE(32);
+    else LLM_TC_CASE(16);
+#undef LLM_TC_CASE
+  }
+  if (rc != LLM_OK) return rc;
+  LLM_CHECK_LAUNCH("gemm_tc");
+  return LLM_OK;
+}
+
+// Reads and clears the error code that a tensor-core kernel may have left (0 = none). Synchronizes.
+extern "C" int llm_gemm_tc_error() {
+  int* w = error_word();
+  if (!w) return -1;
+  int v = 0;
+  if (cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
+  if (v) cudaMemset(w, 0, sizeof(int));
+  return v;
+}

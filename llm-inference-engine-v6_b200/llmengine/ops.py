@@ -54,6 +54,8 @@ class CudaOps:
     def __init__(self):
         self._libs = {}
         self.launches = 0  # kernels launched through this object (a counter for measurements)
+        self.tensor_cores = True  # bfloat16 products on tcgen05 where the operands allow it
+        self._scratch = None
 
     # ------------------------------------------------------------------ loading
     def lib(self, name: str = "core"):
@@ -130,18 +132,107 @@ class CudaOps:
         return out
 
     # ------------------------------------------------------------------ matrix products
+    SM_COUNT = 148  # CTAs aimed at when a weight-streaming product is cut along K
+
+    def _tc_usable(self, a: torch.Tensor, w: torch.Tensor) -> bool:
+        """bfloat16 operands that the tensor-core kernel takes (16-byte aligned rows of K % 8 == 0)."""
+        if a.dtype != torch.bfloat16 or not self.tensor_cores:
+            return False
+        lib = self.lib("tensorcore")
+        return bool(lib.llm_gemm_tc_supported(_ptr(a), _ptr(w), c_int(a.shape[0]), c_int(w.shape[0]), c_int(a.shape[1]),
+                                              c_longlong(a.stride(0)), c_longlong(w.stride(0))))
+
+    def _splits_for(self, M: int, N: int, K: int) -> int:
+        tiles, k_tiles = (N + 127) // 128, (K + 63) // 64
+        if M > self.SWAP_MAX_TOKENS or tiles >= 96:
+            return 1
+        want = min(max(1, self.SM_COUNT // tiles), max(1, k_tiles // 4))
+        return int(self.lib("tensorcore").llm_gemm_tc_splits(c_int(K), c_int(want)))
+
+    SWAP_MAX_TOKENS = 64  # up to here weights fill the accumulator lanes and tokens the columns
+
+    def _gemm_tc(self, a, w, out, splits: int = 1, split_stride: int = 0) -> None:
+        M, K = a.shape
+        N = w.shape[0]
+        swap = 1 if M <= self.SWAP_MAX_TOKENS else 0
+        lib = self.lib("tensorcore")
+        ldo = out.stride(-2)
+        self._check(lib.llm_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)),
+                                    c_longlong(w.stride(0)), c_longlong(ldo), c_int(dtype_code(out.dtype)), c_int(swap),
+                                    c_int(splits), c_longlong(split_stride), c_int(8), _stream()), lib)
+
+    def _scratch_f32(self, numel: int, device) -> torch.Tensor:
+        buf = self._scratch
+        if buf is None or buf.numel() < numel:
+            buf = torch.empty(max(numel, 1 << 20), dtype=torch.float32, device=device)
+            self._scratch = buf
+        return buf
+
     def gemm(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """out[m,n] = sum_k a[m,k]*w[n,k]; float32 accumulation; a and w of one dtype; out float32
-        or that dtype. Rows may be strided views."""
+        or that dtype. Rows may be strided views. bfloat16 runs on the tensor cores (cut along K
+        and reduced when few tokens stream a large weight); float32 on CUDA cores, every output
+        element summed over k in ascending order whatever the batch."""
         _need(a, "gemm.a"); _need(w, "gemm.w", a.dtype); _need(out, "gemm.out")
         M, K = a.shape
         N = w.shape[0]
         assert w.shape[1] == K and out.shape == (M, N)
+        if self._tc_usable(a, w):
+            splits = self._splits_for(M, N, K)
+            if splits == 1:
+                self._gemm_tc(a, w, out)
+            else:
+                parts = self._scratch_f32(splits * M * N, a.device)[:splits * M * N].view(splits, M, N)
+                self._gemm_tc(a, w, parts, splits, M * N)
+                self.reduce_partials(parts, out)
+            return out
         lib = self.lib()
         self._check(lib.llm_gemm_simt(_ptr(a), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
                                       c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
                                       c_int(dtype_code(a.dtype)), c_int(dtype_code(out.dtype)), _stream()), lib)
         return out
+
+    def gemm_partials(self, a: torch.Tensor, w: torch.Tensor, ws, tag: str) -> torch.Tensor:
+        """As gemm, for consumers that add partial sums themselves: returns float32 [parts, M, N]
+        (scratch `tag` of workspace `ws`); the product is the sum over parts, to be taken in index
+        order. parts is 1 unless few tokens stream a weight with few output tiles."""
+        _need(a, "gemm.a"); _need(w, "gemm.w", a.dtype)
+        M, K = a.shape
+        N = w.shape[0]
+        assert w.shape[1] == K
+        if self._tc_usable(a, w):
+            splits = self._splits_for(M, N, K)
+            parts = ws.get(tag, (splits, M, N), torch.float32)
+            self._gemm_tc(a, w, parts, splits, M * N)
+            return parts
+        parts = ws.get(tag, (1, M, N), torch.float32)
+        self.gemm(a, w, parts[0])
+        return parts
+
+    def reduce_partials(self, parts: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """out = sum over parts[p] (index order); out float32 or bfloat16, contiguous."""
+        _need(parts, "reduce.parts", torch.float32); _need(out, "reduce.out")
+        assert parts.is_contiguous() and out.is_contiguous() and parts.dim() == 3 and parts.shape[1:] == out.shape
+        lib = self.lib()
+        self._check(lib.llm_reduce_partials(_ptr(parts), c_int(parts.shape[0]), c_longlong(parts.stride(0)), _ptr(out),
+                                            c_int(dtype_code(out.dtype)), c_longlong(out.numel()), _stream()), lib)
+        return out
+
+    def silu_mul_partials(self, parts: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """parts float32 [p, n, 2*ff] (gate | up partial sums) -> out [n, ff] = silu(gate) * up."""
+        _need(parts, "silu_mul.parts", torch.float32); _need(out, "silu_mul.out")
+        n, ff = out.shape
+        assert parts.is_contiguous() and out.is_contiguous() and parts.shape[1:] == (n, 2 * ff)
+        lib = self.lib()
+        self._check(lib.llm_silu_mul_partials(_ptr(parts), c_int(parts.shape[0]), c_longlong(parts.stride(0)), _ptr(out),
+                                              c_int(dtype_code(out.dtype)), c_int(n), c_int(ff), _stream()), lib)
+        return out
+
+    def tensor_core_error(self) -> int:
+        """Code left by a tensor-core kernel that gave up a bounded wait (0: none). Synchronizes."""
+        if "tensorcore" not in self._libs:
+            return 0
+        return int(self._libs["tensorcore"].llm_gemm_tc_error())
 
     # ------------------------------------------------------------------ attention
     def rope_kv_write(self, qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,

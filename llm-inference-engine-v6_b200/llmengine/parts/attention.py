@@ -53,9 +53,7 @@ class PagedAttention(Mixer):
         att = ctx.ws.get("attention.out", (n, dq), self.env.dtype)
         ops.paged_attention(qkv[:, :dq], cache.k, cache.v, ctx.positions, ctx.token_seq, ctx.block_tables[cache.group],
                             att, n, s.num_heads, s.num_kv_heads, s.head_dim, self.scale, s.window)
-        delta = ctx.ws.get("attention.delta", (n, s.hidden), torch.float32)
-        ops.gemm(att, self.w_o, delta)
-        return delta
+        return ops.gemm_partials(att, self.w_o, ctx.ws, "attention.delta")
 
 
 register_part("mixer", "attention", PagedAttention)

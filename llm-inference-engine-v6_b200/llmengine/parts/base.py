@@ -105,8 +105,8 @@ class Mixer(Part):
         return ()
 
     def forward(self, x: torch.Tensor, ctx, cache: LayerCache) -> torch.Tensor:
-        """x: normalised activations [tokens, hidden] (engine dtype). Returns the float32 delta
-        [tokens, hidden] to be added to the residual stream."""
+        """x: normalised activations [tokens, hidden] (engine dtype). Returns the float32 delta to
+        be added to the residual stream: [tokens, hidden], or [parts, tokens, hidden] partial sums."""
         raise NotImplementedError
 
 

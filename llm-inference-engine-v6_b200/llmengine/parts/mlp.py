@@ -32,13 +32,14 @@ class GatedMLP(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         s, ops, n = self.spec, self.env.ops, ctx.n_tokens
-        gate_up = ctx.ws.get("mlp.gate_up", (n, 2 * s.intermediate), self.env.dtype)
-        ops.gemm(x[:n], self.w_gate_up, gate_up)
         act = ctx.ws.get("mlp.act", (n, s.intermediate), self.env.dtype)
-        ops.silu_mul(gate_up, act)
-        delta = ctx.ws.get("mlp.delta", (n, s.hidden), torch.float32)
-        ops.gemm(act, self.w_down, delta)
-        return delta
+        if n <= 64:  # few tokens: the products may come as partial sums, added by their consumers
+            ops.silu_mul_partials(ops.gemm_partials(x[:n], self.w_gate_up, ctx.ws, "mlp.gate_up_parts"), act)
+        else:
+            gate_up = ctx.ws.get("mlp.gate_up", (n, 2 * s.intermediate), self.env.dtype)
+            ops.gemm(x[:n], self.w_gate_up, gate_up)
+            ops.silu_mul(gate_up, act)
+        return ops.gemm_partials(act, self.w_down, ctx.ws, "mlp.delta")
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

@@ -57,6 +57,20 @@ class CpuOps:
         out.copy_((a.float() @ w.float().t()).to(out.dtype))
         return out
 
+    def gemm_partials(self, a, w, ws, tag):
+        parts = ws.get(tag, (2, a.shape[0], w.shape[0]), torch.float32)  # two parts, to exercise the consumers
+        half = a.shape[1] // 2
+        parts[0] = a[:, :half].float() @ w[:, :half].float().t()
+        parts[1] = a[:, half:].float() @ w[:, half:].float().t()
+        return parts
+
+    def reduce_partials(self, parts, out):
+        out.copy_(parts.sum(0).to(out.dtype))
+        return out
+
+    def silu_mul_partials(self, parts, out):
+        return self.silu_mul(parts.sum(0), out)
+
     def rope_kv_write(self, qkv, positions, token_seq, block_table, cos, sin, kcache, vcache, n_tokens, nq, nkv, hd):
         half = hd // 2
         for t in range(n_tokens):

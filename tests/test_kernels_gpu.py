@@ -98,6 +98,42 @@ def test_gemm(ops, dt, M, N, K):
     assert float(wide_out[:, :2].abs().max()) == 0 and float(wide_out[:, 2 + N:].abs().max()) == 0
 
 
+@pytest.mark.parametrize("M", [1, 8, 17, 64, 65, 128, 300])
+@pytest.mark.parametrize("N,K", [(16, 64), (130, 192), (509, 200), (3072, 2048), (176, 1024)])
+def test_gemm_tensor_cores(ops, M, N, K):
+    """The tcgen05/TMA kernel in both forms (few tokens: weights on the accumulator lanes, K cut in
+    splits; many tokens: 128-token tiles), with tails in every dimension."""
+    a, w = rnd(M, K, dtype=torch.bfloat16, seed=50), rnd(N, K, dtype=torch.bfloat16, seed=51, std=0.1)
+    assert ops._tc_usable(a, w)
+    ref = a.double() @ w.double().t()
+    scale = math.sqrt(K) * 0.1
+    for out_dt in (torch.float32, torch.bfloat16):
+        out = torch.full((M, N), float("nan"), dtype=out_dt, device=DEV)
+        ops.gemm(a, w, out)
+        torch.testing.assert_close(out.double(), ref, **tol(out_dt, scale))
+    from llmengine.engine.context import Workspace
+    parts = ops.gemm_partials(a, w, Workspace(torch.device(DEV)), "t")
+    assert parts.dtype == torch.float32 and parts.shape[1:] == (M, N)
+    if M <= 64 and N <= 3072 and K >= 1024:
+        assert parts.shape[0] > 1  # few tokens, few output tiles, long K: cut along K
+    torch.testing.assert_close(parts.double().sum(0), ref, **tol(torch.float32, scale))
+    red = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.reduce_partials(parts, red)
+    torch.testing.assert_close(red.double(), ref, **tol(torch.bfloat16, scale))
+    assert ops.tensor_core_error() == 0
+    # operands the kernel cannot take (K not a multiple of 8) go to the CUDA-core kernel
+    a2, w2 = rnd(M, 100, dtype=torch.bfloat16, seed=52)[:, :99], rnd(N, 99, dtype=torch.bfloat16, seed=53)
+    assert not ops._tc_usable(a2, w2)
+
+
+def test_silu_mul_partials(ops):
+    parts = rnd(3, 5, 2 * 176, seed=54)
+    out = torch.empty(5, 176, dtype=torch.bfloat16, device=DEV)
+    ops.silu_mul_partials(parts, out)
+    s = parts.sum(0).cpu().numpy()
+    torch.testing.assert_close(out.float().cpu(), torch.from_numpy(P.silu(s[:, :176]) * s[:, 176:]), **tol(torch.bfloat16, 4))
+
+
 def test_gemm_float32_rows_do_not_depend_on_the_batch(ops):
     """A row's result is bit-identical whether it is computed alone or among others."""
     a, w = rnd(77, 300, seed=12), rnd(190, 300, seed=13)
