@@ -133,7 +133,7 @@ def run_ours(args):
     t0 = time.time()
     llmengine.write_random_model(tmp.name, g, seed=0, dtype=torch.bfloat16)
     max_batch = max(args.batch, 64 if args.points else args.batch, 1)
-    room = CONTEXT + 2 * (K + W) + 64
+    room = CONTEXT + 2 * (K + W) + max_batch + 64
     num_blocks = max_batch * (room + BLOCK_SIZE - 1) // BLOCK_SIZE + PREFILL_TOKENS // BLOCK_SIZE + 8
     eng = llmengine.Engine(tmp.name, "bf16", block_size=BLOCK_SIZE, num_blocks=num_blocks, max_concurrent=max_batch)
     eng.configure_cache()
@@ -148,9 +148,12 @@ def run_ours(args):
         """-> (seconds per step, kernel launches per step, h2d bytes, d2h bytes)."""
         sch = llmengine.ContinuousBatchScheduler(eng, None, max_concurrent=batch, max_prefill_tokens_per_step=PREFILL_TOKENS)
         for p in prompts(batch, CONTEXT):
-            sch.enqueue(p, 2 * (k_steps + w_steps) + 8)
-        while sch.core.num_running < batch:  # prefill (untimed): one prompt a step
+            sch.enqueue(p, 2 * (k_steps + w_steps) + batch + 8)  # early requests decode while later prompts prefill
+        for _ in range(2 * batch + 8):  # prefill (untimed): one prompt a step
+            if sch.core.num_running == batch:
+                break
             sch.step()
+        assert sch.core.num_running == batch, "the contexts could not be filled"
         launches = 0
 
         def one_step():

@@ -66,6 +66,8 @@ class CudaOps:
             path = _build.kernel_library_path(name)
             lib = ctypes.CDLL(path)
             lib.llm_last_error.restype = ctypes.c_char_p
+            if name == "tensorcore":
+                lib.llm_attention_mma_scratch_floats.restype = ctypes.c_longlong
             self._libs[name] = lib
         return lib
 
@@ -260,24 +262,42 @@ class CudaOps:
                                           _ptr(vcache), c_int(n_tokens), c_int(nq), c_int(nkv), c_int(hd),
                                           c_int(page_size), _stream()), lib)
 
-    def paged_attention(self, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
-                        positions: torch.Tensor, token_seq: torch.Tensor, block_table: torch.Tensor,
-                        out: torch.Tensor, n_tokens: int, nq: int, nkv: int, hd: int, scale: float,
+    ATTENTION_SPLIT_KEYS = 256  # decoding: keys per split (absolute boundaries, a multiple of 64)
+
+    def paged_attention(self, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, batch,
+                        block_table: torch.Tensor, out: torch.Tensor, nq: int, nkv: int, hd: int, scale: float,
                         window: int = 0) -> torch.Tensor:
-        """q: rows of [nq*hd] (may be a view of the qkv buffer); out [n, nq*hd]."""
+        """Causal attention of every token of the step over cache positions lo..pos of its request.
+        q: rows of [nq*hd] (may be a view of the qkv buffer); out [n, nq*hd]; `batch` is the step
+        context (positions, token_seq, seq_start, seq_ntok, seq_qoff, the counts, scratch).
+        bfloat16 with head sizes 16/32/64/128 runs on tensor cores (with the key range cut into
+        splits when every request brings one token); anything else on CUDA cores in float32."""
         _need(q, "attention.q"); _need(kcache, "attention.kcache", q.dtype); _need(vcache, "attention.vcache", q.dtype)
-        _need(out, "attention.out", q.dtype)
-        _need(positions, "attention.positions", torch.int32); _need(token_seq, "attention.token_seq", torch.int32)
-        _need(block_table, "attention.block_table", torch.int32)
+        _need(out, "attention.out", q.dtype); _need(block_table, "attention.block_table", torch.int32)
         assert kcache.is_contiguous() and vcache.is_contiguous() and block_table.is_contiguous()
         assert kcache.shape[1] == nkv and kcache.shape[3] == hd
+        n_tokens, page = batch.n_tokens, kcache.shape[2]
+        if q.dtype == torch.bfloat16 and self.tensor_cores:
+            lib = self.lib("tensorcore")
+            if lib.llm_attention_mma_supported(c_int(nq), c_int(nkv), c_int(hd), c_longlong(q.stride(0)), c_longlong(out.stride(0))):
+                n_splits, scratch = 1, None
+                if batch.max_new_tokens == 1 and batch.max_seq_len > 2 * self.ATTENTION_SPLIT_KEYS:
+                    n_splits = (batch.max_seq_len + self.ATTENTION_SPLIT_KEYS - 1) // self.ATTENTION_SPLIT_KEYS
+                    floats = int(lib.llm_attention_mma_scratch_floats(c_int(n_tokens), c_int(nq), c_int(hd), c_int(n_splits)))
+                    scratch = batch.ws.get("attention.splits", (floats,), torch.float32)
+                self._check(lib.llm_paged_attention_mma(
+                    _ptr(q), c_longlong(q.stride(0)), _ptr(kcache), _ptr(vcache), _ptr(batch.seq_start), _ptr(batch.seq_ntok),
+                    _ptr(batch.seq_qoff), _ptr(block_table), c_int(block_table.shape[1]), _ptr(out), c_longlong(out.stride(0)),
+                    c_int(batch.n_seqs), c_int(n_tokens), c_int(batch.max_new_tokens), c_int(nq), c_int(nkv), c_int(hd),
+                    c_int(page), c_float(scale), c_int(window), c_int(n_splits), c_int(self.ATTENTION_SPLIT_KEYS),
+                    _ptr(scratch), _stream()), lib)
+                return out
         lib = self.lib()
         self._check(lib.llm_paged_attention_simt(_ptr(q), c_longlong(q.stride(0)), _ptr(kcache), _ptr(vcache),
-                                                 c_int(dtype_code(q.dtype)), _ptr(positions), _ptr(token_seq),
+                                                 c_int(dtype_code(q.dtype)), _ptr(batch.positions), _ptr(batch.token_seq),
                                                  _ptr(block_table), c_int(block_table.shape[1]), _ptr(out),
                                                  c_longlong(out.stride(0)), c_int(n_tokens), c_int(nq), c_int(nkv),
-                                                 c_int(hd), c_int(kcache.shape[2]), c_float(scale), c_int(window),
-                                                 _stream()), lib)
+                                                 c_int(hd), c_int(page), c_float(scale), c_int(window), _stream()), lib)
         return out
 
     # ------------------------------------------------------------------ sampling

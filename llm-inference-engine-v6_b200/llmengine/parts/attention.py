@@ -51,8 +51,8 @@ class PagedAttention(Mixer):
         ops.gemm(x[:n], self.w_qkv, qkv)
         self.position.rotate_and_store(qkv, ctx, cache, s.num_heads, s.num_kv_heads, s.head_dim)
         att = ctx.ws.get("attention.out", (n, dq), self.env.dtype)
-        ops.paged_attention(qkv[:, :dq], cache.k, cache.v, ctx.positions, ctx.token_seq, ctx.block_tables[cache.group],
-                            att, n, s.num_heads, s.num_kv_heads, s.head_dim, self.scale, s.window)
+        ops.paged_attention(qkv[:, :dq], cache.k, cache.v, ctx, ctx.block_tables[cache.group], att, s.num_heads,
+                            s.num_kv_heads, s.head_dim, self.scale, s.window)
         return ops.gemm_partials(att, self.w_o, ctx.ws, "attention.delta")
 
 

@@ -95,7 +95,8 @@ class CpuOps:
             else:
                 qkv[t, nq * hd:(nq + nkv) * hd] = k.reshape(-1).to(qkv.dtype)
 
-    def paged_attention(self, q, kcache, vcache, positions, token_seq, block_table, out, n_tokens, nq, nkv, hd, scale, window=0):
+    def paged_attention(self, q, kcache, vcache, batch, block_table, out, nq, nkv, hd, scale, window=0):
+        positions, token_seq, n_tokens = batch.positions, batch.token_seq, batch.n_tokens
         ps = kcache.shape[2]
         g = nq // nkv
         for t in range(n_tokens):

@@ -177,47 +177,77 @@ def _attention_ref(q, K, V, pos, nq, nkv, hd, scale, window):
     return out.reshape(-1)
 
 
+class Batch:
+    """The fields of a step context that the attention kernels read."""
+
+    def __init__(self, seqs):
+        """seqs: [(first position, number of tokens)] for batch rows 0, 1, ..."""
+        from llmengine.engine.context import Workspace
+        pos, tseq, qoff = [], [], [0]
+        for i, (start, n) in enumerate(seqs):
+            pos += list(range(start, start + n))
+            tseq += [i] * n
+            qoff.append(qoff[-1] + n)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        self.positions, self.token_seq, self.seq_qoff = i32(pos), i32(tseq), i32(qoff)
+        self.seq_start, self.seq_ntok = i32([s for s, _ in seqs]), i32([n for _, n in seqs])
+        self.n_tokens, self.n_seqs = len(pos), len(seqs)
+        self.max_new_tokens = max(n for _, n in seqs)
+        self.max_seq_len = max(s + n for s, n in seqs)
+        self.ws = Workspace(torch.device(DEV))
+        self.tokens = list(zip(tseq, pos))
+
+
 @pytest.mark.parametrize("dt", DTYPES)
 @pytest.mark.parametrize("nq,nkv,hd,page,window", [(8, 2, 64, 16, 0), (6, 1, 32, 4, 0), (5, 5, 48, 8, 0), (4, 2, 16, 4, 9),
-                                                   (8, 4, 128, 16, 40), (2, 1, 256, 16, 0), (3, 3, 80, 64, 0)])
+                                                   (8, 4, 128, 16, 40), (2, 1, 256, 16, 0), (3, 3, 80, 64, 0), (32, 8, 64, 16, 0),
+                                                   (12, 2, 64, 16, 100)])
 def test_paged_attention(ops, dt, nq, nkv, hd, page, window):
-    seq_lens = [1, 37, 130, 64]
-    kc, vc, table, dense = _paged_setup(dt, nkv, hd, page, seq_lens, 40 if page >= 8 else 80)
-    # tokens: a portion of request 2 (positions 100..129), one decoded token of each other request
-    toks = [(0, 0), (1, 36), (3, 63), (3, 15), (3, 16)] + [(2, p) for p in range(100, 130)]
-    q = rnd(len(toks), nq * hd, dtype=dt, seed=20)
-    positions = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
-    token_seq = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
-    out = torch.empty(len(toks), nq * hd, dtype=dt, device=DEV)
+    seq_lens = [1, 37, 130, 64, 700]
+    kc, vc, table, dense = _paged_setup(dt, nkv, hd, page, seq_lens, sum((L + page - 1) // page for L in seq_lens) + 3)
     scale = 1.0 / math.sqrt(hd)
-    ops.paged_attention(q, kc, vc, positions, token_seq, table, out, len(toks), nq, nkv, hd, scale, window)
-    for i, (s, p) in enumerate(toks):
-        ref = _attention_ref(q[i].cpu().view(nq, hd), dense[s][0], dense[s][1], p, nq, nkv, hd, scale, window)
-        torch.testing.assert_close(out[i].float().cpu(), ref, **tol(dt, 2))
+    batches = [
+        # a prompt portion that starts in the middle of a page beside single decoded tokens
+        Batch([(0, 1), (36, 1), (101, 29), (63, 1), (650, 50)]),
+        # whole prompts from position 0, one longer than a tile of query tokens
+        Batch([(0, 1), (0, 37), (0, 130), (0, 2), (0, 3)]),
+        # decoding only: one token each (long contexts are cut into key splits on the tensor-core path)
+        Batch([(0, 1), (36, 1), (129, 1), (15, 1), (699, 1)]),
+    ]
+    for b in batches:
+        q = rnd(b.n_tokens, nq * hd, dtype=dt, seed=20)
+        out = torch.full((b.n_tokens, nq * hd), float("nan"), dtype=dt, device=DEV)
+        ops.paged_attention(q, kc, vc, b, table, out, nq, nkv, hd, scale, window)
+        for i, (s, p) in enumerate(b.tokens):
+            ref = _attention_ref(q[i].cpu().view(nq, hd), dense[s][0], dense[s][1], p, nq, nkv, hd, scale, window)
+            torch.testing.assert_close(out[i].float().cpu(), ref, **tol(dt, 2))
 
 
 @pytest.mark.parametrize("dt", DTYPES)
-@pytest.mark.parametrize("special", [0, 15, 16, 31, 32, 255, 256, 499])
-def test_attention_finds_one_far_key_among_hundreds(ops, dt, special):
+@pytest.mark.parametrize("special", [0, 15, 16, 31, 32, 63, 64, 255, 256, 499])
+@pytest.mark.parametrize("n_new", [1, 3])
+def test_attention_finds_one_far_key_among_hundreds(ops, dt, special, n_new):
     """Random values hide a skipped key (its weight is ~1/500). Here one key is made to match the
-    query, so that the output must be that key's value: a key lost at a page's edge, at the start or
-    at the end of the range shows as an error of order one."""
+    query, so that the output must be that key's value: a key lost at a page's edge, at a tile's or
+    a split's edge, at the start or at the end of the range shows as an error of order one."""
     nq, nkv, hd, page, L = 4, 2, 64, 16, 500
     kc, vc, table, dense = _paged_setup(dt, nkv, hd, page, [L], 40, seed=special)
-    q = rnd(1, nq * hd, dtype=dt, seed=21)
+    b = Batch([(L - n_new, n_new)])
+    q = rnd(n_new, nq * hd, dtype=dt, seed=21)
     K, V = dense[0]
     pg, off = int(table[0, special // page]), special % page
     for h in range(nkv):  # both kv heads: key `special` := 4 * (a query of that group), others stay random
-        K[special, h] = (q[0].cpu().view(nq, hd)[h * 2].float() * 4).to(dt)
+        K[special, h] = (q[n_new - 1].cpu().view(nq, hd)[h * 2].float() * 4).to(dt)
         kc[pg, h, off] = K[special, h].to(DEV)
-    positions = torch.tensor([L - 1], dtype=torch.int32, device=DEV)
-    out = torch.empty(1, nq * hd, dtype=dt, device=DEV)
-    ops.paged_attention(q, kc, vc, positions, torch.zeros(1, dtype=torch.int32, device=DEV), table, out, 1, nq, nkv, hd, 1.0, 0)
-    ref = _attention_ref(q[0].cpu().view(nq, hd), K, V, L - 1, nq, nkv, hd, 1.0, 0)
-    o = out[0].float().cpu().view(nq, hd)
-    torch.testing.assert_close(o.reshape(-1), ref, **tol(dt, 2))
-    for h in (0, 2):  # the matching heads return (almost exactly) the special key's value
-        assert (o[h] - V[special, h // 2].float()).abs().max() < 0.05
+    out = torch.empty(n_new, nq * hd, dtype=dt, device=DEV)
+    ops.paged_attention(q, kc, vc, b, table, out, nq, nkv, hd, 1.0, 0)
+    for i in range(n_new):
+        ref = _attention_ref(q[i].cpu().view(nq, hd), K, V, L - n_new + i, nq, nkv, hd, 1.0, 0)
+        torch.testing.assert_close(out[i].float().cpu(), ref, **tol(dt, 2))
+    if special <= L - n_new:
+        o = out[n_new - 1].float().cpu().view(nq, hd)
+        for h in (0, 2):  # the matching heads return (almost exactly) the special key's value
+            assert (o[h] - V[special, h // 2].float()).abs().max() < 0.05
 
 
 @pytest.mark.parametrize("dt", DTYPES)
@@ -231,8 +261,7 @@ def test_attention_window_edge(ops, dt):
         K[special, 0] = (q[0].cpu().view(nq, hd)[0].float() * 4).to(dt)
         kc[int(table[0, special // page]), 0, special % page] = K[special, 0].to(DEV)
         out = torch.empty(1, nq * hd, dtype=dt, device=DEV)
-        ops.paged_attention(q, kc, vc, torch.tensor([L - 1], dtype=torch.int32, device=DEV),
-                            torch.zeros(1, dtype=torch.int32, device=DEV), table, out, 1, nq, nkv, hd, 1.0, W)
+        ops.paged_attention(q, kc, vc, Batch([(L - 1, 1)]), table, out, nq, nkv, hd, 1.0, W)
         ref = _attention_ref(q[0].cpu().view(nq, hd), K, V, L - 1, nq, nkv, hd, 1.0, W)
         torch.testing.assert_close(out[0].float().cpu(), ref, **tol(dt, 2))
         hit = (out[0].float().cpu()[:hd] - V[special, 0].float()).abs().max() < 0.05
@@ -305,8 +334,8 @@ def test_kernels_refuse_what_they_cannot_take(ops):
     from llmengine.ops import KernelError
     with pytest.raises(KernelError, match="head_dim"):
         ops.paged_attention(rnd(1, 2 * 512), torch.zeros(2, 1, 4, 512, device=DEV), torch.zeros(2, 1, 4, 512, device=DEV),
-                            torch.zeros(1, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
-                            torch.zeros(1, 1, dtype=torch.int32, device=DEV), torch.empty(1, 1024, device=DEV), 1, 2, 1, 512, 1.0)
+                            Batch([(0, 1)]), torch.zeros(1, 1, dtype=torch.int32, device=DEV), torch.empty(1, 1024, device=DEV),
+                            2, 1, 512, 1.0)
     with pytest.raises(KernelError, match="CUDA tensor"):
         ops.gemm(torch.zeros(2, 2), torch.zeros(2, 2), torch.zeros(2, 2))
     with pytest.raises(KernelError):
