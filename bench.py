@@ -135,7 +135,11 @@ def run_ours(args):
     max_batch = max(args.batch, 64 if args.points else args.batch, 1)
     room = CONTEXT + 2 * (K + W) + max_batch + 64
     num_blocks = max_batch * (room + BLOCK_SIZE - 1) // BLOCK_SIZE + PREFILL_TOKENS // BLOCK_SIZE + 8
-    eng = llmengine.Engine(tmp.name, "bf16", block_size=BLOCK_SIZE, num_blocks=num_blocks, max_concurrent=max_batch)
+    skip = set(x for x in args.skip.split(",") if x)
+    if "points" in skip:
+        args.points = False
+    eng = llmengine.Engine(tmp.name, "bf16", block_size=BLOCK_SIZE, num_blocks=num_blocks, max_concurrent=max_batch,
+                           cuda_graphs=args.graphs)
     eng.configure_cache()
     sys.stderr.write(f"[bench] model written and loaded in {time.time() - t0:.1f}s; {num_blocks} pages\n")
     gen = torch.Generator().manual_seed(1)
@@ -161,8 +165,14 @@ def run_ours(args):
                 sch.step()
                 return
             entries = sch.core.plan()
-            ctx, logits = eng.step(entries)
-            eng.sampler.sample_device(logits, ctx, ctx.n_rows)
+            if eng.cuda_graphs:
+                if eng.graphs is None:
+                    from llmengine.engine.graphs import DecodeGraphs
+                    eng.graphs = DecodeGraphs(eng)
+                eng.graphs.run_device(entries)
+            else:
+                ctx, logits = eng.step(entries)
+                eng.sampler.sample_device(logits, ctx, ctx.n_rows)
             sch.core.commit([1] * len(entries))  # timing only: the token values do not matter
 
         for _ in range(w_steps):
@@ -209,8 +219,10 @@ def run_ours(args):
     clocks.start()
     sec, launches, _, _ = decode_run(args.batch, K, W, e2e=False)
     clock_rec = clocks.stop()
-    e2e_sec, _, h2d, d2h = decode_run(args.batch, K, W, e2e=True)
-    pre_sec = prefill_run(max(2, min(K, 5)), max(1, min(W, 3)))
+    e2e_sec, h2d, d2h = sec, 0, 0
+    if "e2e" not in skip:
+        e2e_sec, _, h2d, d2h = decode_run(args.batch, K, W, e2e=True)
+    pre_sec = prefill_run(max(2, min(K, 5)), max(1, min(W, 3))) if "prefill" not in skip else float("inf")
     points = {}
     if args.points:
         for b in (1, 64):
@@ -315,6 +327,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the full configuration (named in `config`)")
     ap.add_argument("--no-points", dest="points", action="store_false", help="skip the batch 1 and 64 points")
+    ap.add_argument("--skip", default="", help="comma list of parts to leave out: e2e,prefill,points (for profiling runs)")
+    ap.add_argument("--no-cuda-graphs", dest="graphs", action="store_false", help="launch decode steps kernel by kernel")
     ap.add_argument("--reference-setup-limit", type=float, default=900.0, help="seconds the reference arm may spend filling contexts")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:

@@ -63,7 +63,7 @@ class BlockManager:
 
 class Engine:
     def __init__(self, model_dir: str, dtype: str = "fp32", *, device: str = "cuda:0", block_size: int = 16,
-                 num_blocks: Optional[int] = None, max_concurrent: int = 64, ops=None):
+                 num_blocks: Optional[int] = None, max_concurrent: int = 64, ops=None, cuda_graphs: Optional[bool] = None):
         if dtype not in _DTYPES:
             raise ValueError(f"dtype must be 'fp32' | 'bf16', got: {dtype}")
         self.model_dir = model_dir
@@ -84,6 +84,9 @@ class Engine:
         self.buffers: Optional[StepBuffers] = None
         self.sampler = Sampler(self.ops, self.device)
         self._next_private_id = -1
+        # decode-only steps replay CUDA graphs (bfloat16 serving path; the 32-bit path stays eager)
+        self.cuda_graphs = (self.torch_dtype == torch.bfloat16 and self.device.type == "cuda") if cuda_graphs is None else cuda_graphs
+        self.graphs = None
         self._id_bases = 0
         self._ckpt_names: Optional[List[str]] = None
 
@@ -169,6 +172,7 @@ class Engine:
                 c.states = {}
             model.allocate_cache([num_blocks] * len(model.windows), num_slots)
             self.buffers = StepBuffers(self.device, len(model.windows), block_size, self.ws)
+            self.graphs = None  # graphs point into the old pool
             self.block_manager = manager
             if manager is not None:
                 manager._engine = self
@@ -194,6 +198,21 @@ class Engine:
             ctx = self.buffers.prepare(self.cm, entries, self.spec.vocab_size, self.max_pos, pad_to)
             logits = self.model.forward(ctx)
             return ctx, logits
+
+    def step_and_sample(self, entries) -> List[int]:
+        """A step followed by the choice of one token for every wanted row (greedy or by the rows'
+        temperature, seed and draw index); the tokens come back to the host. Steps in which every
+        request brings one token replay a CUDA graph when `cuda_graphs` is on."""
+        with self._lock:
+            self._ensure_cache()
+            n = len(entries)
+            if self.cuda_graphs and n and entries.max_tokens() == 1 and entries.num_rows() == n:
+                if self.graphs is None:
+                    from .graphs import DecodeGraphs
+                    self.graphs = DecodeGraphs(self)
+                return self.graphs.run(entries)
+            ctx, logits = self.step(entries)
+            return self.sampler.sample(logits, ctx, ctx.n_rows)
 
     def run_step(self, batch: Sequence[Tuple[int, Sequence[int], Sequence[int]]], end: Iterable[int] = ()) -> torch.Tensor:
         """The whole step function for callers that bring their own schedule (trace replay, tests):

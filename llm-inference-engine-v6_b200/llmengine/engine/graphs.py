@@ -1,0 +1,119 @@
+"""CUDA graphs for decode-only steps.
+
+A step in which every request brings one token launches well over a hundred small kernels; at
+that size the launches, not the kernels, bound the step. Such steps are captured once per
+(request capacity, block-table width) as a CUDA graph over a batch padded to the capacity, and
+replayed: the host then only fills the step's int32 arrays (pinned), copies them, launches the
+graph and reads the sampled tokens back. Padded rows belong to a null request that owns the null
+page and the null slot, so they touch nothing live. Each graph has its own workspace, batch
+buffer and sampler output, so that nothing it points at is ever moved by a later step.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..cache.host import host_module
+from ..sampling.sampler import Sampler
+from .context import StepBuffers, Workspace
+
+
+class _Captured:
+    def __init__(self):
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.buffers: Optional[StepBuffers] = None
+        self.tokens: Optional[torch.Tensor] = None
+        self.host_tokens: Optional[torch.Tensor] = None
+        self.pad_to: Tuple[int, int, int, int] = (0, 0, 0, 0)
+        self.kernels = 0  # kernel launches inside the graph
+
+
+class DecodeGraphs:
+    BLOCK_BUCKET = 64  # block-table widths are rounded up to this many pages
+
+    def __init__(self, engine):
+        self.engine = engine
+        self.captured: Dict[Tuple[int, int], _Captured] = {}
+
+    def clear(self) -> None:
+        self.captured.clear()
+
+    @staticmethod
+    def _capacity(n: int) -> int:
+        cap = 1
+        while cap < n:
+            cap *= 2
+        return cap
+
+    def _capture(self, cap: int, blocks: int) -> _Captured:
+        eng = self.engine
+        H = host_module()
+        c = _Captured()
+        ws = Workspace(eng.device)
+        c.buffers = StepBuffers(eng.device, eng.cm.num_groups, eng.cm.page_size, ws)
+        sampler = Sampler(eng.ops, eng.device)
+        c.pad_to = (cap, cap, cap, blocks)
+        page = eng.cm.page_size
+
+        def prepare(entries):
+            ctx = c.buffers.prepare(eng.cm, entries, eng.spec.vocab_size, eng.max_pos, c.pad_to)
+            # the longest context this graph may meet decides the key splits of attention
+            ctx.max_seq_len, ctx.max_new_tokens, ctx.decode_only = blocks * page, 1, True
+            return ctx
+
+        empty = H.StepEntries()  # only padded rows: every kernel runs on the null request
+        side = torch.cuda.Stream(device=eng.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            ctx = prepare(empty)
+            for _ in range(2):  # sizes every scratch buffer and loads every kernel before the capture
+                logits = eng.model.forward(ctx)
+                sampler.sample_device(logits, ctx, cap)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(eng.device)
+        ws.frozen = True
+        graph = torch.cuda.CUDAGraph()
+        before = eng.ops.launches
+        with torch.cuda.graph(graph):
+            logits = eng.model.forward(ctx)
+            c.tokens = sampler.sample_device(logits, ctx, cap)
+        c.kernels = eng.ops.launches - before
+        c.graph = graph
+        c.host_tokens = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+        c.prepare = prepare
+        return c
+
+    def run(self, entries) -> List[int]:
+        """entries: every request brings exactly one token and wants its logits."""
+        eng = self.engine
+        H = host_module()
+        tokens, seqs, rows, blocks = H.step_caps(eng.cm, entries)
+        cap = self._capacity(seqs)
+        blocks = (blocks + self.BLOCK_BUCKET - 1) // self.BLOCK_BUCKET * self.BLOCK_BUCKET
+        c = self.captured.get((cap, blocks))
+        if c is None:
+            c = self._capture(cap, blocks)
+            self.captured[(cap, blocks)] = c
+        c.prepare(entries)
+        c.graph.replay()
+        eng.ops.launches += c.kernels
+        c.host_tokens[:seqs].copy_(c.tokens[:seqs], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return c.host_tokens[:seqs].tolist()
+
+    def run_device(self, entries) -> torch.Tensor:
+        """As run, without reading the tokens back (for device-time measurements)."""
+        eng = self.engine
+        H = host_module()
+        tokens, seqs, rows, blocks = H.step_caps(eng.cm, entries)
+        cap = self._capacity(seqs)
+        blocks = (blocks + self.BLOCK_BUCKET - 1) // self.BLOCK_BUCKET * self.BLOCK_BUCKET
+        c = self.captured.get((cap, blocks))
+        if c is None:
+            c = self._capture(cap, blocks)
+            self.captured[(cap, blocks)] = c
+        c.prepare(entries)
+        c.graph.replay()
+        eng.ops.launches += c.kernels
+        return c.tokens[:seqs]

@@ -48,9 +48,7 @@ class ContinuousBatchScheduler:
             for rid in self.core.last_admitted:
                 eng.model.reset_slot(self._cm.slot(rid))
             if len(entries):
-                ctx, logits = eng.step(entries)
-                tokens = eng.sampler.sample(logits, ctx, ctx.n_rows)
-                self.core.commit(tokens)
+                self.core.commit(eng.step_and_sample(entries))
                 self.steps += 1
         return not self.core.idle
 

@@ -55,7 +55,6 @@ class CudaOps:
         self._libs = {}
         self.launches = 0  # kernels launched through this object (a counter for measurements)
         self.tensor_cores = True  # bfloat16 products on tcgen05 where the operands allow it
-        self._scratch = None
 
     # ------------------------------------------------------------------ loading
     def lib(self, name: str = "core"):
@@ -163,28 +162,22 @@ class CudaOps:
                                     c_longlong(w.stride(0)), c_longlong(ldo), c_int(dtype_code(out.dtype)), c_int(swap),
                                     c_int(splits), c_longlong(split_stride), c_int(8), _stream()), lib)
 
-    def _scratch_f32(self, numel: int, device) -> torch.Tensor:
-        buf = self._scratch
-        if buf is None or buf.numel() < numel:
-            buf = torch.empty(max(numel, 1 << 20), dtype=torch.float32, device=device)
-            self._scratch = buf
-        return buf
-
-    def gemm(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    def gemm(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ws=None) -> torch.Tensor:
         """out[m,n] = sum_k a[m,k]*w[n,k]; float32 accumulation; a and w of one dtype; out float32
-        or that dtype. Rows may be strided views. bfloat16 runs on the tensor cores (cut along K
-        and reduced when few tokens stream a large weight); float32 on CUDA cores, every output
-        element summed over k in ascending order whatever the batch."""
+        or that dtype. Rows may be strided views. bfloat16 runs on the tensor cores (with a
+        workspace `ws`: cut along K and reduced when few tokens stream a weight with few output
+        tiles); float32 on CUDA cores, every output element summed over k in ascending order
+        whatever the batch."""
         _need(a, "gemm.a"); _need(w, "gemm.w", a.dtype); _need(out, "gemm.out")
         M, K = a.shape
         N = w.shape[0]
         assert w.shape[1] == K and out.shape == (M, N)
         if self._tc_usable(a, w):
-            splits = self._splits_for(M, N, K)
+            splits = self._splits_for(M, N, K) if (ws is not None and out.is_contiguous()) else 1
             if splits == 1:
                 self._gemm_tc(a, w, out)
             else:
-                parts = self._scratch_f32(splits * M * N, a.device)[:splits * M * N].view(splits, M, N)
+                parts = ws.get("gemm.parts", (splits, M, N), torch.float32)
                 self._gemm_tc(a, w, parts, splits, M * N)
                 self.reduce_partials(parts, out)
             return out

@@ -108,10 +108,11 @@ def test_gemm_tensor_cores(ops, M, N, K):
     ref = a.double() @ w.double().t()
     scale = math.sqrt(K) * 0.1
     for out_dt in (torch.float32, torch.bfloat16):
-        out = torch.full((M, N), float("nan"), dtype=out_dt, device=DEV)
-        ops.gemm(a, w, out)
-        torch.testing.assert_close(out.double(), ref, **tol(out_dt, scale))
-    from llmengine.engine.context import Workspace
+        from llmengine.engine.context import Workspace
+        for ws in (None, Workspace(torch.device(DEV))):  # with a workspace the product may be cut along K
+            out = torch.full((M, N), float("nan"), dtype=out_dt, device=DEV)
+            ops.gemm(a, w, out, ws)
+            torch.testing.assert_close(out.double(), ref, **tol(out_dt, scale))
     parts = ops.gemm_partials(a, w, Workspace(torch.device(DEV)), "t")
     assert parts.dtype == torch.float32 and parts.shape[1:] == (M, N)
     if M <= 64 and N <= 3072 and K >= 1024:
