@@ -69,6 +69,8 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Attn
   bf16* k_s = q_s + M_TILE * LD;                     // [2][N_TILE][LD]
   bf16* v_s = k_s + 2 * N_TILE * LD;                 // [2][N_TILE][LD]
 
+  dep_launch();
+  dep_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int seq = blockIdx.y;
   const int g = p.nq / p.nkv;
@@ -271,31 +273,51 @@ template <int HD>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int n_splits,
                                          long long part_stride_tokens, int nq, bf16* __restrict__ out, long long ld_out,
                                          int n_tokens) {
+  dep_launch();
+  dep_wait();
   const int item = blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (item >= n_tokens * nq) return;
   const int tok = item / nq, head = item % nq;
+  const size_t split_stride = (size_t)part_stride_tokens * nq;  // slots from one split to the next
+  const size_t slot0 = (size_t)tok * nq + head;
   float mx = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, part_ml[(((size_t)s * part_stride_tokens + tok) * nq + head) * 2]);
-  float acc[(HD + 31) / 32];
+  for (int s = lane; s < n_splits; s += 32) mx = fmaxf(mx, part_ml[(slot0 + s * split_stride) * 2]);
+  mx = warp_max(mx);
+  constexpr int R = (HD + 31) / 32;
+  float acc[R];
 #pragma unroll
-  for (int i = 0; i < (HD + 31) / 32; ++i) acc[i] = 0.f;
+  for (int i = 0; i < R; ++i) acc[i] = 0.f;
   float den = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const size_t slot = ((size_t)s * part_stride_tokens + tok) * nq + head;
-    const float m = part_ml[slot * 2], l = part_ml[slot * 2 + 1];
-    if (m == -INFINITY) continue;  // this split held no key of the row (its partial was never meaningful)
-    const float w = l * exp2f(m - mx);
-    den += w;
+  for (int s0 = 0; s0 < n_splits; s0 += 4) {  // four splits' loads in flight; added in index order
+    float w[4], v[4][R];
 #pragma unroll
-    for (int i = 0; i < (HD + 31) / 32; ++i) {
-      const int d = lane + 32 * i;
-      if (d < HD) acc[i] = fmaf(w, part_o[slot * HD + d], acc[i]);
+    for (int u = 0; u < 4; ++u) {
+      const int s = s0 + u;
+      w[u] = 0.f;
+      if (s < n_splits) {
+        const size_t slot = slot0 + s * split_stride;
+        const float m = part_ml[slot * 2], l = part_ml[slot * 2 + 1];
+        w[u] = (m == -INFINITY) ? 0.f : l * exp2f(m - mx);  // -inf: the split held no key of the row
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          const int d = lane + 32 * i;
+          v[u][i] = (d < HD && w[u] != 0.f) ? part_o[slot * HD + d] : 0.f;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (s0 + u < n_splits && w[u] != 0.f) {
+        den += w[u];
+#pragma unroll
+        for (int i = 0; i < R; ++i) acc[i] = fmaf(w[u], v[u][i], acc[i]);
+      }
     }
   }
   const float inv = den > 0.f ? 1.f / den : 0.f;
 #pragma unroll
-  for (int i = 0; i < (HD + 31) / 32; ++i) {
+  for (int i = 0; i < R; ++i) {
     const int d = lane + 32 * i;
     if (d < HD) out[(size_t)tok * ld_out + (size_t)head * HD + d] = __float2bfloat16_rn(acc[i] * inv);
   }
@@ -314,13 +336,13 @@ int launch(const AttnParams& p, int n_seqs, int max_new_tokens, int n_tokens, bo
   };
   if (split) {
     if (!set_attr(paged_attention_mma_kernel<HD, true>)) return 1;
-    paged_attention_mma_kernel<HD, true><<<grid, THREADS, smem, stream>>>(p);
+    launch_kernel(paged_attention_mma_kernel<HD, true>, grid, THREADS, smem, stream, p);
     const int items = n_tokens * p.nq;
-    attention_combine_kernel<HD><<<(items + 3) / 4, 128, 0, stream>>>(p.part_o, p.part_ml, p.n_splits, p.part_stride_tokens, p.nq,
-                                                                      p.out, p.ld_out, n_tokens);
+    launch_kernel(attention_combine_kernel<HD>, (items + 3) / 4, 128, 0, stream, (const float*)p.part_o, (const float*)p.part_ml,
+                  p.n_splits, p.part_stride_tokens, p.nq, p.out, p.ld_out, n_tokens);
   } else {
     if (!set_attr(paged_attention_mma_kernel<HD, false>)) return 1;
-    paged_attention_mma_kernel<HD, false><<<grid, THREADS, smem, stream>>>(p);
+    launch_kernel(paged_attention_mma_kernel<HD, false>, grid, THREADS, smem, stream, p);
   }
   return 0;
 }

@@ -28,6 +28,8 @@ __global__ void __launch_bounds__(WARPS * 32)
                                 int max_blocks, T* __restrict__ out, long long ld_out, int n_tokens, int nq,
                                 int nkv, int hd, int page_size, float scale, int window) {
   __shared__ float q_s[WARPS][MAX_HD];
+  dep_launch();
+  dep_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * WARPS + warp;
   if (item >= (long long)n_tokens * nq) return;  // whole warp leaves together
@@ -97,9 +99,9 @@ int launch(const void* q, long long ld_q, const void* kc, const void* vc, const 
   const long long items = (long long)n_tokens * nq;
   const int grid = ceil_div(items, WARPS);
 #define LLM_ATT_CASE(R)                                                                                     \
-  paged_attention_simt_kernel<T, R><<<grid, WARPS * 32, 0, stream>>>(                                       \
-      (const T*)q, ld_q, (const T*)kc, (const T*)vc, positions, token_seq, block_table, max_blocks, (T*)out, \
-      ld_out, n_tokens, nq, nkv, hd, page_size, scale, window)
+  launch_kernel(paged_attention_simt_kernel<T, R>, grid, WARPS * 32, 0, stream, (const T*)q, ld_q, (const T*)kc, \
+                (const T*)vc, positions, token_seq, block_table, max_blocks, (T*)out, ld_out, n_tokens, nq, nkv, hd, \
+                page_size, scale, window)
   if (hd <= 32) LLM_ATT_CASE(1);
   else if (hd <= 64) LLM_ATT_CASE(2);
   else if (hd <= 128) LLM_ATT_CASE(4);

@@ -81,3 +81,33 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch. Kernels of a step run back to back on one stream; each is
+// launched with the attribute that lets its blocks start while the previous kernel is still
+// draining. A kernel may do work that depends on nothing the stream produced (setting up shared
+// memory, fetching weights) before dep_wait(); after dep_wait() every earlier kernel of the stream
+// has finished and its writes are visible. EVERY kernel calls dep_wait() before it reads what an
+// earlier kernel wrote and before its first global write. dep_launch() lets the next kernel's
+// blocks be scheduled once all blocks of this one have called it (or left).
+__device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern "C" void llm_set_dependent_launch(int on);
+bool llm_dependent_launch();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = llm_dependent_launch() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

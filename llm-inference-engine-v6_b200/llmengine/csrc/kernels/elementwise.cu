@@ -1,6 +1,6 @@
-// Embedding gather, RMSNorm (with the residual sum fused in), SiLU*up, residual add.
-// The residual stream is float32 in both engine precisions; sums of squares, the reciprocal root
-// and the activation are computed in float32.
+// Embedding gather, RMSNorm (with the residual sum fused in), SiLU*up, residual add, sums of
+// K-split partials. The residual stream is float32 in both engine precisions; sums of squares, the
+// reciprocal root and the activation are computed in float32.
 //
 // Formulas follow the reference CPU ops: rmsnorm_f32 (src/kernels.cpp:18-24: out = w*x*inv_rms,
 // inv_rms = 1/sqrt(sum(x^2)/dim + eps)), silu_f32 (src/kernels.cpp:26-31: v/(1+exp(-v))) with the
@@ -12,6 +12,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int dim, int vocab) {
+  dep_launch();
+  dep_wait();
   const int row = blockIdx.x;
   int id = ids[row];
   if (id < 0 || id >= vocab) id = 0;  // ids are validated on the host; never read out of range
@@ -26,9 +28,9 @@ extern "C" int llm_embed(const void* table, int table_dtype, const int* ids, flo
   LLM_REQUIRE(n_rows > 0 && dim > 0 && vocab > 0, "embed: bad sizes rows=%d dim=%d vocab=%d", n_rows, dim, vocab);
   const int threads = dim >= 1024 ? 256 : 128;
   if (table_dtype == LLM_F32)
-    embed_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)table, ids, out, dim, vocab);
+    launch_kernel(embed_kernel<float>, n_rows, threads, 0, stream, (const float*)table, ids, out, dim, vocab);
   else if (table_dtype == LLM_BF16)
-    embed_kernel<bf16><<<n_rows, threads, 0, stream>>>((const bf16*)table, ids, out, dim, vocab);
+    launch_kernel(embed_kernel<bf16>, n_rows, threads, 0, stream, (const bf16*)table, ids, out, dim, vocab);
   else
     LLM_REQUIRE(false, "embed: unknown table dtype %d", table_dtype);
   LLM_CHECK_LAUNCH("embed");
@@ -39,12 +41,83 @@ extern "C" int llm_embed(const void* table, int table_dtype, const int* ids, flo
 // One block per output row. Source row r = rows ? rows[blockIdx.x] : blockIdx.x.
 // x = h[r] + sum_p delta[p][r] (partials added in index order); if write_back, h[r] = x.
 // out[blockIdx.x] = (w * x) * inv_rms.
+template <typename T>
+__device__ __forceinline__ void store4(T* dst, float a, float b, float c, float d);
+template <>
+__device__ __forceinline__ void store4<float>(float* dst, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+template <>
+__device__ __forceinline__ void store4<bf16>(bf16* dst, float a, float b, float c, float d) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 v;
+  v.x = *reinterpret_cast<uint32_t*>(&lo);
+  v.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = v;
+}
+
+// dim % 4 == 0 and dim <= 4 * R * blockDim: the row stays in registers between the two passes.
+template <typename TOut, int R>
+__global__ void __launch_bounds__(1024) rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ delta, int n_partials,
+                                                           size_t partial_stride, const float* __restrict__ w,
+                                                           const int* __restrict__ rows, TOut* __restrict__ out, int dim,
+                                                           float eps, int write_back) {
+  __shared__ float red[33];
+  dep_launch();
+  float4 wv[R];
+#pragma unroll
+  for (int k = 0; k < R; ++k) {  // the norm weight is not produced by the stream: fetch it before waiting
+    const int i = (threadIdx.x + k * blockDim.x) * 4;
+    wv[k] = i < dim ? *reinterpret_cast<const float4*>(w + i) : make_float4(0, 0, 0, 0);
+  }
+  dep_wait();
+  const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+  float* hr = h + (size_t)r * dim;
+  const float* dr = delta ? delta + (size_t)r * dim : nullptr;
+  float4 x[R];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < R; ++k) {
+    const int i = (threadIdx.x + k * blockDim.x) * 4;
+    x[k] = make_float4(0, 0, 0, 0);
+    if (i < dim) {
+      x[k] = *reinterpret_cast<const float4*>(hr + i);
+      if (dr) {
+        for (int p0 = 0; p0 < n_partials; p0 += 8) {  // eight loads in flight, then added in index order
+          float4 d[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            d[u] = (p0 + u < n_partials) ? *reinterpret_cast<const float4*>(dr + (size_t)(p0 + u) * partial_stride + i)
+                                         : make_float4(0, 0, 0, 0);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            if (p0 + u < n_partials) { x[k].x += d[u].x; x[k].y += d[u].y; x[k].z += d[u].z; x[k].w += d[u].w; }
+          }
+        }
+        if (write_back) *reinterpret_cast<float4*>(hr + i) = x[k];
+      }
+      ss += x[k].x * x[k].x + x[k].y * x[k].y + x[k].z * x[k].z + x[k].w * x[k].w;
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+  TOut* o = out + (size_t)blockIdx.x * dim;
+#pragma unroll
+  for (int k = 0; k < R; ++k) {
+    const int i = (threadIdx.x + k * blockDim.x) * 4;
+    if (i < dim)
+      store4<TOut>(o + i, (wv[k].x * x[k].x) * inv, (wv[k].y * x[k].y) * inv, (wv[k].z * x[k].z) * inv, (wv[k].w * x[k].w) * inv);
+  }
+}
+
 template <typename TOut>
 __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int n_partials,
                                size_t partial_stride, const float* __restrict__ w,
                                const int* __restrict__ rows, TOut* __restrict__ out, int dim, float eps,
                                int write_back) {
   __shared__ float red[33];
+  dep_launch();
+  dep_wait();
   const int r = rows ? rows[blockIdx.x] : blockIdx.x;
   float* hr = h + (size_t)r * dim;
   const float* dr = delta ? delta + (size_t)r * dim : nullptr;
@@ -68,6 +141,28 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ 
   }
 }
 
+template <typename TOut>
+static void launch_rmsnorm(float* h, const float* delta, int n_partials, size_t partial_stride, const float* w, const int* rows,
+                           TOut* out, int n_out_rows, int dim, float eps, int write_back, cudaStream_t stream) {
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  const bool vec = dim % 4 == 0 && dim <= 16384 && al(h) && al(w) && al(out) && (!delta || (al(delta) && partial_stride % 4 == 0));
+  if (vec) {
+    const int quads = dim / 4;
+    int threads = quads <= 1024 ? ((quads + 31) / 32) * 32 : 1024;
+    const int per_thread = (quads + threads - 1) / threads;
+    if (per_thread == 1)
+      launch_kernel(rmsnorm_vec_kernel<TOut, 1>, n_out_rows, threads, 0, stream, h, delta, n_partials, partial_stride, w, rows, out, dim, eps, write_back);
+    else if (per_thread == 2)
+      launch_kernel(rmsnorm_vec_kernel<TOut, 2>, n_out_rows, threads, 0, stream, h, delta, n_partials, partial_stride, w, rows, out, dim, eps, write_back);
+    else
+      launch_kernel(rmsnorm_vec_kernel<TOut, 4>, n_out_rows, threads, 0, stream, h, delta, n_partials, partial_stride, w, rows, out, dim, eps, write_back);
+    return;
+  }
+  int threads = 128;
+  while (threads < 1024 && threads * 4 < dim) threads *= 2;
+  launch_kernel(rmsnorm_kernel<TOut>, n_out_rows, threads, 0, stream, h, delta, n_partials, partial_stride, w, rows, out, dim, eps, write_back);
+}
+
 extern "C" int llm_rmsnorm(float* h, const float* delta, int n_partials, long long partial_stride,
                            const float* w, const int* rows, void* out, int out_dtype, int n_out_rows,
                            int dim, float eps, int write_back, cudaStream_t stream) {
@@ -75,14 +170,10 @@ extern "C" int llm_rmsnorm(float* h, const float* delta, int n_partials, long lo
   LLM_REQUIRE(n_out_rows > 0 && dim > 0, "rmsnorm: bad sizes rows=%d dim=%d", n_out_rows, dim);
   LLM_REQUIRE(!(rows && write_back), "rmsnorm: write_back with a row list is not allowed");
   LLM_REQUIRE(!delta || n_partials >= 1, "rmsnorm: delta needs n_partials >= 1");
-  int threads = 128;
-  while (threads < 1024 && threads * 4 < dim) threads *= 2;
   if (out_dtype == LLM_F32)
-    rmsnorm_kernel<float><<<n_out_rows, threads, 0, stream>>>(h, delta, n_partials, (size_t)partial_stride, w, rows,
-                                                              (float*)out, dim, eps, write_back);
+    launch_rmsnorm<float>(h, delta, n_partials, (size_t)partial_stride, w, rows, (float*)out, n_out_rows, dim, eps, write_back, stream);
   else if (out_dtype == LLM_BF16)
-    rmsnorm_kernel<bf16><<<n_out_rows, threads, 0, stream>>>(h, delta, n_partials, (size_t)partial_stride, w, rows,
-                                                             (bf16*)out, dim, eps, write_back);
+    launch_rmsnorm<bf16>(h, delta, n_partials, (size_t)partial_stride, w, rows, (bf16*)out, n_out_rows, dim, eps, write_back, stream);
   else
     LLM_REQUIRE(false, "rmsnorm: unknown out dtype %d", out_dtype);
   LLM_CHECK_LAUNCH("rmsnorm");
@@ -92,6 +183,8 @@ extern "C" int llm_rmsnorm(float* h, const float* delta, int n_partials, long lo
 // ------------------------------------------------------------------------------------ residual add
 __global__ void residual_add_kernel(float* __restrict__ h, const float* __restrict__ delta, int n_partials,
                                     size_t partial_stride, size_t n) {
+  dep_launch();
+  dep_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float x = h[i];
@@ -103,7 +196,7 @@ extern "C" int llm_residual_add(float* h, const float* delta, int n_partials, lo
                                 long long n, cudaStream_t stream) {
   if (n == 0) return LLM_OK;
   LLM_REQUIRE(n > 0 && n_partials >= 1, "residual_add: bad sizes");
-  residual_add_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(h, delta, n_partials, (size_t)partial_stride, (size_t)n);
+  launch_kernel(residual_add_kernel, ceil_div(n, 256), 256, 0, stream, h, delta, n_partials, (size_t)partial_stride, (size_t)n);
   LLM_CHECK_LAUNCH("residual_add");
   return LLM_OK;
 }
@@ -112,6 +205,8 @@ extern "C" int llm_residual_add(float* h, const float* delta, int n_partials, lo
 // in: [rows, 2*ff] with gate in columns [0,ff) and up in [ff,2ff); out: [rows, ff].
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int ff, size_t total) {
+  dep_launch();
+  dep_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t r = i / ff;
@@ -128,9 +223,9 @@ extern "C" int llm_silu_mul(const void* in, void* out, int dtype, int n_rows, in
   const size_t total = (size_t)n_rows * ff;
   const int blocks = ceil_div((long long)total, 256);
   if (dtype == LLM_F32)
-    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)in, (float*)out, ff, total);
+    launch_kernel(silu_mul_kernel<float>, blocks, 256, 0, stream, (const float*)in, (float*)out, ff, total);
   else if (dtype == LLM_BF16)
-    silu_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)in, (bf16*)out, ff, total);
+    launch_kernel(silu_mul_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)in, (bf16*)out, ff, total);
   else
     LLM_REQUIRE(false, "silu_mul: unknown dtype %d", dtype);
   LLM_CHECK_LAUNCH("silu_mul");
@@ -143,6 +238,8 @@ extern "C" int llm_silu_mul(const void* in, void* out, int dtype, int n_rows, in
 template <typename T>
 __global__ void reduce_partials_kernel(const float* __restrict__ partials, int n_partials, size_t stride,
                                        T* __restrict__ out, size_t total) {
+  dep_launch();
+  dep_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   float x = partials[i];
@@ -156,9 +253,9 @@ extern "C" int llm_reduce_partials(const float* partials, int n_partials, long l
   LLM_REQUIRE(total > 0 && n_partials >= 1, "reduce_partials: bad sizes");
   const int blocks = ceil_div(total, 256);
   if (out_dtype == LLM_F32)
-    reduce_partials_kernel<float><<<blocks, 256, 0, stream>>>(partials, n_partials, (size_t)stride, (float*)out, (size_t)total);
+    launch_kernel(reduce_partials_kernel<float>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (float*)out, (size_t)total);
   else if (out_dtype == LLM_BF16)
-    reduce_partials_kernel<bf16><<<blocks, 256, 0, stream>>>(partials, n_partials, (size_t)stride, (bf16*)out, (size_t)total);
+    launch_kernel(reduce_partials_kernel<bf16>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (bf16*)out, (size_t)total);
   else
     LLM_REQUIRE(false, "reduce_partials: unknown dtype %d", out_dtype);
   LLM_CHECK_LAUNCH("reduce_partials");
@@ -169,15 +266,27 @@ extern "C" int llm_reduce_partials(const float* partials, int n_partials, long l
 template <typename T>
 __global__ void silu_mul_partials_kernel(const float* __restrict__ partials, int n_partials, size_t stride,
                                          T* __restrict__ out, int ff, size_t total) {
+  dep_launch();
+  dep_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t r = i / ff;
   const int c = (int)(i - r * ff);
   const size_t gi = r * 2 * ff + c, ui = gi + ff;
-  float g = partials[gi], u = partials[ui];
-  for (int p = 1; p < n_partials; ++p) {
-    g += partials[(size_t)p * stride + gi];
-    u += partials[(size_t)p * stride + ui];
+  float g = 0.f, u = 0.f;
+  for (int p0 = 0; p0 < n_partials; p0 += 4) {  // four parts' loads in flight, added in index order
+    float gv[4], uv[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const bool in = p0 + k < n_partials;
+      gv[k] = in ? partials[(size_t)(p0 + k) * stride + gi] : 0.f;
+      uv[k] = in ? partials[(size_t)(p0 + k) * stride + ui] : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      g += gv[k];
+      u += uv[k];
+    }
   }
   const float s = g / (1.0f + expf(-g));
   out[i] = from_f32<T>(s * u);
@@ -190,9 +299,9 @@ extern "C" int llm_silu_mul_partials(const float* partials, int n_partials, long
   const size_t total = (size_t)n_rows * ff;
   const int blocks = ceil_div((long long)total, 256);
   if (out_dtype == LLM_F32)
-    silu_mul_partials_kernel<float><<<blocks, 256, 0, stream>>>(partials, n_partials, (size_t)stride, (float*)out, ff, total);
+    launch_kernel(silu_mul_partials_kernel<float>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (float*)out, ff, total);
   else if (out_dtype == LLM_BF16)
-    silu_mul_partials_kernel<bf16><<<blocks, 256, 0, stream>>>(partials, n_partials, (size_t)stride, (bf16*)out, ff, total);
+    launch_kernel(silu_mul_partials_kernel<bf16>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (bf16*)out, ff, total);
   else
     LLM_REQUIRE(false, "silu_mul_partials: unknown dtype %d", out_dtype);
   LLM_CHECK_LAUNCH("silu_mul_partials");

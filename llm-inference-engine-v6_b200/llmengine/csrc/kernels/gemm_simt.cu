@@ -18,6 +18,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TA* __restrict__ a
                                                         long long lda, long long ldw, long long ldo) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
+  dep_launch();
+  dep_wait();
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -80,7 +82,7 @@ template <typename TA, typename TW, typename TO>
 int launch(const void* a, const void* w, void* out, int M, int N, int K, long long lda, long long ldw,
            long long ldo, cudaStream_t stream) {
   dim3 grid(ceil_div(N, BN), ceil_div(M, BM));
-  gemm_simt_kernel<TA, TW, TO><<<grid, 256, 0, stream>>>((const TA*)a, (const TW*)w, (TO*)out, M, N, K, lda, ldw, ldo);
+  launch_kernel(gemm_simt_kernel<TA, TW, TO>, grid, 256, 0, stream, (const TA*)a, (const TW*)w, (TO*)out, M, N, K, lda, ldw, ldo);
   return 0;
 }
 

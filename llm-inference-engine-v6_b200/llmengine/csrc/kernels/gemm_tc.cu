@@ -196,11 +196,26 @@ __global__ void __launch_bounds__(128)
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
+  dep_launch();
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- producer: TMA loads
-    int issued = 0;
+    // The weight operand is not produced by the stream: its first tiles are requested before the
+    // wait on the previous kernel, the activation tiles after it.
+    const CUtensorMap* weight_map = SWAP ? &map_a : &map_b;
+    const CUtensorMap* act_map = SWAP ? &map_b : &map_a;
+    const int weight_row0 = SWAP ? a_row0 : b_row0, act_row0 = SWAP ? b_row0 : a_row0;
+    constexpr int WEIGHT_OFF = SWAP ? 0 : A_BYTES, ACT_OFF = SWAP ? A_BYTES : 0;
+    const int early = min(stages, n_iter);
+    for (int it = 0; it < early; ++it) {
+      mbar_expect_tx(&full[it], STAGE_BYTES);
+      tma_load_2d(smem + (size_t)it * STAGE_BYTES + WEIGHT_OFF, weight_map, (kt_begin + it) * BK, weight_row0, &full[it]);
+    }
+    dep_wait();
+    for (int it = 0; it < early; ++it)
+      tma_load_2d(smem + (size_t)it * STAGE_BYTES + ACT_OFF, act_map, (kt_begin + it) * BK, act_row0, &full[it]);
+    int issued = early;
     bool ok = true;
-    for (int it = 0; it < n_iter && ok; ++it) {
+    for (int it = early; it < n_iter && ok; ++it) {
       const int s = it % stages;
       const uint32_t ph = (uint32_t)(it / stages) & 1u;
       ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag, error_out, ERR_PRODUCER);
@@ -244,6 +259,7 @@ __global__ void __launch_bounds__(128)
     if (ok) mma_commit(acc_ready);
   }
   __syncwarp();
+  dep_wait();  // every thread: no global write before the previous kernels have finished
 
   // ------------------------------------------------------------------ epilogue: all four warps
   bool ready = n_iter > 0;
@@ -377,7 +393,7 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, i
     attr_set = true;
   }
   dim3 grid((RA + BM - 1) / BM, (RB + BN - 1) / BN, splits);
-  kernel<<<grid, 128, smem, stream>>>(ma, mb, (TO*)out, RA, RB, k_tiles, per_split, ldo, split_stride, stages, error_word());
+  launch_kernel(kernel, grid, 128, smem, stream, ma, mb, (TO*)out, RA, RB, k_tiles, per_split, ldo, split_stride, stages, error_word());
   return LLM_OK;
 }
 

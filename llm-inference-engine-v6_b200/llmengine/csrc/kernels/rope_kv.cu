@@ -11,19 +11,65 @@
 // request is block_table[request_row][p / page_size].
 #include "common.cuh"
 
+// With `parts` (float32 [n_parts, tokens, width] partial sums of the q|k|v product) the values are
+// the sums over parts in index order and only the q section of qkv is written.
+//
+// grid (tokens, chunks of 128 items); an item is one rotation pair of a q or k head, or two
+// neighbouring elements of v. Eight partial-sum loads are in flight per thread.
 template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long ld_qkv, const int* __restrict__ positions,
-                                     const int* __restrict__ token_seq, const int* __restrict__ block_table,
-                                     int max_blocks, const float* __restrict__ cos_t,
-                                     const float* __restrict__ sin_t, T* __restrict__ kcache,
-                                     T* __restrict__ vcache, int nq, int nkv, int hd, int page_size) {
+__global__ void __launch_bounds__(128)
+    rope_kv_write_kernel(T* __restrict__ qkv, long long ld_qkv, const float* __restrict__ parts, int n_parts, size_t part_stride,
+                         const int* __restrict__ positions, const int* __restrict__ token_seq,
+                         const int* __restrict__ block_table, int max_blocks, const float* __restrict__ cos_t,
+                         const float* __restrict__ sin_t, T* __restrict__ kcache, T* __restrict__ vcache, int nq, int nkv,
+                         int hd, int page_size) {
+  dep_launch();
+  dep_wait();
   const int t = blockIdx.x;
-  const int pos = positions[t];
   const int half = hd >> 1;
+  const int n_pairs = (nq + nkv) * half, n_vpairs = vcache ? nkv * half : 0;
+  const int item = blockIdx.y * blockDim.x + threadIdx.x;
+  if (item >= n_pairs + n_vpairs) return;
+  const int pos = positions[t];
+  const int width = (nq + 2 * nkv) * hd;
   T* row = qkv + (size_t)t * ld_qkv;
-  T* q = row;
-  T* k = row + (size_t)nq * hd;
-  T* v = k + (size_t)nkv * hd;
+
+  // the two columns of the q|k|v row that this thread owns
+  int col_a, col_b, head = 0, i = 0;
+  const bool is_v = item >= n_pairs;
+  if (!is_v) {
+    head = item / half;
+    i = item - head * half;
+    col_a = head * hd + i;
+    col_b = col_a + half;
+  } else {
+    col_a = (nq + nkv) * hd + 2 * (item - n_pairs);
+    col_b = col_a + 1;
+  }
+  float a, b;
+  if (parts) {
+    const float* pa = parts + (size_t)t * width + col_a;
+    const float* pb = parts + (size_t)t * width + col_b;
+    a = 0.f;
+    b = 0.f;
+    for (int p0 = 0; p0 < n_parts; p0 += 8) {
+      float va[8], vb[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const bool in = p0 + u < n_parts;
+        va[u] = in ? pa[(size_t)(p0 + u) * part_stride] : 0.f;
+        vb[u] = in ? pb[(size_t)(p0 + u) * part_stride] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {  // index order; the zeros of a short last batch change nothing
+        a += va[u];
+        b += vb[u];
+      }
+    }
+  } else {
+    a = to_f32(row[col_a]);
+    b = to_f32(row[col_b]);
+  }
 
   size_t cache_base = 0;
   if (kcache) {
@@ -32,43 +78,34 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long ld_qkv, cons
   }
   const size_t head_stride = (size_t)page_size * hd;
 
-  // q and k heads: (nq + nkv) * half pairs
-  const int n_pairs = (nq + nkv) * half;
-  for (int idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
-    const int head = idx / half, i = idx - head * half;
-    T* x = (head < nq) ? q + (size_t)head * hd : k + (size_t)(head - nq) * hd;
-    float a = to_f32(x[i]), b = to_f32(x[i + half]);
-    float ra = a, rb = b;
-    if (cos_t) {
-      const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
-      ra = a * c - b * s;
-      rb = b * c + a * s;
-    }
-    const T oa = from_f32<T>(ra), ob = from_f32<T>(rb);
-    if (head < nq) {
-      x[i] = oa;
-      x[i + half] = ob;
-    } else if (kcache) {
-      T* dst = kcache + cache_base + (size_t)(head - nq) * head_stride;
-      dst[i] = oa;
-      dst[i + half] = ob;
-    } else {
-      x[i] = oa;
-      x[i + half] = ob;
-    }
+  if (is_v) {
+    const int e = 2 * (item - n_pairs), vh = e / hd, vi = e - vh * hd;  // hd is even: both elements in one head
+    T* dst = vcache + cache_base + (size_t)vh * head_stride + vi;
+    dst[0] = from_f32<T>(a);
+    dst[1] = from_f32<T>(b);
+    return;
   }
-  if (vcache) {
-    const int n_v = nkv * hd;
-    for (int idx = threadIdx.x; idx < n_v; idx += blockDim.x) {
-      const int head = idx / hd, i = idx - head * hd;
-      vcache[cache_base + (size_t)head * head_stride + i] = v[idx];
-    }
+  float ra = a, rb = b;
+  if (cos_t) {
+    const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
+    ra = a * c - b * s;
+    rb = b * c + a * s;
+  }
+  const T oa = from_f32<T>(ra), ob = from_f32<T>(rb);
+  if (head < nq || !kcache) {
+    row[col_a] = oa;
+    row[col_b] = ob;
+  } else {
+    T* dst = kcache + cache_base + (size_t)(head - nq) * head_stride;
+    dst[i] = oa;
+    dst[i + half] = ob;
   }
 }
 
 // cos_t/sin_t may be null (no rotation); kcache/vcache may be null (a layer that reads another
 // layer's cache writes nothing, and k is then rotated in place in qkv).
-extern "C" int llm_rope_kv_write(void* qkv, long long ld_qkv, int dtype, const int* positions,
+extern "C" int llm_rope_kv_write(void* qkv, long long ld_qkv, int dtype, const float* parts, int n_parts,
+                                 long long part_stride, const int* positions,
                                  const int* token_seq, const int* block_table, int max_blocks,
                                  const float* cos_t, const float* sin_t, void* kcache, void* vcache,
                                  int n_tokens, int nq, int nkv, int hd, int page_size, cudaStream_t stream) {
@@ -77,15 +114,19 @@ extern "C" int llm_rope_kv_write(void* qkv, long long ld_qkv, int dtype, const i
               "rope_kv_write: bad sizes tokens=%d nq=%d nkv=%d hd=%d page=%d", n_tokens, nq, nkv, hd, page_size);
   LLM_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "rope_kv_write: cos and sin tables go together");
   LLM_REQUIRE((kcache == nullptr) == (vcache == nullptr), "rope_kv_write: k and v caches go together");
-  const int threads = 256;
+  LLM_REQUIRE(!parts || (n_parts >= 1 && kcache), "rope_kv_write: partial sums need n_parts >= 1 and a cache to write to");
+  const int threads = 128;
+  const int items = (nq + nkv) * (hd / 2) + (vcache ? nkv * (hd / 2) : 0);
+  const dim3 grid(n_tokens, ceil_div(items, threads));
+  LLM_REQUIRE(grid.y <= 65535, "rope_kv_write: too many heads");
   if (dtype == LLM_F32)
-    rope_kv_write_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)qkv, ld_qkv, positions, token_seq,
-                                                                  block_table, max_blocks, cos_t, sin_t,
-                                                                  (float*)kcache, (float*)vcache, nq, nkv, hd, page_size);
+    launch_kernel(rope_kv_write_kernel<float>, grid, threads, 0, stream, (float*)qkv, ld_qkv, parts, n_parts,
+                  (size_t)part_stride, positions, token_seq, block_table, max_blocks, cos_t, sin_t, (float*)kcache,
+                  (float*)vcache, nq, nkv, hd, page_size);
   else if (dtype == LLM_BF16)
-    rope_kv_write_kernel<bf16><<<n_tokens, threads, 0, stream>>>((bf16*)qkv, ld_qkv, positions, token_seq,
-                                                                 block_table, max_blocks, cos_t, sin_t,
-                                                                 (bf16*)kcache, (bf16*)vcache, nq, nkv, hd, page_size);
+    launch_kernel(rope_kv_write_kernel<bf16>, grid, threads, 0, stream, (bf16*)qkv, ld_qkv, parts, n_parts,
+                  (size_t)part_stride, positions, token_seq, block_table, max_blocks, cos_t, sin_t, (bf16*)kcache,
+                  (bf16*)vcache, nq, nkv, hd, page_size);
   else
     LLM_REQUIRE(false, "rope_kv_write: unknown dtype %d", dtype);
   LLM_CHECK_LAUNCH("rope_kv_write");

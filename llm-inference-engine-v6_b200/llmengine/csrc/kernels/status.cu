@@ -14,3 +14,8 @@ void llm_set_error(const char* fmt, ...) {
   vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
   va_end(ap);
 }
+
+static bool g_dependent_launch = true;
+
+extern "C" void llm_set_dependent_launch(int on) { g_dependent_launch = on != 0; }
+bool llm_dependent_launch() { return g_dependent_launch; }

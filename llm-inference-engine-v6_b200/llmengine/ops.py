@@ -133,7 +133,11 @@ class CudaOps:
         return out
 
     # ------------------------------------------------------------------ matrix products
-    SM_COUNT = 148  # CTAs aimed at when a weight-streaming product is cut along K
+    # A weight-streaming product (few tokens) is bound by memory; measured on B200 it streams fastest
+    # with several CTAs per SM, each with a short ring of stages; but every split adds a partial
+    # result that the consumer has to read. The K range is cut until there are about this many CTAs
+    # (each keeping at least two k-tiles of 64).
+    SPLIT_TARGET_CTAS = 296
 
     def _tc_usable(self, a: torch.Tensor, w: torch.Tensor) -> bool:
         """bfloat16 operands that the tensor-core kernel takes (16-byte aligned rows of K % 8 == 0)."""
@@ -145,9 +149,9 @@ class CudaOps:
 
     def _splits_for(self, M: int, N: int, K: int) -> int:
         tiles, k_tiles = (N + 127) // 128, (K + 63) // 64
-        if M > self.SWAP_MAX_TOKENS or tiles >= 96:
+        if M > self.SWAP_MAX_TOKENS:
             return 1
-        want = min(max(1, self.SM_COUNT // tiles), max(1, k_tiles // 4))
+        want = min(max(1, -(-self.SPLIT_TARGET_CTAS // tiles)), max(1, k_tiles // 2))
         return int(self.lib("tensorcore").llm_gemm_tc_splits(c_int(K), c_int(want)))
 
     SWAP_MAX_TOKENS = 64  # up to here weights fill the accumulator lanes and tokens the columns
@@ -160,7 +164,7 @@ class CudaOps:
         ldo = out.stride(-2)
         self._check(lib.llm_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)),
                                     c_longlong(w.stride(0)), c_longlong(ldo), c_int(dtype_code(out.dtype)), c_int(swap),
-                                    c_int(splits), c_longlong(split_stride), c_int(8), _stream()), lib)
+                                    c_int(splits), c_longlong(split_stride), c_int(3 if swap else 8), _stream()), lib)
 
     def gemm(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ws=None) -> torch.Tensor:
         """out[m,n] = sum_k a[m,k]*w[n,k]; float32 accumulation; a and w of one dtype; out float32
@@ -233,9 +237,11 @@ class CudaOps:
     def rope_kv_write(self, qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,
                       block_table: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                       kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor], n_tokens: int, nq: int,
-                      nkv: int, hd: int) -> None:
+                      nkv: int, hd: int, parts: Optional[torch.Tensor] = None) -> None:
         """Rotates q and k of qkv [n, (nq+2nkv)*hd] in place by the tables cos/sin [max_pos, hd/2]
-        and writes k, v of each token into its page: kcache/vcache [pages, nkv, page_size, hd]."""
+        and writes k, v of each token into its page: kcache/vcache [pages, nkv, page_size, hd].
+        With `parts` (float32 [p, n, width] partial sums of the q|k|v product) the values are the
+        sums over parts; then only the q section of qkv is written (k and v go to the cache)."""
         _need(qkv, "rope.qkv"); _need(positions, "rope.positions", torch.int32)
         _need(token_seq, "rope.token_seq", torch.int32); _need(block_table, "rope.block_table", torch.int32)
         page_size = 1
@@ -249,8 +255,13 @@ class CudaOps:
             assert cos.is_contiguous() and sin.is_contiguous() and cos.shape[1] == hd // 2
         assert qkv.shape[1] == (nq + 2 * nkv) * hd and block_table.is_contiguous()
         lib = self.lib()
+        n_parts, pstride = 0, 0
+        if parts is not None:
+            _need(parts, "rope.parts", torch.float32)
+            assert parts.is_contiguous() and parts.dim() == 3 and parts.shape[2] == qkv.shape[1] and parts.shape[1] >= n_tokens
+            n_parts, pstride = parts.shape[0], parts.stride(0)
         self._check(lib.llm_rope_kv_write(_ptr(qkv), c_longlong(qkv.stride(0)), c_int(dtype_code(qkv.dtype)),
-                                          _ptr(positions), _ptr(token_seq), _ptr(block_table),
+                                          _ptr(parts), c_int(n_parts), c_longlong(pstride), _ptr(positions), _ptr(token_seq), _ptr(block_table),
                                           c_int(block_table.shape[1]), _ptr(cos), _ptr(sin), _ptr(kcache),
                                           _ptr(vcache), c_int(n_tokens), c_int(nq), c_int(nkv), c_int(hd),
                                           c_int(page_size), _stream()), lib)
@@ -294,19 +305,34 @@ class CudaOps:
         return out
 
     # ------------------------------------------------------------------ sampling
+    def sample_scratch_words(self, n_rows: int, vocab: int) -> int:
+        """4-byte words of scratch that `sample` needs for n_rows rows."""
+        return 2 * n_rows * int(self.lib().llm_sample_chunks(c_int(vocab)))
+
     def sample(self, logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
                seeds: Optional[torch.Tensor] = None, draws: Optional[torch.Tensor] = None,
-               n_rows: Optional[int] = None) -> torch.Tensor:
-        """out[r] (int32) = greedy or temperature choice for logits row r (float32)."""
+               n_rows: Optional[int] = None, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """out[r] (int32) = greedy or temperature choice for logits row r (float32). scratch: int32
+        tensor of sample_scratch_words(rows, vocab) elements (made here when not given)."""
         _need(logits, "sample.logits", torch.float32); _need(out, "sample.out", torch.int32)
         n = logits.shape[0] if n_rows is None else n_rows
         for t, nm in ((temperature, "temperature"), (seeds, "seeds"), (draws, "draws")):
             if t is not None:
                 _need(t, f"sample.{nm}", torch.float32 if nm == "temperature" else torch.int32)
         lib = self.lib()
+        words = self.sample_scratch_words(max(n, 1), logits.shape[1])
+        if scratch is None:
+            scratch = torch.empty(words, dtype=torch.int32, device=logits.device)
+        assert scratch.dtype == torch.int32 and scratch.numel() >= words and scratch.is_cuda
         self._check(lib.llm_sample(_ptr(logits), c_longlong(logits.stride(0)), _ptr(temperature), _ptr(seeds),
-                                   _ptr(draws), _ptr(out), c_int(n), c_int(logits.shape[1]), _stream()), lib)
+                                   _ptr(draws), _ptr(out), c_int(n), c_int(logits.shape[1]), _ptr(scratch), _stream()), lib)
+        self.launches += 1  # two kernels
         return out
+
+    def set_dependent_launch(self, on: bool) -> None:
+        """Programmatic dependent launch of the kernels (on by default); off for A/B measurements."""
+        for name in ("core", "tensorcore"):
+            self.lib(name).llm_set_dependent_launch(c_int(1 if on else 0))
 
 
 _OPS: Optional[CudaOps] = None

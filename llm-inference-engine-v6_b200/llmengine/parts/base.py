@@ -90,8 +90,12 @@ class Norm(Part):
 class PositionEncoding(Part):
     category = "position"
 
+    # True if rotate_and_store takes `parts`: float32 [p, tokens, width] partial sums of the q|k|v
+    # product to be added (in index order) while encoding, instead of finished values in qkv.
+    takes_partial_sums = False
+
     def rotate_and_store(self, qkv: torch.Tensor, ctx, cache: LayerCache, num_heads: int, num_kv_heads: int,
-                         head_dim: int) -> None:
+                         head_dim: int, parts: Optional[torch.Tensor] = None) -> None:
         """Encodes positions into q and k of qkv [tokens, (heads + 2 kv_heads) * head_dim] in place
         and writes k, v of every token into its page of `cache` (if cache.writes)."""
         raise NotImplementedError

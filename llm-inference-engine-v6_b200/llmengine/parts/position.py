@@ -48,6 +48,8 @@ def rope_tables(spec: PositionSpec):
 
 
 class RotaryPosition(PositionEncoding):
+    takes_partial_sums = True
+
     def __init__(self, spec: PositionSpec, env):
         super().__init__(spec, env)
         if spec.head_dim <= 0 or spec.head_dim % 2:
@@ -58,18 +60,22 @@ class RotaryPosition(PositionEncoding):
         self.cos = torch.from_numpy(cos).to(env.device)
         self.sin = torch.from_numpy(sin).to(env.device)
 
-    def rotate_and_store(self, qkv, ctx, cache: LayerCache, num_heads, num_kv_heads, head_dim) -> None:
+    def rotate_and_store(self, qkv, ctx, cache: LayerCache, num_heads, num_kv_heads, head_dim, parts=None) -> None:
         write = cache.writes and cache.k is not None
         self.env.ops.rope_kv_write(qkv, ctx.positions, ctx.token_seq, ctx.block_tables[cache.group], self.cos, self.sin,
                                    cache.k if write else None, cache.v if write else None, ctx.n_tokens, num_heads,
-                                   num_kv_heads, head_dim)
+                                   num_kv_heads, head_dim, parts=parts)
 
 
 class NoPosition(PositionEncoding):
-    def rotate_and_store(self, qkv, ctx, cache: LayerCache, num_heads, num_kv_heads, head_dim) -> None:
+    takes_partial_sums = True
+
+    def rotate_and_store(self, qkv, ctx, cache: LayerCache, num_heads, num_kv_heads, head_dim, parts=None) -> None:
         if cache.writes and cache.k is not None:
             self.env.ops.rope_kv_write(qkv, ctx.positions, ctx.token_seq, ctx.block_tables[cache.group], None, None,
-                                       cache.k, cache.v, ctx.n_tokens, num_heads, num_kv_heads, head_dim)
+                                       cache.k, cache.v, ctx.n_tokens, num_heads, num_kv_heads, head_dim, parts=parts)
+        elif parts is not None:
+            self.env.ops.reduce_partials(parts, qkv)
 
 
 register_part("position", "rope", RotaryPosition)

@@ -17,6 +17,7 @@ class Sampler:
         self.ops, self.device = ops, device
         self._out: Optional[torch.Tensor] = None
         self._host: Optional[torch.Tensor] = None
+        self._scratch: Optional[torch.Tensor] = None
 
     def _buffers(self, n: int):
         if self._out is None or self._out.numel() < n:
@@ -25,12 +26,21 @@ class Sampler:
             self._host = torch.empty(cap, dtype=torch.int32, pin_memory=self.device.type == "cuda")
         return self._out, self._host
 
+    def _scratch_for(self, n: int, vocab: int):
+        if not hasattr(self.ops, "sample_scratch_words"):
+            return None
+        words = self.ops.sample_scratch_words(n, vocab)
+        if self._scratch is None or self._scratch.numel() < words:
+            self._scratch = torch.empty(max(words, 1024), dtype=torch.int32, device=self.device)
+        return self._scratch
+
     def sample_device(self, logits: torch.Tensor, ctx, n_rows: Optional[int] = None) -> torch.Tensor:
         """-> int32 device tensor [rows]; the rows' parameters come from the step's batch."""
         n = logits.shape[0] if n_rows is None else n_rows
         out, _ = self._buffers(max(n, 1))
         if n:
-            self.ops.sample(logits, out, ctx.row_temperature, ctx.row_seed, ctx.row_draw, n_rows=n)
+            self.ops.sample(logits, out, ctx.row_temperature, ctx.row_seed, ctx.row_draw, n_rows=n,
+                            scratch=self._scratch_for(n, logits.shape[1]))
         return out[:n]
 
     def sample(self, logits: torch.Tensor, ctx, n_rows: Optional[int] = None) -> List[int]:
@@ -50,5 +60,5 @@ class Sampler:
         if n == 0:
             return []
         out, _ = self._buffers(n)
-        self.ops.sample(logits, out, None, None, None, n_rows=n)
+        self.ops.sample(logits, out, None, None, None, n_rows=n, scratch=self._scratch_for(n, logits.shape[1]))
         return out[:n].tolist()

@@ -71,11 +71,12 @@ class CpuOps:
     def silu_mul_partials(self, parts, out):
         return self.silu_mul(parts.sum(0), out)
 
-    def rope_kv_write(self, qkv, positions, token_seq, block_table, cos, sin, kcache, vcache, n_tokens, nq, nkv, hd):
+    def rope_kv_write(self, qkv, positions, token_seq, block_table, cos, sin, kcache, vcache, n_tokens, nq, nkv, hd, parts=None):
         half = hd // 2
+        src = qkv if parts is None else parts.sum(0)
         for t in range(n_tokens):
             pos = int(positions[t])
-            row = qkv[t].float()
+            row = src[t].float()
             q = row[: nq * hd].view(nq, hd).clone()
             k = row[nq * hd:(nq + nkv) * hd].view(nkv, hd).clone()
             v = row[(nq + nkv) * hd:].view(nkv, hd)
@@ -125,7 +126,7 @@ class CpuOps:
         x ^= x >> np.uint32(16)
         return x
 
-    def sample(self, logits, out, temperature=None, seeds=None, draws=None, n_rows=None):
+    def sample(self, logits, out, temperature=None, seeds=None, draws=None, n_rows=None, scratch=None):
         n = logits.shape[0] if n_rows is None else n_rows
         V = logits.shape[1]
         for r in range(n):

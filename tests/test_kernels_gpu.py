@@ -115,7 +115,7 @@ def test_gemm_tensor_cores(ops, M, N, K):
             torch.testing.assert_close(out.double(), ref, **tol(out_dt, scale))
     parts = ops.gemm_partials(a, w, Workspace(torch.device(DEV)), "t")
     assert parts.dtype == torch.float32 and parts.shape[1:] == (M, N)
-    if M <= 64 and N <= 3072 and K >= 1024:
+    if M <= 64 and N <= 3072 and K >= 256:
         assert parts.shape[0] > 1  # few tokens, few output tiles, long K: cut along K
     torch.testing.assert_close(parts.double().sum(0), ref, **tol(torch.float32, scale))
     red = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
@@ -300,6 +300,22 @@ def test_rope_and_cache_write(ops, dt, nq, nkv, hd, page):
         assert torch.equal(vc[pg, :, p % page].float().cpu(), torch.from_numpy(v_ref[i]))
     # nothing else was touched
     assert float(kc.float().abs().sum(dim=(1, 3)).cpu()[~written].sum()) == 0
+    # the same from K-split partial sums: three float32 parts that add up to the q|k|v rows
+    of = orig.float()
+    p1, p2 = rnd(n, of.shape[1], seed=31), rnd(n, of.shape[1], seed=32)
+    parts = torch.stack([p1, p2, of - p1 - p2]).contiguous()
+    summed = (parts[0] + parts[1] + parts[2])
+    qkv3 = torch.zeros_like(orig)
+    kc3, vc3 = torch.zeros_like(kc), torch.zeros_like(vc)
+    ops.rope_kv_write(qkv3, positions, token_seq, table, cos_d, sin_d, kc3, vc3, n, nq, nkv, hd, parts=parts)
+    s3 = summed.cpu().numpy()
+    q3 = P.apply_rope(s3[:, :nq * hd].reshape(n, nq, hd), cos[pos], sin[pos])
+    k3 = P.apply_rope(s3[:, nq * hd:(nq + nkv) * hd].reshape(n, nkv, hd), cos[pos], sin[pos])
+    torch.testing.assert_close(qkv3[:, :nq * hd].float().cpu(), torch.from_numpy(q3.reshape(n, -1)), **tol(dt, 4))
+    for i, (s_, p_) in enumerate(toks):
+        pg = int(table[s_, p_ // page])
+        torch.testing.assert_close(kc3[pg, :, p_ % page].float().cpu(), torch.from_numpy(k3[i]), **tol(dt, 4))
+        torch.testing.assert_close(vc3[pg, :, p_ % page].float().cpu(), torch.from_numpy(s3[i, (nq + nkv) * hd:].reshape(nkv, hd)), **tol(dt, 4))
     # no tables: q, k stay as they are, k and v are only stored
     qkv2 = orig.clone()
     ops.rope_kv_write(qkv2, positions, token_seq, table, None, None, kc, vc, n, nq, nkv, hd)
