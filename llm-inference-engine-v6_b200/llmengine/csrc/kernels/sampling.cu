@@ -128,3 +128,66 @@ extern "C" int llm_sample(const float* logits, long long ld, const float* temper
   LLM_CHECK_LAUNCH("sample");
   return LLM_OK;
 }
+
+// ------------------------------------------------------------------------------------------------
+// The variant that allocates nothing (see sampling_no_alloc.h for who needs it and its contract).
+#include "sampling_no_alloc.h"
+
+#include <mutex>
+
+namespace {
+
+// Scratch of the two-stage argmax for the largest request this entry point takes. It is part of
+// the library's device image: every GPU that loads the library keeps it until the process ends.
+static __device__ __align__(256) unsigned char g_sample_scratch[LLM_SAMPLE_NO_ALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+void* g_sample_scratch_addr[kMaxDevices] = {};  // device address of the array, per device ordinal
+std::mutex g_sample_scratch_mu;
+
+// In host code `g_sample_scratch` is only a handle for the runtime, not a device address: the
+// address has to be asked for, once per device, while that device is current.
+int sample_scratch_for_current_device(void** addr) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    llm_set_error("sample_no_alloc: cannot tell the current device (%s)", e == cudaSuccess ? "ordinal out of range" : cudaGetErrorString(e));
+    return LLM_ERR_LAUNCH;
+  }
+  std::lock_guard<std::mutex> lock(g_sample_scratch_mu);
+  if (!g_sample_scratch_addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_sample_scratch);
+    if (e != cudaSuccess || !p) {
+      llm_set_error("sample_no_alloc: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+      return LLM_ERR_LAUNCH;
+    }
+    g_sample_scratch_addr[dev] = p;
+  }
+  *addr = g_sample_scratch_addr[dev];
+  return LLM_OK;
+}
+
+}  // namespace
+
+extern "C" int llm_sample_no_alloc(const float* logits, long long ld, const float* temperature, const int* seeds,
+                                   const int* draws, int* out, int n_rows, int vocab, cudaStream_t stream) {
+  if (n_rows == 0) return LLM_OK;
+  LLM_REQUIRE(n_rows > 0 && vocab > 0 && ld >= vocab, "sample_no_alloc: bad sizes rows=%d vocab=%d", n_rows, vocab);
+  LLM_REQUIRE(n_rows <= LLM_SAMPLE_NO_ALLOC_MAX_ROWS, "sample_no_alloc: %d rows exceed the built-in scratch (at most %d rows a call)",
+              n_rows, LLM_SAMPLE_NO_ALLOC_MAX_ROWS);
+  LLM_REQUIRE(!temperature || (seeds && draws), "sample_no_alloc: temperature needs seeds and draw indices");
+  const int chunks = llm_sample_chunks(vocab);
+  LLM_REQUIRE(chunks <= LLM_SAMPLE_NO_ALLOC_MAX_CHUNKS, "sample_no_alloc: %d chunks exceed the built-in scratch", chunks);
+  void* scratch = nullptr;
+  const int rc = sample_scratch_for_current_device(&scratch);
+  if (rc != LLM_OK) return rc;
+  const int chunk = (vocab + chunks - 1) / chunks;
+  float* best_val = (float*)scratch;
+  int* best_idx = (int*)scratch + (size_t)n_rows * chunks;
+  // every (row, chunk) word read by the merge is written by the scan of this same call
+  launch_kernel(sample_scan_kernel, dim3(chunks, n_rows), 256, 0, stream, logits, ld, temperature, seeds, draws, best_val, best_idx, vocab, chunk);
+  launch_kernel(sample_merge_kernel, ceil_div(n_rows, 4), 128, 0, stream, (const float*)best_val, (const int*)best_idx, chunks, out, n_rows);
+  LLM_CHECK_LAUNCH("sample_no_alloc");
+  return LLM_OK;
+}
