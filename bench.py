@@ -217,7 +217,10 @@ def run_ours(args):
 
     clocks = ClockSampler()
     clocks.start()
-    sec, launches, _, _ = decode_run(args.batch, K, W, e2e=False)
+    if "decode" in skip:  # profiling runs of the prefill alone
+        sec, launches = float("inf"), 0
+    else:
+        sec, launches, _, _ = decode_run(args.batch, K, W, e2e=False)
     clock_rec = clocks.stop()
     e2e_sec, h2d, d2h = sec, 0, 0
     if "e2e" not in skip:
@@ -231,12 +234,12 @@ def run_ours(args):
 
     value = args.batch / sec
     bytes_step = decode_bytes(g, layers, args.batch, CONTEXT + W + K // 2)
-    achieved = bytes_step / sec / 1e9
+    achieved = bytes_step / sec / 1e9 if sec != float("inf") else 0.0
     pf = flops_of_prefill(g, layers, PREFILL_TOKENS)
     rec = {
         "metric": "decode tok/s at batch 8 (Llama 3.2 1B geometry, 2048-token contexts)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
-        "ms_per_step": round(sec * 1e3, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": round(sec * 1e3, 4) if sec != float("inf") else None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), uniform random token ids", "impl": "ours",
         "config": {"model": "llama-3.2-1b-geometry", "global_batch": args.batch, "seq_len": CONTEXT,
                    "context_limit": CONTEXT_LIMIT, "parallelism": "single-gpu", "layers": layers,
@@ -327,7 +330,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the full configuration (named in `config`)")
     ap.add_argument("--no-points", dest="points", action="store_false", help="skip the batch 1 and 64 points")
-    ap.add_argument("--skip", default="", help="comma list of parts to leave out: e2e,prefill,points (for profiling runs)")
+    ap.add_argument("--skip", default="", help="comma list of parts to leave out: decode,e2e,prefill,points (for profiling runs)")
     ap.add_argument("--no-cuda-graphs", dest="graphs", action="store_false", help="launch decode steps kernel by kernel")
     ap.add_argument("--reference-setup-limit", type=float, default=900.0, help="seconds the reference arm may spend filling contexts")
     args = ap.parse_args()

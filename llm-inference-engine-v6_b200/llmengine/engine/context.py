@@ -35,6 +35,15 @@ class Workspace:
             self._buffers[tag] = buf
         return buf[:nbytes].view(dtype).view(shape)
 
+    def get_zeroed(self, tag: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        """As get, for memory that must read zero the first time: the buffer is cleared when it is
+        made (or grown), not at every call; its users leave it zero again."""
+        before = self._buffers.get(tag)
+        out = self.get(tag, shape, dtype)
+        if self._buffers.get(tag) is not before:
+            self._buffers[tag].zero_()
+        return out
+
     def bytes(self) -> int:
         return sum(b.numel() for b in self._buffers.values())
 

@@ -30,7 +30,7 @@ class _Captured:
 
 
 class DecodeGraphs:
-    BLOCK_BUCKET = 64  # block-table widths are rounded up to this many pages
+    BLOCK_BUCKET = 16  # block-table widths are rounded up to this many pages (one graph per width)
 
     def __init__(self, engine):
         self.engine = engine

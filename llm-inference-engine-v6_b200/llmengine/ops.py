@@ -266,7 +266,9 @@ class CudaOps:
                                           _ptr(vcache), c_int(n_tokens), c_int(nq), c_int(nkv), c_int(hd),
                                           c_int(page_size), _stream()), lib)
 
-    ATTENTION_SPLIT_KEYS = 256  # decoding: keys per split (absolute boundaries, a multiple of 64)
+    # decoding: the key range is cut at absolute multiples of `split_keys` (a multiple of 64) into as
+    # many splits as still fit the GPU in ONE wave of CTAs (three 76 KB CTAs per SM at head size 64)
+    ATTENTION_TARGET_CTAS = 444
 
     def paged_attention(self, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, batch,
                         block_table: torch.Tensor, out: torch.Tensor, nq: int, nkv: int, hd: int, scale: float,
@@ -284,17 +286,21 @@ class CudaOps:
         if q.dtype == torch.bfloat16 and self.tensor_cores:
             lib = self.lib("tensorcore")
             if lib.llm_attention_mma_supported(c_int(nq), c_int(nkv), c_int(hd), c_longlong(q.stride(0)), c_longlong(out.stride(0))):
-                n_splits, scratch = 1, None
-                if batch.max_new_tokens == 1 and batch.max_seq_len > 2 * self.ATTENTION_SPLIT_KEYS:
-                    n_splits = (batch.max_seq_len + self.ATTENTION_SPLIT_KEYS - 1) // self.ATTENTION_SPLIT_KEYS
+                n_splits, split_keys, scratch, counters = 1, 256, None, None
+                if batch.max_new_tokens == 1 and batch.n_tokens == batch.n_seqs and batch.max_seq_len > 256:
+                    want = max(1, self.ATTENTION_TARGET_CTAS // (batch.n_seqs * nkv))
+                    split_keys = -(-max(64, -(-batch.max_seq_len // want)) // 64) * 64
+                    n_splits = -(-batch.max_seq_len // split_keys)
+                if n_splits > 1:
                     floats = int(lib.llm_attention_mma_scratch_floats(c_int(n_tokens), c_int(nq), c_int(hd), c_int(n_splits)))
                     scratch = batch.ws.get("attention.splits", (floats,), torch.float32)
+                    counters = batch.ws.get_zeroed("attention.split_counters", (batch.n_seqs * nkv,), torch.int32)
                 self._check(lib.llm_paged_attention_mma(
                     _ptr(q), c_longlong(q.stride(0)), _ptr(kcache), _ptr(vcache), _ptr(batch.seq_start), _ptr(batch.seq_ntok),
                     _ptr(batch.seq_qoff), _ptr(block_table), c_int(block_table.shape[1]), _ptr(out), c_longlong(out.stride(0)),
                     c_int(batch.n_seqs), c_int(n_tokens), c_int(batch.max_new_tokens), c_int(nq), c_int(nkv), c_int(hd),
-                    c_int(page), c_float(scale), c_int(window), c_int(n_splits), c_int(self.ATTENTION_SPLIT_KEYS),
-                    _ptr(scratch), _stream()), lib)
+                    c_int(page), c_float(scale), c_int(window), c_int(n_splits), c_int(split_keys),
+                    _ptr(scratch), _ptr(counters), _stream()), lib)
                 return out
         lib = self.lib()
         self._check(lib.llm_paged_attention_simt(_ptr(q), c_longlong(q.stride(0)), _ptr(kcache), _ptr(vcache),
