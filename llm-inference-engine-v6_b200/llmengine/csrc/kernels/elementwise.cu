@@ -202,30 +202,44 @@ extern "C" int llm_residual_add(float* h, const float* delta, int n_partials, lo
 }
 
 // ------------------------------------------------------------------------------------ SiLU(gate) * up
-// in: [rows, 2*ff] with gate in columns [0,ff) and up in [ff,2ff); out: [rows, ff].
+// in: [rows, 2*ff]; out: [rows, ff]. Column layout of `in`: block == 0: gate in columns [0,ff), up in
+// [ff,2ff); block == b > 0: blocks of 2b columns, b of gate followed by the b matching ones of up.
+__device__ __forceinline__ void gate_up_columns(int c, int ff, int block, size_t* gate, size_t* up) {
+  if (block == 0) {
+    *gate = c;
+    *up = (size_t)ff + c;
+  } else {
+    *gate = (size_t)(c / block) * 2 * block + (c % block);
+    *up = *gate + block;
+  }
+}
+
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int ff, size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int ff, size_t total, int block) {
   dep_launch();
   dep_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t r = i / ff;
   const int c = (int)(i - r * ff);
-  const float g = to_f32(in[r * 2 * ff + c]);
-  const float u = to_f32(in[r * 2 * ff + ff + c]);
+  size_t gc, uc;
+  gate_up_columns(c, ff, block, &gc, &uc);
+  const float g = to_f32(in[r * 2 * ff + gc]);
+  const float u = to_f32(in[r * 2 * ff + uc]);
   float s = g / (1.0f + expf(-g));
   out[i] = from_f32<T>(s * u);
 }
 
-extern "C" int llm_silu_mul(const void* in, void* out, int dtype, int n_rows, int ff, cudaStream_t stream) {
+extern "C" int llm_silu_mul(const void* in, void* out, int dtype, int n_rows, int ff, int block, cudaStream_t stream) {
   if (n_rows == 0) return LLM_OK;
   LLM_REQUIRE(n_rows > 0 && ff > 0, "silu_mul: bad sizes rows=%d ff=%d", n_rows, ff);
+  LLM_REQUIRE(block >= 0 && (block == 0 || ff % block == 0), "silu_mul: column block %d does not divide %d", block, ff);
   const size_t total = (size_t)n_rows * ff;
   const int blocks = ceil_div((long long)total, 256);
   if (dtype == LLM_F32)
-    launch_kernel(silu_mul_kernel<float>, blocks, 256, 0, stream, (const float*)in, (float*)out, ff, total);
+    launch_kernel(silu_mul_kernel<float>, blocks, 256, 0, stream, (const float*)in, (float*)out, ff, total, block);
   else if (dtype == LLM_BF16)
-    launch_kernel(silu_mul_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)in, (bf16*)out, ff, total);
+    launch_kernel(silu_mul_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)in, (bf16*)out, ff, total, block);
   else
     LLM_REQUIRE(false, "silu_mul: unknown dtype %d", dtype);
   LLM_CHECK_LAUNCH("silu_mul");
@@ -265,14 +279,16 @@ extern "C" int llm_reduce_partials(const float* partials, int n_partials, long l
 // partials: [parts, rows, 2*ff] float32 (gate | up); out [rows, ff] = silu(sum gate) * (sum up).
 template <typename T>
 __global__ void silu_mul_partials_kernel(const float* __restrict__ partials, int n_partials, size_t stride,
-                                         T* __restrict__ out, int ff, size_t total) {
+                                         T* __restrict__ out, int ff, size_t total, int block) {
   dep_launch();
   dep_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t r = i / ff;
   const int c = (int)(i - r * ff);
-  const size_t gi = r * 2 * ff + c, ui = gi + ff;
+  size_t gc, uc;
+  gate_up_columns(c, ff, block, &gc, &uc);
+  const size_t gi = r * 2 * ff + gc, ui = r * 2 * ff + uc;
   float g = 0.f, u = 0.f;
   for (int p0 = 0; p0 < n_partials; p0 += 4) {  // four parts' loads in flight, added in index order
     float gv[4], uv[4];
@@ -293,15 +309,16 @@ __global__ void silu_mul_partials_kernel(const float* __restrict__ partials, int
 }
 
 extern "C" int llm_silu_mul_partials(const float* partials, int n_partials, long long stride, void* out, int out_dtype,
-                                     int n_rows, int ff, cudaStream_t stream) {
+                                     int n_rows, int ff, int block, cudaStream_t stream) {
   if (n_rows == 0) return LLM_OK;
   LLM_REQUIRE(n_rows > 0 && ff > 0 && n_partials >= 1, "silu_mul_partials: bad sizes");
+  LLM_REQUIRE(block >= 0 && (block == 0 || ff % block == 0), "silu_mul_partials: column block %d does not divide %d", block, ff);
   const size_t total = (size_t)n_rows * ff;
   const int blocks = ceil_div((long long)total, 256);
   if (out_dtype == LLM_F32)
-    launch_kernel(silu_mul_partials_kernel<float>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (float*)out, ff, total);
+    launch_kernel(silu_mul_partials_kernel<float>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (float*)out, ff, total, block);
   else if (out_dtype == LLM_BF16)
-    launch_kernel(silu_mul_partials_kernel<bf16>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (bf16*)out, ff, total);
+    launch_kernel(silu_mul_partials_kernel<bf16>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (bf16*)out, ff, total, block);
   else
     LLM_REQUIRE(false, "silu_mul_partials: unknown dtype %d", out_dtype);
   LLM_CHECK_LAUNCH("silu_mul_partials");

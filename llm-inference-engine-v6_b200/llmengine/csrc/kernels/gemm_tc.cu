@@ -156,7 +156,11 @@ __device__ __forceinline__ void store_row16<bf16>(bf16* dst, const float* v, int
 }
 
 // grid: (tiles of A rows, tiles of B rows, K splits); block: 128 threads.
-template <int BN, bool SWAP, typename TO>
+// SWIGLU (token tiles of 256 outputs only): the weight rows come in blocks of 256 = 128 rows of the
+// gate projection followed by the 128 matching rows of the up projection, so one accumulator tile
+// holds both; the epilogue writes silu(gate) * up, 128 columns per tile, and the 2x wider
+// intermediate never goes to memory.
+template <int BN, bool SWAP, typename TO, bool SWIGLU = false>
 __global__ void __launch_bounds__(128)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TO* __restrict__ out,
                    int RA, int RB, int k_tiles, int k_tiles_per_split, long long ldo, long long split_stride, int stages,
@@ -268,7 +272,23 @@ __global__ void __launch_bounds__(128)
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   TO* o = out + (size_t)blockIdx.z * split_stride;
   const int ra = a_row0 + warp * 32 + lane;
-  if (ready || n_iter == 0) {
+  if (SWIGLU) {
+    if (ready) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN / 2; c0 += 16) {
+        float gv[16], uv[16];
+        tmem_load16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, gv);
+        tmem_load16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c0 + BN / 2), uv);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) gv[i] = (gv[i] / (1.0f + expf(-gv[i]))) * uv[i];
+        const int col0 = b_row0 / 2 + c0;  // column of the activation matrix [tokens, RB / 2]
+        if (ra < RA && col0 < RB / 2) {
+          TO* dst = o + (size_t)ra * ldo + col0;
+          store_row16<TO>(dst, gv, min(16, RB / 2 - col0), (reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+        }
+      }
+    }
+  } else if (ready || n_iter == 0) {
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 16) {
       float v[16];
@@ -373,7 +393,7 @@ int* error_word() {
   return word;
 }
 
-template <int BN, bool SWAP, typename TO>
+template <int BN, bool SWAP, typename TO, bool SWIGLU = false>
 int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, int splits, long long ldo,
               long long split_stride, int stages, cudaStream_t stream) {
   constexpr int STAGE_BYTES = A_BYTES + BN * BK * 2;
@@ -383,7 +403,7 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, i
   stages = std::min(stages, (227 * 1024 - 2048) / STAGE_BYTES);
   if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
   const size_t smem = (size_t)stages * STAGE_BYTES + (2 * stages + 1) * sizeof(uint64_t) + 16 + 1024;
-  auto kernel = gemm_tc_kernel<BN, SWAP, TO>;
+  auto kernel = gemm_tc_kernel<BN, SWAP, TO, SWIGLU>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
@@ -456,6 +476,22 @@ extern "C" int llm_gemm_tc(const void* a, const void* w, void* out, int M, int N
   }
   if (rc != LLM_OK) return rc;
   LLM_CHECK_LAUNCH("gemm_tc");
+  return LLM_OK;
+}
+
+// act[m, c] = silu(g[m, c]) * u[m, c] with g | u = a . w^T, for w [2*FF, K] whose rows are blocks of
+// 128 gate rows followed by the 128 matching up rows (FF a multiple of 128). act: bf16 [M, FF].
+extern "C" int llm_gemm_tc_swiglu(const void* a, const void* w, void* act, int M, int FF, int K, long long lda, long long ldw,
+                                  long long ld_act, cudaStream_t stream) {
+  if (M == 0 || FF == 0) return LLM_OK;
+  LLM_REQUIRE(llm_gemm_tc_supported(a, w, M, 2 * FF, K, lda, ldw), "gemm_tc_swiglu: operands must be 16-byte aligned with K and row strides multiples of 8");
+  LLM_REQUIRE(FF % 128 == 0, "gemm_tc_swiglu: the intermediate size %d must be a multiple of 128", FF);
+  LLM_REQUIRE(error_word() != nullptr, "gemm_tc_swiglu: cannot allocate the error word");
+  CUtensorMap ma, mb;
+  LLM_REQUIRE(tensor_map_for(a, M, K, lda, BM, &ma) && tensor_map_for(w, 2 * FF, K, ldw, 256, &mb), "gemm_tc_swiglu: cuTensorMapEncodeTiled failed");
+  const int rc = launch_tc<256, false, bf16, true>(ma, mb, act, M, 2 * FF, K, 1, ld_act, 0, 4, stream);
+  if (rc != LLM_OK) return rc;
+  LLM_CHECK_LAUNCH("gemm_tc_swiglu");
   return LLM_OK;
 }
 

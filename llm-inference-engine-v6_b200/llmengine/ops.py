@@ -122,15 +122,38 @@ class CudaOps:
                                          _stream()), lib)
         return h
 
-    def silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        """gate_up [n, 2*ff] (gate columns first) -> out [n, ff] = silu(gate)*up."""
+    def silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> torch.Tensor:
+        """gate_up [n, 2*ff] -> out [n, ff] = silu(gate)*up. block 0: gate columns first, then up;
+        block b: blocks of 2b columns, b of gate followed by the b matching ones of up."""
         _need(gate_up, "silu_mul.in"); _need(out, "silu_mul.out", gate_up.dtype)
         lib = self.lib()
         n, ff = out.shape
         assert gate_up.is_contiguous() and out.is_contiguous() and gate_up.shape == (n, 2 * ff)
         self._check(lib.llm_silu_mul(_ptr(gate_up), _ptr(out), c_int(dtype_code(out.dtype)), c_int(n), c_int(ff),
-                                     _stream()), lib)
+                                     c_int(block), _stream()), lib)
         return out
+
+    def gemm_swiglu(self, a: torch.Tensor, w_blocked: torch.Tensor, out: torch.Tensor, ws=None) -> torch.Tensor:
+        """out [m, ff] = silu(gate) * up where gate | up = a @ w_blocked.T and w_blocked [2*ff, k] holds
+        blocks of 128 gate rows followed by the 128 matching up rows. With many tokens in bfloat16
+        the activation is applied in the product's epilogue and the [m, 2*ff] intermediate never
+        exists; otherwise the product runs first (as partial sums when few tokens are in the step)."""
+        _need(a, "gemm_swiglu.a"); _need(w_blocked, "gemm_swiglu.w", a.dtype); _need(out, "gemm_swiglu.out", a.dtype)
+        m, k = a.shape
+        ff = out.shape[1]
+        assert w_blocked.shape == (2 * ff, k) and out.shape[0] == m and out.is_contiguous() and ff % 128 == 0
+        if m > self.SWAP_MAX_TOKENS and self._tc_usable(a, w_blocked):
+            lib = self.lib("tensorcore")
+            self._check(lib.llm_gemm_tc_swiglu(_ptr(a), _ptr(w_blocked), _ptr(out), c_int(m), c_int(ff), c_int(k),
+                                               c_longlong(a.stride(0)), c_longlong(w_blocked.stride(0)),
+                                               c_longlong(out.stride(0)), _stream()), lib)
+            return out
+        assert ws is not None, "gemm_swiglu needs a workspace when it cannot fuse"
+        if m <= self.SWAP_MAX_TOKENS:
+            return self.silu_mul_partials(self.gemm_partials(a, w_blocked, ws, "swiglu.parts"), out, block=128)
+        gate_up = ws.get("swiglu.gate_up", (m, 2 * ff), a.dtype)
+        self.gemm(a, w_blocked, gate_up)
+        return self.silu_mul(gate_up, out, block=128)
 
     # ------------------------------------------------------------------ matrix products
     # A weight-streaming product (few tokens) is bound by memory; measured on B200 it streams fastest
@@ -217,14 +240,15 @@ class CudaOps:
                                             c_int(dtype_code(out.dtype)), c_longlong(out.numel()), _stream()), lib)
         return out
 
-    def silu_mul_partials(self, parts: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        """parts float32 [p, n, 2*ff] (gate | up partial sums) -> out [n, ff] = silu(gate) * up."""
+    def silu_mul_partials(self, parts: torch.Tensor, out: torch.Tensor, block: int = 0) -> torch.Tensor:
+        """parts float32 [p, n, 2*ff] (gate | up partial sums, columns laid out as in silu_mul)
+        -> out [n, ff] = silu(gate) * up."""
         _need(parts, "silu_mul.parts", torch.float32); _need(out, "silu_mul.out")
         n, ff = out.shape
         assert parts.is_contiguous() and out.is_contiguous() and parts.shape[1:] == (n, 2 * ff)
         lib = self.lib()
         self._check(lib.llm_silu_mul_partials(_ptr(parts), c_int(parts.shape[0]), c_longlong(parts.stride(0)), _ptr(out),
-                                              c_int(dtype_code(out.dtype)), c_int(n), c_int(ff), _stream()), lib)
+                                              c_int(dtype_code(out.dtype)), c_int(n), c_int(ff), c_int(block), _stream()), lib)
         return out
 
     def tensor_core_error(self) -> int:

@@ -1,5 +1,8 @@
 """Dense gated feed-forward: down( silu(gate(x)) * up(x) ), no bias (src/engine.cpp:383-412;
-silu as v/(1+exp(-v)), src/kernels.cpp:26-31). gate and up run as one product against [Wg; Wu]."""
+silu as v/(1+exp(-v)), src/kernels.cpp:26-31). gate and up run as one product against their rows
+put together: [Wg; Wu], or, in bfloat16 when the intermediate size is a multiple of 128, blocks of
+128 gate rows followed by the 128 matching up rows, so that one 256-wide accumulator tile of the
+tensor-core product holds both and the activation is applied in its epilogue."""
 from __future__ import annotations
 
 from typing import List
@@ -27,13 +30,20 @@ class GatedMLP(FeedForward):
 
     def load(self, tensors) -> None:
         s = self.spec
-        self.w_gate_up = torch.cat([tensors[s.gate_weight], tensors[s.up_weight]], dim=0).contiguous()
+        g, u = tensors[s.gate_weight], tensors[s.up_weight]
+        self.blocked = g.dtype == torch.bfloat16 and s.intermediate % 128 == 0
+        if self.blocked:
+            self.w_gate_up = torch.stack([g.view(-1, 128, s.hidden), u.view(-1, 128, s.hidden)], dim=1).reshape(2 * s.intermediate, s.hidden).contiguous()
+        else:
+            self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         self.w_down = tensors[s.down_weight]
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         s, ops, n = self.spec, self.env.ops, ctx.n_tokens
         act = ctx.ws.get("mlp.act", (n, s.intermediate), self.env.dtype)
-        if n <= 64:  # few tokens: the products may come as partial sums, added by their consumers
+        if self.blocked:
+            ops.gemm_swiglu(x[:n], self.w_gate_up, act, ctx.ws)
+        elif n <= 64:  # few tokens: the products may come as partial sums, added by their consumers
             ops.silu_mul_partials(ops.gemm_partials(x[:n], self.w_gate_up, ctx.ws, "mlp.gate_up_parts"), act)
         else:
             gate_up = ctx.ws.get("mlp.gate_up", (n, 2 * s.intermediate), self.env.dtype)

@@ -46,10 +46,14 @@ class CpuOps:
         h[:n] += d[:n]
         return h
 
-    def silu_mul(self, gate_up, out):
+    def silu_mul(self, gate_up, out, block=0):
         ff = out.shape[1]
-        g = gate_up[:, :ff].float()
-        u = gate_up[:, ff:].float()
+        if block:
+            gu = gate_up.float().view(gate_up.shape[0], ff // block, 2, block)
+            g, u = gu[:, :, 0].reshape(-1, ff), gu[:, :, 1].reshape(-1, ff)
+        else:
+            g = gate_up[:, :ff].float()
+            u = gate_up[:, ff:].float()
         out.copy_(((g / (1.0 + torch.exp(-g))) * u).to(out.dtype))
         return out
 
@@ -68,8 +72,12 @@ class CpuOps:
         out.copy_(parts.sum(0).to(out.dtype))
         return out
 
-    def silu_mul_partials(self, parts, out):
-        return self.silu_mul(parts.sum(0), out)
+    def silu_mul_partials(self, parts, out, block=0):
+        return self.silu_mul(parts.sum(0), out, block)
+
+    def gemm_swiglu(self, a, w_blocked, out, ws=None):
+        gate_up = (a.float() @ w_blocked.float().t())
+        return self.silu_mul(gate_up, out, 128)
 
     def rope_kv_write(self, qkv, positions, token_seq, block_table, cos, sin, kcache, vcache, n_tokens, nq, nkv, hd, parts=None):
         half = hd // 2

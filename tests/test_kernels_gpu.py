@@ -127,6 +127,22 @@ def test_gemm_tensor_cores(ops, M, N, K):
     assert not ops._tc_usable(a2, w2)
 
 
+@pytest.mark.parametrize("M", [5, 64, 65, 300])
+@pytest.mark.parametrize("FF,K", [(128, 64), (384, 192), (1024, 512)])
+def test_gemm_with_fused_swiglu(ops, M, FF, K):
+    """silu(gate) * up from the product's epilogue (many tokens) and from its partial sums (few)."""
+    from llmengine.engine.context import Workspace
+    a = rnd(M, K, dtype=torch.bfloat16, seed=60)
+    g, u = rnd(FF, K, dtype=torch.bfloat16, seed=61, std=0.1), rnd(FF, K, dtype=torch.bfloat16, seed=62, std=0.1)
+    blocked = torch.stack([g.view(-1, 128, K), u.view(-1, 128, K)], dim=1).reshape(2 * FF, K).contiguous()
+    out = torch.full((M, FF), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_swiglu(a, blocked, out, Workspace(torch.device(DEV)))
+    gf, uf = (a.float() @ g.float().t()).cpu().numpy(), (a.float() @ u.float().t()).cpu().numpy()
+    ref = torch.from_numpy(P.silu(gf) * uf)
+    torch.testing.assert_close(out.float().cpu(), ref, **tol(torch.bfloat16, math.sqrt(K) * 0.1))
+    assert ops.tensor_core_error() == 0
+
+
 def test_silu_mul_partials(ops):
     parts = rnd(3, 5, 2 * 176, seed=54)
     out = torch.empty(5, 176, dtype=torch.bfloat16, device=DEV)
