@@ -270,18 +270,20 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Attn
 
 // Decoding form: every request brings ONE token. A CTA owns (request, key/value head, split of the
 // key range); its 16 rows hold the `group` query heads of that key/value head. The four warps take
-// the split's 64-key tiles in turn (warp w: tiles w, w+4, ...), each fetching its own tile, so a
-// split of 256 keys is four tiles in flight at once and no warp waits in a loop; the warps' partial
-// (max, sum, output) are then merged through shared memory in warp order. Result: a normalised
-// partial per split with its (max, sum), or the final output when there is one split.
+// the split's 32-key tiles in turn (warp w: tiles w, w+4, ...); every warp has its own ring of two
+// tile buffers, so it computes on one tile while the next is on its way, and the first two tiles of
+// every warp are requested before the wait on the previous kernel (keys written by earlier steps
+// do not depend on it). The warps' partial (max, sum, output) are merged through shared memory in
+// warp order. Result: a normalised partial per split with its (max, sum), merged by the CTA that
+// finishes last for its (request, key/value head); or the final output when there is one split.
 template <int HD>
 __global__ void __launch_bounds__(THREADS) paged_attention_decode_kernel(const AttnParams p) {
   constexpr int LD = HD + 8;
   constexpr int KSTEPS = HD / 16, DTILES = HD / 8;
-  constexpr int ROWS = 16;
+  constexpr int ROWS = 16, TK = 32;  // query rows per CTA, keys per tile
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [ROWS][LD]
-  bf16* kv_s = q_s + ROWS * LD;                    // [4 warps][2 (k, v)][N_TILE][LD]
+  bf16* kv_s = q_s + ROWS * LD;                    // [4 warps][2 stages][2 (k, v)][TK][LD]
   dep_launch();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -297,16 +299,20 @@ __global__ void __launch_bounds__(THREADS) paged_attention_decode_kernel(const A
   hi = min(hi, (split + 1) * p.split_keys - 1);
   const int* table = p.block_table + (size_t)seq * p.max_blocks;
   const size_t head_stride = (size_t)p.page_size * HD;
-  bf16* kb = kv_s + (size_t)warp * 2 * N_TILE * LD;
-  bf16* vb = kb + N_TILE * LD;
-  const int kt_first = lo / N_TILE, kt_last = hi / N_TILE;
+  bf16* ring = kv_s + (size_t)warp * 4 * TK * LD;
   const bool any = hi >= lo;
+  const int kt_first = lo / TK, kt_last = hi / TK;
+  const int n_my = (any && kt_first + warp <= kt_last) ? (kt_last - (kt_first + warp)) / 4 + 1 : 0;  // this warp's tiles
 
-  auto fetch_tile = [&](int kt, int newest_excluded) {
-    // rows of keys in [lo, hi]; the row of key `newest_excluded` (if >= 0) is left for later
-    for (int c = lane; c < N_TILE * (HD / 8); c += 32) {
+  auto fetch_tile = [&](int j, int newest_excluded) {
+    // tile j of this warp -> stage j % 2; rows of keys in [lo, hi]; the row of key
+    // `newest_excluded` (if >= 0) is left for later
+    const int kt = kt_first + warp + 4 * j;
+    bf16* kb = ring + (size_t)(j & 1) * 2 * TK * LD;
+    bf16* vb = kb + TK * LD;
+    for (int c = lane; c < TK * (HD / 8); c += 32) {
       const int r = c / (HD / 8), ch = c % (HD / 8);
-      const int key = kt * N_TILE + r;
+      const int key = kt * TK + r;
       if (key == newest_excluded) continue;
       const bool valid = key >= lo && key <= hi;
       size_t off = 0;
@@ -318,19 +324,25 @@ __global__ void __launch_bounds__(THREADS) paged_attention_decode_kernel(const A
       cp_async16(vb + r * LD + ch * 8, p.vcache + off, valid);
     }
   };
-  const int kt0 = kt_first + warp;
-  const bool has_first = any && kt0 <= kt_last;
-  if (has_first) fetch_tile(kt0, pos);
+  if (n_my > 0) fetch_tile(0, pos);
+  cp_async_commit();
+  if (n_my > 1) fetch_tile(1, pos);
   cp_async_commit();
   dep_wait();
-  if (has_first && pos >= lo && pos <= hi && pos / N_TILE == kt0) {  // the newest key, written just before
-    const int r = pos - kt0 * N_TILE;
-    const int page = table[pos / p.page_size];
-    const size_t off = ((size_t)page * p.nkv + kvh) * head_stride + (size_t)(pos % p.page_size) * HD;
-    for (int c = lane; c < 2 * (HD / 8); c += 32) {
-      const int ch = c % (HD / 8);
-      if (c < HD / 8) cp_async16(kb + r * LD + ch * 8, p.kcache + off + ch * 8, true);
-      else cp_async16(vb + r * LD + ch * 8, p.vcache + off + ch * 8, true);
+  if (any && pos >= lo && pos <= hi) {  // the newest key, written just before: only if its tile is already under way
+    const int kt_pos = pos / TK;
+    const int j = (kt_pos - kt_first - warp) / 4;
+    if (kt_pos >= kt_first + warp && (kt_pos - kt_first - warp) % 4 == 0 && j < 2) {
+      bf16* kb = ring + (size_t)(j & 1) * 2 * TK * LD;
+      bf16* vb = kb + TK * LD;
+      const int r = pos - kt_pos * TK;
+      const int page = table[pos / p.page_size];
+      const size_t off = ((size_t)page * p.nkv + kvh) * head_stride + (size_t)(pos % p.page_size) * HD;
+      for (int c = lane; c < 2 * (HD / 8); c += 32) {
+        const int ch = c % (HD / 8);
+        if (c < HD / 8) cp_async16(kb + r * LD + ch * 8, p.kcache + off + ch * 8, true);
+        else cp_async16(vb + r * LD + ch * 8, p.vcache + off + ch * 8, true);
+      }
     }
   }
   for (int c = tid; c < ROWS * (HD / 8); c += THREADS) {  // q rows (zeros beyond the group), in flight with the keys
@@ -352,91 +364,93 @@ __global__ void __launch_bounds__(THREADS) paged_attention_decode_kernel(const A
   float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
   const float sl2 = p.scale * 1.4426950408889634f;
 
-  if (any) {
-    for (int kt = kt0; kt <= kt_last; kt += 4) {
-      if (kt != kt0) {
-        __syncwarp();  // the warp has finished reading its buffers
-        fetch_tile(kt, -1);
-      }
-      cp_async_commit();
-      cp_async_wait<0>();
+  for (int j = 0; j < n_my; ++j) {
+    if (j > 0) {
+      cp_async_wait<1>();  // tile j has landed; tile j + 1 may still be on its way
       __syncwarp();
+    }
+    const int kt = kt_first + warp + 4 * j;
+    const bf16* kb = ring + (size_t)(j & 1) * 2 * TK * LD;
+    const bf16* vb = kb + TK * LD;
 
-      float s[N_TILE / 8][4];
+    float s[TK / 8][4];
 #pragma unroll
-      for (int j = 0; j < N_TILE / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    for (int i = 0; i < TK / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
 #pragma unroll
-      for (int ks = 0; ks < KSTEPS; ++ks) {
+    for (int ks = 0; ks < KSTEPS; ++ks) {
 #pragma unroll
-        for (int j2 = 0; j2 < N_TILE / 16; ++j2) {
-          uint32_t b[4];
-          ldmatrix_x4(b, kb + (j2 * 16 + (lane % 8) + (lane / 16) * 8) * LD + ks * 16 + ((lane / 8) % 2) * 8);
-          mma_bf16(s[2 * j2], qa[ks], b[0], b[1]);
-          mma_bf16(s[2 * j2 + 1], qa[ks], b[2], b[3]);
-        }
-      }
-      const int key0 = kt * N_TILE + 2 * (lane % 4);
-      float mx_a = -INFINITY, mx_b = -INFINITY;
-#pragma unroll
-      for (int j = 0; j < N_TILE / 8; ++j) {
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int key = key0 + j * 8 + e;
-          const bool in = key >= lo && key <= hi;
-          s[j][e] = (in && va_row) ? s[j][e] * sl2 : -INFINITY;
-          s[j][2 + e] = (in && vb_row) ? s[j][2 + e] * sl2 : -INFINITY;
-          mx_a = fmaxf(mx_a, s[j][e]);
-          mx_b = fmaxf(mx_b, s[j][2 + e]);
-        }
-      }
-      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
-      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
-      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
-      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-      const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
-      const float base_a = (mn_a == -INFINITY) ? 0.f : mn_a, base_b = (mn_b == -INFINITY) ? 0.f : mn_b;
-      const float al_a = exp2f(m_a - base_a), al_b = exp2f(m_b - base_b);
-      float sum_a = 0.f, sum_b = 0.f;
-#pragma unroll
-      for (int j = 0; j < N_TILE / 8; ++j) {
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          s[j][e] = exp2f(s[j][e] - base_a);
-          s[j][2 + e] = exp2f(s[j][2 + e] - base_b);
-          sum_a += s[j][e];
-          sum_b += s[j][2 + e];
-        }
-      }
-      sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
-      sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
-      sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
-      sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
-      l_a = l_a * al_a + sum_a;
-      l_b = l_b * al_b + sum_b;
-      m_a = mn_a;
-      m_b = mn_b;
-#pragma unroll
-      for (int d = 0; d < DTILES; ++d) {
-        o_acc[d][0] *= al_a; o_acc[d][1] *= al_a;
-        o_acc[d][2] *= al_b; o_acc[d][3] *= al_b;
-      }
-#pragma unroll
-      for (int kk = 0; kk < N_TILE / 16; ++kk) {
-        uint32_t pa[4];
-        pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-        pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-        pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-        pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-#pragma unroll
-        for (int d2 = 0; d2 < DTILES / 2; ++d2) {
-          uint32_t b[4];
-          ldmatrix_x4_trans(b, vb + (kk * 16 + (lane % 8) + ((lane / 8) % 2) * 8) * LD + d2 * 16 + (lane / 16) * 8);
-          mma_bf16(o_acc[2 * d2], pa, b[0], b[1]);
-          mma_bf16(o_acc[2 * d2 + 1], pa, b[2], b[3]);
-        }
+      for (int j2 = 0; j2 < TK / 16; ++j2) {
+        uint32_t b[4];
+        ldmatrix_x4(b, kb + (j2 * 16 + (lane % 8) + (lane / 16) * 8) * LD + ks * 16 + ((lane / 8) % 2) * 8);
+        mma_bf16(s[2 * j2], qa[ks], b[0], b[1]);
+        mma_bf16(s[2 * j2 + 1], qa[ks], b[2], b[3]);
       }
     }
+    const int key0 = kt * TK + 2 * (lane % 4);
+    float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < TK / 8; ++i) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int key = key0 + i * 8 + e;
+        const bool in = key >= lo && key <= hi;
+        s[i][e] = (in && va_row) ? s[i][e] * sl2 : -INFINITY;
+        s[i][2 + e] = (in && vb_row) ? s[i][2 + e] * sl2 : -INFINITY;
+        mx_a = fmaxf(mx_a, s[i][e]);
+        mx_b = fmaxf(mx_b, s[i][2 + e]);
+      }
+    }
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+    const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+    const float base_a = (mn_a == -INFINITY) ? 0.f : mn_a, base_b = (mn_b == -INFINITY) ? 0.f : mn_b;
+    const float al_a = exp2f(m_a - base_a), al_b = exp2f(m_b - base_b);
+    float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+    for (int i = 0; i < TK / 8; ++i) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        s[i][e] = exp2f(s[i][e] - base_a);
+        s[i][2 + e] = exp2f(s[i][2 + e] - base_b);
+        sum_a += s[i][e];
+        sum_b += s[i][2 + e];
+      }
+    }
+    sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
+    sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+    sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
+    sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+    l_a = l_a * al_a + sum_a;
+    l_b = l_b * al_b + sum_b;
+    m_a = mn_a;
+    m_b = mn_b;
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) {
+      o_acc[d][0] *= al_a; o_acc[d][1] *= al_a;
+      o_acc[d][2] *= al_b; o_acc[d][3] *= al_b;
+    }
+#pragma unroll
+    for (int kk = 0; kk < TK / 16; ++kk) {
+      uint32_t pa[4];
+      pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int d2 = 0; d2 < DTILES / 2; ++d2) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, vb + (kk * 16 + (lane % 8) + ((lane / 8) % 2) * 8) * LD + d2 * 16 + (lane / 16) * 8);
+        mma_bf16(o_acc[2 * d2], pa, b[0], b[1]);
+        mma_bf16(o_acc[2 * d2 + 1], pa, b[2], b[3]);
+      }
+    }
+    __syncwarp();  // the warp has finished reading this stage
+    if (j + 2 < n_my) fetch_tile(j + 2, -1);
+    cp_async_commit();
   }
+  cp_async_wait<0>();
   // ---- merge the four warps (in warp order) through shared memory: [warp][row][HD + 2] floats
   __syncthreads();  // all tiles consumed: the key/value buffers can be reused
   float* mg = reinterpret_cast<float*>(kv_s);

@@ -419,6 +419,10 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, i
 
 }  // namespace
 
+// Tuning knobs of the token-tile form (0 = built-in choice): width of the output tile and ring depth.
+static int g_force_bn = 0, g_force_stages = 0;
+extern "C" void llm_gemm_tc_tune(int bn, int stages) { g_force_bn = bn; g_force_stages = stages; }
+
 // Number of K splits llm_gemm_tc will really use for (K, wanted splits).
 extern "C" int llm_gemm_tc_splits(int K, int splits) {
   const int k_tiles = (K + BK - 1) / BK;
@@ -449,7 +453,9 @@ extern "C" int llm_gemm_tc(const void* a, const void* w, void* out, int M, int N
   CUtensorMap ma, mb;
   int rc = LLM_OK;
   if (!swap) {
-    const int bn = N >= 256 ? 256 : (N > 64 ? 128 : (N > 32 ? 64 : (N > 16 ? 32 : 16)));
+    int bn = N >= 256 ? 256 : (N > 64 ? 128 : (N > 32 ? 64 : (N > 16 ? 32 : 16)));
+    if (g_force_bn) bn = g_force_bn;
+    if (g_force_stages) stages = g_force_stages;
     LLM_REQUIRE(tensor_map_for(a, M, K, lda, BM, &ma) && tensor_map_for(w, N, K, ldw, bn, &mb), "gemm_tc: cuTensorMapEncodeTiled failed");
 #define LLM_TC_CASE(BN_)                                                                                                   \
   rc = (out_dtype == LLM_F32) ? launch_tc<BN_, false, float>(ma, mb, out, M, N, K, 1, ldo, 0, std::min(stages, BN_ == 256 ? 4 : 6), stream) \
