@@ -284,6 +284,7 @@ __global__ void __launch_bounds__(THREADS) paged_attention_decode_kernel(const A
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [ROWS][LD]
   bf16* kv_s = q_s + ROWS * LD;                    // [4 warps][2 stages][2 (k, v)][TK][LD]
+  int* page_s = reinterpret_cast<int*>(kv_s + 16 * TK * LD);  // the split's slice of the block table
   dep_launch();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -303,6 +304,14 @@ __global__ void __launch_bounds__(THREADS) paged_attention_decode_kernel(const A
   const bool any = hi >= lo;
   const int kt_first = lo / TK, kt_last = hi / TK;
   const int n_my = (any && kt_first + warp <= kt_last) ? (kt_last - (kt_first + warp)) / 4 + 1 : 0;  // this warp's tiles
+  // The pages of the split, read once by the whole CTA: a copy that looked its page up in global
+  // memory would wait for that read before it could even be issued, row after row.
+  const int page_lo = lo / p.page_size;
+  if (any) {
+    const int n_pages = hi / p.page_size - page_lo + 1;
+    for (int i = tid; i < n_pages; i += THREADS) page_s[i] = table[page_lo + i];
+  }
+  __syncthreads();
 
   auto fetch_tile = [&](int j, int newest_excluded) {
     // tile j of this warp -> stage j % 2; rows of keys in [lo, hi]; the row of key
@@ -317,7 +326,7 @@ __global__ void __launch_bounds__(THREADS) paged_attention_decode_kernel(const A
       const bool valid = key >= lo && key <= hi;
       size_t off = 0;
       if (valid) {
-        const int page = table[key / p.page_size];
+        const int page = page_s[key / p.page_size - page_lo];
         off = ((size_t)page * p.nkv + kvh) * head_stride + (size_t)(key % p.page_size) * HD + ch * 8;
       }
       cp_async16(kb + r * LD + ch * 8, p.kcache + off, valid);
@@ -336,7 +345,7 @@ __global__ void __launch_bounds__(THREADS) paged_attention_decode_kernel(const A
       bf16* kb = ring + (size_t)(j & 1) * 2 * TK * LD;
       bf16* vb = kb + TK * LD;
       const int r = pos - kt_pos * TK;
-      const int page = table[pos / p.page_size];
+      const int page = page_s[pos / p.page_size - page_lo];
       const size_t off = ((size_t)page * p.nkv + kvh) * head_stride + (size_t)(pos % p.page_size) * HD;
       for (int c = lane; c < 2 * (HD / 8); c += 32) {
         const int ch = c % (HD / 8);
@@ -616,7 +625,9 @@ int launch(const AttnParams& p, int n_seqs, int max_new_tokens, int n_tokens, bo
     return true;
   };
   if (decode) {  // one token per request, group <= 16
-    const size_t smem = (size_t)(16 + 8 * N_TILE) * LD * sizeof(bf16);
+    const int keys_per_cta = p.n_splits > 1 ? p.split_keys : p.max_blocks * p.page_size;
+    const size_t smem = (size_t)(16 + 8 * N_TILE) * LD * sizeof(bf16) + (size_t)(keys_per_cta / p.page_size + 2) * sizeof(int);
+    if (smem > 200 * 1024) return 2;  // an absurdly long split of tiny pages: the caller must split more
     if (!set_attr(paged_attention_decode_kernel<HD>, smem)) return 1;
     launch_kernel(paged_attention_decode_kernel<HD>, dim3(n_seqs, p.nkv, p.n_splits), THREADS, smem, stream, p);
   } else {
@@ -690,6 +701,7 @@ extern "C" int llm_paged_attention_mma(const void* q, long long ld_q, const void
   else if (hd == 32) rc = launch<32>(p, n_seqs, max_new_tokens, n_tokens, split, decode, stream);
   else if (hd == 64) rc = launch<64>(p, n_seqs, max_new_tokens, n_tokens, split, decode, stream);
   else rc = launch<128>(p, n_seqs, max_new_tokens, n_tokens, split, decode, stream);
+  LLM_REQUIRE(rc != 2, "attention_mma: %d keys per split with pages of %d do not fit the block-table copy in shared memory", n_splits > 1 ? split_keys : max_blocks * page_size, page_size);
   LLM_REQUIRE(rc == 0, "attention_mma: cannot raise the shared memory limit");
   LLM_CHECK_LAUNCH("paged_attention_mma");
   return LLM_OK;
