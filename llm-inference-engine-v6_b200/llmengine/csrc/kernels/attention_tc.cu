@@ -1,0 +1,383 @@
+// Causal grouped-query attention of prompt portions on the 5th-generation tensor cores.
+//
+// A CTA owns 128 rows = (query token, query head of the group) pairs that share one key/value
+// head, i.e. 128/group tokens of one request, and walks the request's cached keys in tiles of 128
+// (absolute positions), fetched page by page with TMA through the block table:
+//
+//   S = Q K^T        tcgen05.mma, Q and K in shared memory (128-byte swizzle), S in tensor memory
+//   softmax          thread t owns row t: it reads its 128 scores from tensor memory, masks them by
+//                    its own token's position (and window), keeps the running max and sum in
+//                    float32 and writes P = exp2(S - max) as bfloat16 back to tensor memory
+//   O += P V         tcgen05.mma with P read from tensor memory and V from shared memory (V is
+//                    [key][dim], i.e. the "MN-major" operand form); O stays in tensor memory and is
+//                    rescaled by the owner of each row when its max moves
+//
+// Warps 0-3 are the softmax threads; one thread of a fifth warp issues the TMA loads and the MMAs
+// and runs ahead of them (the next tile's S = Q K^T is queued right behind the current P V), the
+// two sides meeting only at mbarriers; two CTAs per SM fill each other's gaps. Every
+// wait on an mbarrier is bounded (see tc_common.cuh). head_dim 64, page sizes that are multiples
+// of 8 and divide 128, group sizes that divide 128; the caller uses the mma.sync kernel otherwise.
+//
+// Formula: the reference's attention_f32 (src/kernels.cpp:413-474): kv head = q head / group,
+// score = (q . k) * scale applied after the dot, softmax in float32, weighted sum of values.
+#include "tc_common.cuh"
+
+#include <cmath>
+
+namespace {
+
+constexpr int HD = 64;
+constexpr int ROWS = 128, KEYS = 128;
+constexpr int Q_BYTES = ROWS * HD * 2, KV_BYTES = KEYS * HD * 2;
+constexpr int S_COL = 0, P_COL = 128, O_COL = 192, TMEM_COLS_ATT = 256;
+enum : int { ERR_ATT_KV = 11, ERR_ATT_S = 12, ERR_ATT_O = 13 };
+
+struct AttnTcParams {
+  const bf16* q; long long ld_q;
+  const int* seq_start; const int* seq_ntok; const int* seq_qoff; const int* block_table;
+  int max_blocks, nq, nkv, page_size, window;
+  float scale;
+  bf16* out; long long ld_out;
+  int* error_out;
+};
+
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, "
+      "%18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// The registers of tmem_load32 calls may be read only after this.
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, "
+      "%18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+      "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+      "r"(r[31])
+      : "memory");
+}
+
+// 2^x on the special-function unit, one instruction (exp2f adds range handling that is not needed here).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// tcgen05.mma with the A operand in tensor memory.
+__device__ __forceinline__ void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// bf16 x bf16 -> f32, M = 128; b_mn_major: the B operand is stored with N contiguous ([k][n]).
+__host__ __device__ constexpr uint32_t instr_desc_att(int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+constexpr int ATT_THREADS = 160;  // warps 0-3: one softmax thread per row; warp 4: one thread issues TMA and MMA
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 200 registers a thread
+    paged_attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const AttnTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* q_s = smem;                  // [128 rows][128 B], 128-byte swizzle
+  uint8_t* kv_s = smem + Q_BYTES;       // [2 stages][K 16 KB | V 16 KB], rows of 128 B, 128-byte swizzle
+  uint64_t* full = reinterpret_cast<uint64_t*>(kv_s + 4 * KV_BYTES);  // [2] keys and values of a tile have landed
+  uint64_t* s_bar = full + 2;           // the scores of a tile are in tensor memory
+  uint64_t* p_bar = s_bar + 1;          // all 128 rows of P are in tensor memory (128 arrivals)
+  uint64_t* o_bar = p_bar + 1;          // the P V product of a tile is done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* page_s = reinterpret_cast<int*>(tmem_slot + 4);  // the tile range's slice of the block table
+
+  dep_launch();
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int seq = blockIdx.y, kvh = blockIdx.z;
+  const int g = p.nq / p.nkv;
+  const int tq_cap = ROWS / g;
+  // the batch arrays came with the step's host-to-device copy: they may be read before the wait
+  const int ntok = p.seq_ntok[seq];
+  // late query tiles see the most keys: they are scheduled first so that the grid's tail is short
+  const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * tq_cap;
+  if (q0 >= ntok) return;
+  const int n_tq = min(tq_cap, ntok - q0);
+  const int n_rows = n_tq * g;
+  const int tok_base = p.seq_qoff[seq] + q0;
+  const int pos0 = p.seq_start[seq] + q0;
+  const int pos_last = pos0 + n_tq - 1;
+  const int lo = (p.window > 0) ? max(0, pos0 - p.window + 1) : 0;
+  const int hi = pos_last;
+  const int kt_first = lo / KEYS, kt_last = hi / KEYS;
+  const int n_tiles = kt_last - kt_first + 1;
+  const int* table = p.block_table + (size_t)seq * p.max_blocks;
+  const int pages_per_tile = KEYS / p.page_size;
+
+  if (tid == 0) {
+    mbar_init(&full[0], 1);
+    mbar_init(&full[1], 1);
+    mbar_init(s_bar, 1);
+    mbar_init(p_bar, ROWS);
+    mbar_init(o_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS_ATT) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // The pages of this CTA's key range, read once by all threads: the thread that issues the copies
+  // would otherwise wait for a global read before every single one of them.
+  const int page_lo = (kt_first * KEYS) / p.page_size;
+  {
+    const int n_pages_all = hi / p.page_size - page_lo + 1;
+    for (int i = tid; i < n_pages_all; i += ATT_THREADS) page_s[i] = table[page_lo + i];
+  }
+  // key/value stages start as zeros: rows that no copy fills (beyond the request's last page) are
+  // multiplied by probabilities of exactly zero and must not hold NaN patterns
+  for (int i = tid; i < 4 * KV_BYTES / 16; i += ATT_THREADS) reinterpret_cast<uint4*>(kv_s)[i] = make_uint4(0, 0, 0, 0);
+  dep_wait();
+  // ---- Q rows -> shared memory in the swizzled K-major layout (16-byte chunk c of row r at c ^ (r % 8))
+  if (tid < ROWS) {
+    const int r = tid;
+    uint4 vals[8];
+    if (r < n_rows) {
+      const int tq = r / g, hg = r % g;
+      const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)(tok_base + tq) * p.ld_q + (size_t)(kvh * g + hg) * HD);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) vals[c] = src[c];
+    } else {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) vals[c] = make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(q_s + r * 128 + ((c ^ (r & 7)) << 4)) = vals[c];
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to TMA / MMA
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
+
+  if (warp == 4) {
+    if (tid == 4 * 32) {
+      // ------------------------------------------------------------ the thread that issues TMA and MMA
+      auto issue_tile = [&](int i) {  // keys and values of tile i -> stage i % 2; pages beyond the newest key are not fetched
+        const int first_key = (kt_first + i) * KEYS;
+        uint8_t* ks = kv_s + (size_t)(i & 1) * 2 * KV_BYTES;
+        uint8_t* vs = ks + KV_BYTES;
+        int n_pages = 0;
+        for (int pg = 0; pg < pages_per_tile; ++pg)
+          if (first_key + pg * p.page_size <= hi) n_pages = pg + 1;
+        mbar_expect_tx(&full[i & 1], (uint32_t)(n_pages * p.page_size * HD * 2 * 2));
+        for (int pg = 0; pg < n_pages; ++pg) {
+          const int page = page_s[(first_key + pg * p.page_size) / p.page_size - page_lo];
+          const int row = (page * p.nkv + kvh) * p.page_size;
+          tma_load_2d(ks + (size_t)pg * p.page_size * 128, &map_k, 0, row, &full[i & 1]);
+          tma_load_2d(vs + (size_t)pg * p.page_size * 128, &map_v, 0, row, &full[i & 1]);
+        }
+      };
+      auto issue_scores = [&](int i) {  // S = Q K^T of tile i
+        const uint64_t dq = smem_desc_sw128(smem_u32(q_s));
+        const uint64_t dk = smem_desc_sw128(smem_u32(kv_s + (size_t)(i & 1) * 2 * KV_BYTES));
+        constexpr uint32_t idesc_s = instr_desc_att(KEYS, false);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) mma_f16(tmem_base + S_COL, dq + (uint64_t)(2 * k), dk + (uint64_t)(2 * k), idesc_s, k > 0 ? 1u : 0u);
+        mma_commit(s_bar);
+      };
+      issue_tile(0);
+      if (n_tiles > 1) issue_tile(1);
+      ok = mbar_wait(&full[0], 0, abort_flag, p.error_out, ERR_ATT_KV);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        issue_scores(0);
+      }
+      for (int i = 0; i < n_tiles && ok; ++i) {
+        // P of tile i is in tensor memory (so its scores have been read: the S columns are free again)
+        ok = mbar_wait(p_bar, (uint32_t)i & 1u, abort_flag, p.error_out, ERR_ATT_S);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t dv = smem_desc_sw128(smem_u32(kv_s + (size_t)(i & 1) * 2 * KV_BYTES + KV_BYTES));
+        constexpr uint32_t idesc_o = instr_desc_att(HD, true);
+#pragma unroll
+        for (int k = 0; k < KEYS / 16; ++k)  // 16 keys = 16 rows of 128 B further down the V stage; 8 columns further along P
+          mma_f16_ts(tmem_base + O_COL, tmem_base + P_COL + (uint32_t)(k * 8), dv + (uint64_t)(k * (16 * 128 >> 4)), idesc_o,
+                     (i > 0 || k > 0) ? 1u : 0u);
+        mma_commit(o_bar);
+        if (i + 1 < n_tiles) {  // the next tile's scores go to the tensor pipe right behind this product
+          ok = mbar_wait(&full[(i + 1) & 1], (uint32_t)((i + 1) >> 1) & 1u, abort_flag, p.error_out, ERR_ATT_KV);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_scores(i + 1);
+        }
+        if (i + 2 < n_tiles) {  // stage i % 2 is free once the product of tile i is done
+          ok = mbar_wait(o_bar, (uint32_t)i & 1u, abort_flag, p.error_out, ERR_ATT_O);
+          if (ok) issue_tile(i + 2);
+        }
+      }
+    }
+  } else {
+    // -------------------------------------------------------------- softmax: thread t owns row t
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const int tq_row = tid / g;
+    const int pos_r = (tid < n_rows) ? pos0 + tq_row : -1;  // -1: padding row, sees no key
+    const int lo_r = (p.window > 0) ? pos_r - p.window + 1 : 0;
+    const float sl2 = p.scale * 1.4426950408889634f;
+    float m_run = -INFINITY, l_run = 0.f;
+    for (int i = 0; i < n_tiles; ++i) {
+      ok = mbar_wait(s_bar, (uint32_t)i & 1u, abort_flag, p.error_out, ERR_ATT_S);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      float s[KEYS];
+#pragma unroll
+      for (int c = 0; c < KEYS / 32; ++c) tmem_load32(tmem_base + lane_base + S_COL + c * 32, s + c * 32);
+      tmem_load_wait();  // four loads in flight, one wait
+      const int key0 = (kt_first + i) * KEYS;
+      const bool full_tile = (key0 + KEYS - 1 <= pos_r) && (key0 >= lo_r);
+      float mx = -INFINITY;
+      if (full_tile) {
+#pragma unroll
+        for (int j = 0; j < KEYS; ++j) {
+          s[j] *= sl2;
+          mx = fmaxf(mx, s[j]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < KEYS; ++j) {
+          const int key = key0 + j;
+          s[j] = (key <= pos_r && key >= lo_r) ? s[j] * sl2 : -INFINITY;
+          mx = fmaxf(mx, s[j]);
+        }
+      }
+      // The running max is only moved when it would grow by more than 2^8: until then the row keeps
+      // its older, smaller reference (probabilities up to 256 instead of 1, harmless in float32 and
+      // bfloat16) and its sum and output need no rescaling. Sum and output always share one reference.
+      const bool move = (mx > m_run + 8.0f) || (m_run == -INFINITY && mx > -INFINITY);
+      const float m_new = move ? mx : m_run;
+      const float base = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = move ? fast_exp2(m_run - base) : 1.0f;  // 0 when the row had seen no key yet
+      float sum = 0.f;
+      uint32_t packed[KEYS / 2];
+#pragma unroll
+      for (int j = 0; j < KEYS; j += 2) {
+        const float p0 = fast_exp2(s[j] - base), p1 = fast_exp2(s[j + 1] - base);
+        sum += p0 + p1;
+        __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
+        packed[j / 2] = *reinterpret_cast<uint32_t*>(&t);
+      }
+      l_run = l_run * alpha + sum;
+      m_run = m_new;
+      tmem_store32(tmem_base + lane_base + P_COL, packed);
+      tmem_store32(tmem_base + lane_base + P_COL + 32, packed + 32);
+      if (i > 0 && __any_sync(0xffffffffu, move)) {  // rescale the warp's rows of O (the previous product is done: s_bar came after it)
+        float o[HD];
+        tmem_load32(tmem_base + lane_base + O_COL, o);
+        tmem_load32(tmem_base + lane_base + O_COL + 32, o + 32);
+        tmem_load_wait();
+        uint32_t ou[HD];
+#pragma unroll
+        for (int d = 0; d < HD; ++d) ou[d] = __float_as_uint(o[d] * alpha);
+        tmem_store32(tmem_base + lane_base + O_COL, ou);
+        tmem_store32(tmem_base + lane_base + O_COL + 32, ou + 32);
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(p_bar);
+    }
+    // ---- the rows of O, normalised
+    if (ok && n_tiles > 0) ok = mbar_wait(o_bar, (uint32_t)(n_tiles - 1) & 1u, abort_flag, p.error_out, ERR_ATT_O);
+    ok = __all_sync(0xffffffffu, ok);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {  // every thread of a warp takes part in the tensor-memory loads; only real rows are stored
+      float o[HD];
+      tmem_load32(tmem_base + lane_base + O_COL, o);
+      tmem_load32(tmem_base + lane_base + O_COL + 32, o + 32);
+      tmem_load_wait();
+      if (tid < n_rows) {
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        const int tq = tid / g, hg = tid % g;
+        uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(tok_base + tq) * p.ld_out + (size_t)(kvh * g + hg) * HD);
+#pragma unroll
+        for (int c = 0; c < HD / 8; ++c) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 t = __floats2bfloat162_rn(o[c * 8 + 2 * e] * inv, o[c * 8 + 2 * e + 1] * inv);
+            w[e] = *reinterpret_cast<uint32_t*>(&t);
+          }
+          dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS_ATT) : "memory");
+}
+
+}  // namespace
+
+// Whether the tcgen05 attention takes this geometry (else the caller uses the mma.sync kernel).
+extern "C" int llm_attention_tc_supported(int nq, int nkv, int hd, int page_size, long long ld_q, long long ld_out) {
+  if (nkv <= 0 || nq % nkv) return 0;
+  const int g = nq / nkv;
+  return hd == HD && g <= ROWS && ROWS % g == 0 && page_size % 8 == 0 && KEYS % page_size == 0 && (ld_q % 8) == 0 && (ld_out % 8) == 0 &&
+         encode_fn() != nullptr;
+}
+
+// q: rows of [nq*64] bf16; caches [pages, nkv, page_size, 64] bf16 (n_cache_pages pages each);
+// seq_* and block_table as in the step's batch; out [n_tokens, nq*64] bf16.
+extern "C" int llm_paged_attention_tc(const void* q, long long ld_q, const void* kcache, const void* vcache, long long n_cache_pages,
+                                      const int* seq_start, const int* seq_ntok, const int* seq_qoff, const int* block_table,
+                                      int max_blocks, void* out, long long ld_out, int n_seqs, int max_new_tokens, int nq, int nkv,
+                                      int hd, int page_size, float scale, int window, cudaStream_t stream) {
+  if (n_seqs == 0 || max_new_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(llm_attention_tc_supported(nq, nkv, hd, page_size, ld_q, ld_out), "attention_tc: geometry not supported (nq=%d nkv=%d hd=%d page=%d)", nq, nkv, hd, page_size);
+  auto al = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
+  LLM_REQUIRE(al(q) && al(kcache) && al(vcache) && al(out), "attention_tc: q, the caches and out must be 16-byte aligned");
+  LLM_REQUIRE(max_blocks > 0 && window >= 0 && n_seqs <= 65535 && nkv <= 65535, "attention_tc: bad sizes");
+  LLM_REQUIRE(error_word() != nullptr, "attention_tc: cannot allocate the error word");
+  CUtensorMap mk, mv;
+  const long long rows = n_cache_pages * nkv * page_size;
+  LLM_REQUIRE(tensor_map_for(kcache, rows, HD, HD, page_size, &mk) && tensor_map_for(vcache, rows, HD, HD, page_size, &mv),
+              "attention_tc: cuTensorMapEncodeTiled failed");
+  AttnTcParams p;
+  p.q = (const bf16*)q; p.ld_q = ld_q; p.seq_start = seq_start; p.seq_ntok = seq_ntok; p.seq_qoff = seq_qoff; p.block_table = block_table;
+  p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.scale = scale;
+  p.out = (bf16*)out; p.ld_out = ld_out; p.error_out = error_word();
+  LLM_REQUIRE(max_blocks <= 4096, "attention_tc: block tables wider than 4096 pages are not supported");
+  const size_t smem = Q_BYTES + 4 * KV_BYTES + 4 * sizeof(uint64_t) + 16 + (size_t)max_blocks * sizeof(int) + 1024;
+  static size_t attr_smem = 0;
+  if (smem > attr_smem) {
+    LLM_REQUIRE(cudaFuncSetAttribute(paged_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess,
+                "attention_tc: cannot raise the shared memory limit");
+    attr_smem = smem;
+  }
+  const int g = nq / nkv, tq_cap = ROWS / g;
+  dim3 grid((max_new_tokens + tq_cap - 1) / tq_cap, n_seqs, nkv);
+  launch_kernel(paged_attention_tc_kernel, grid, ATT_THREADS, smem, stream, mk, mv, p);
+  LLM_CHECK_LAUNCH("paged_attention_tc");
+  return LLM_OK;
+}

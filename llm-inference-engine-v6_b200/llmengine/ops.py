@@ -55,6 +55,7 @@ class CudaOps:
         self._libs = {}
         self.launches = 0  # kernels launched through this object (a counter for measurements)
         self.tensor_cores = True  # bfloat16 products on tcgen05 where the operands allow it
+        self.tcgen05_attention = True  # prompt portions: attention on tcgen05 where the geometry allows it
 
     # ------------------------------------------------------------------ loading
     def lib(self, name: str = "core"):
@@ -293,6 +294,7 @@ class CudaOps:
     # decoding: the key range is cut at absolute multiples of `split_keys` (a multiple of 64) into as
     # many splits as still fit the GPU in ONE wave of CTAs (three 76 KB CTAs per SM at head size 64)
     ATTENTION_TARGET_CTAS = 444
+    TC_ATTENTION_MIN_TOKENS = 32  # longest portion of the step from which the tcgen05 attention kernel is used
 
     def paged_attention(self, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, batch,
                         block_table: torch.Tensor, out: torch.Tensor, nq: int, nkv: int, hd: int, scale: float,
@@ -309,6 +311,17 @@ class CudaOps:
         n_tokens, page = batch.n_tokens, kcache.shape[2]
         if q.dtype == torch.bfloat16 and self.tensor_cores:
             lib = self.lib("tensorcore")
+            if (self.tcgen05_attention and batch.max_new_tokens >= self.TC_ATTENTION_MIN_TOKENS and
+                    lib.llm_attention_tc_supported(c_int(nq), c_int(nkv), c_int(hd), c_int(page), c_longlong(q.stride(0)),
+                                                   c_longlong(out.stride(0)))):
+                # prompt portions: tcgen05 kernel (128 rows per CTA, scores and output in tensor memory)
+                self._check(lib.llm_paged_attention_tc(
+                    _ptr(q), c_longlong(q.stride(0)), _ptr(kcache), _ptr(vcache), c_longlong(kcache.shape[0]),
+                    _ptr(batch.seq_start), _ptr(batch.seq_ntok), _ptr(batch.seq_qoff), _ptr(block_table),
+                    c_int(block_table.shape[1]), _ptr(out), c_longlong(out.stride(0)), c_int(batch.n_seqs),
+                    c_int(batch.max_new_tokens), c_int(nq), c_int(nkv), c_int(hd), c_int(page), c_float(scale), c_int(window),
+                    _stream()), lib)
+                return out
             if lib.llm_attention_mma_supported(c_int(nq), c_int(nkv), c_int(hd), c_longlong(q.stride(0)), c_longlong(out.stride(0))):
                 n_splits, split_keys, scratch, counters = 1, 256, None, None
                 if batch.max_new_tokens == 1 and batch.n_tokens == batch.n_seqs and batch.max_seq_len > 256:

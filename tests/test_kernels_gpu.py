@@ -240,9 +240,32 @@ def test_paged_attention(ops, dt, nq, nkv, hd, page, window):
             torch.testing.assert_close(out[i].float().cpu(), ref, **tol(dt, 2))
 
 
+@pytest.mark.parametrize("nq,nkv,window", [(32, 8, 0), (8, 2, 0), (4, 4, 0), (16, 1, 0), (8, 2, 150)])
+def test_paged_attention_tcgen05(ops, nq, nkv, window):
+    """The tcgen05 kernel for prompt portions (head size 64, pages of 16): portions that start in the
+    middle of a page and of a 128-key tile, span several tiles, stand beside single tokens."""
+    hd, page, dt = 64, 16, torch.bfloat16
+    seq_lens = [300, 1, 129, 700, 128]
+    kc, vc, table, dense = _paged_setup(dt, nkv, hd, page, seq_lens, sum((L + page - 1) // page for L in seq_lens) + 3, seed=9)
+    scale = 1.0 / math.sqrt(hd)
+    from llmengine.ops import KernelError
+    for b in (Batch([(0, 300), (0, 1), (0, 129), (0, 50), (0, 128)]), Batch([(251, 49), (0, 1), (100, 29), (310, 390), (127, 1)])):
+        assert b.max_new_tokens >= ops.TC_ATTENTION_MIN_TOKENS
+        q = rnd(b.n_tokens, nq * hd, dtype=dt, seed=23)
+        out = torch.full((b.n_tokens, nq * hd), float("nan"), dtype=dt, device=DEV)
+        ops.paged_attention(q, kc, vc, b, table, out, nq, nkv, hd, scale, window)
+        assert ops.tensor_core_error() == 0
+        rows = list(range(0, b.n_tokens, 7)) + [b.n_tokens - 1]
+        for i in rows:
+            s_, p_ = b.tokens[i]
+            ref = _attention_ref(q[i].cpu().view(nq, hd), dense[s_][0], dense[s_][1], p_, nq, nkv, hd, scale, window)
+            torch.testing.assert_close(out[i].float().cpu(), ref, **tol(dt, 2))
+        assert not torch.isnan(out.float()).any()
+
+
 @pytest.mark.parametrize("dt", DTYPES)
-@pytest.mark.parametrize("special", [0, 15, 16, 31, 32, 63, 64, 255, 256, 499])
-@pytest.mark.parametrize("n_new", [1, 3])
+@pytest.mark.parametrize("special", [0, 15, 16, 31, 32, 63, 64, 127, 128, 255, 256, 499])
+@pytest.mark.parametrize("n_new", [1, 3, 40])
 def test_attention_finds_one_far_key_among_hundreds(ops, dt, special, n_new):
     """Random values hide a skipped key (its weight is ~1/500). Here one key is made to match the
     query, so that the output must be that key's value: a key lost at a page's edge, at a tile's or
