@@ -264,3 +264,73 @@ def test_layer_order_is_data(tmp_path):
     first = eng.run_step([(9, ids[:11], range(11))]).clone()  # the logits tensor is scratch of the next step
     second = eng.run_step([(9, ids[11:], range(8))], end=[9])
     np.testing.assert_allclose(torch.cat([first, second]).cpu().numpy(), ref, atol=2e-4, rtol=0)
+
+
+def test_window_layers_share_the_engine_with_full_layers(tmp_path):
+    """A model whose first layer reads a window of the last 9 keys and whose second reads all of
+    them: two cache groups with their own pages; the window group gives pages back while a request
+    is still running, and they are used again by the next one."""
+    from dataclasses import replace
+    from llmengine.config.registry import Architecture, register_architecture
+    from llmengine.config.llama import LlamaConfig
+    from llmengine.models.llama import describe_llama
+    W = 9
+
+    def describe(cfg):
+        spec = describe_llama(cfg)
+        layers = list(spec.layers)
+        layers[0] = replace(layers[0], mixer=replace(layers[0].mixer, window=W))
+        return replace(spec, architecture="WindowedModel", layers=tuple(layers))
+
+    register_architecture(Architecture("WindowedModel", LlamaConfig.from_dict, describe,
+                                       lambda c: dict(c.to_dict(), architectures=["WindowedModel"])), replace=True)
+    cfg = dict(TINY_A, architectures=["WindowedModel"])
+    T, hd, nq, nkv = 41, 16, 4, 2
+    for dtype, wdt, tol in (("fp32", torch.float32, 2e-4), ("bf16", torch.bfloat16, 6e-2)):
+        d = str(tmp_path / f"windowed_{dtype}")
+        llmengine.write_random_model(d, cfg, seed=8, dtype=wdt, std=0.05)
+        pc, w = P.read_model(d)
+        ids = random_ids(T, 256, 12)
+        cos, sin = P.rope_tables(P.llama3_inv_freq(hd, pc["rope_theta"], False, 1, 1, 1, 0), T, hd)
+        h = P.embed(w["model.embed_tokens.weight"], ids)
+        for l in range(2):
+            p = f"model.layers.{l}."
+            x = P.rmsnorm(h, w[p + "input_layernorm.weight"], pc["rms_norm_eps"])
+            q = P.apply_rope(P.linear(x, w[p + "self_attn.q_proj.weight"]).reshape(T, nq, hd), cos, sin)
+            k = P.apply_rope(P.linear(x, w[p + "self_attn.k_proj.weight"]).reshape(T, nkv, hd), cos, sin)
+            v = P.linear(x, w[p + "self_attn.v_proj.weight"]).reshape(T, nkv, hd)
+            if l == 0:  # the plain implementation has no window: restrict the keys query by query
+                a = np.stack([_window_row(q[t], k[max(0, t - W + 1):t + 1], v[max(0, t - W + 1):t + 1], nq, nkv, hd) for t in range(T)])
+            else:
+                a = P.causal_gqa_attention(q, k, v)
+            h = h + P.linear(a, w[p + "self_attn.o_proj.weight"])
+            x = P.rmsnorm(h, w[p + "post_attention_layernorm.weight"], pc["rms_norm_eps"])
+            h = h + P.swiglu_mlp(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+        ref = P.linear(P.rmsnorm(h, w["model.norm.weight"], pc["rms_norm_eps"]), w["lm_head.weight"])
+        eng = llmengine.Engine(d, dtype, block_size=4, num_blocks=12, max_concurrent=2)  # 48 tokens of pages per group
+        eng.configure_cache()
+        assert eng.cm.num_groups == 2 and sorted(eng.cm.window(g) for g in range(2)) == [0, W]
+        gw = [g for g in range(2) if eng.cm.window(g) == W][0]
+        got, pos = [], 0
+        for n in (6, 2, 13, 1, 1, 9, 9):
+            got.append(eng.run_step([(1, ids[pos:pos + n], range(n))]).clone())
+            pos += n
+            held = sum(pg >= 0 for pg in eng.cm.block_table(1, gw))
+            assert held <= (W + 3) // 4 + 1  # the window group never holds more than the window needs
+        assert sum(pg >= 0 for pg in eng.cm.block_table(1, 1 - gw)) == (T + 3) // 4
+        np.testing.assert_allclose(torch.cat(got).float().cpu().numpy(), ref, atol=tol, rtol=0)
+        # a second request of 41 tokens fits beside the first only because window pages came back
+        eng.run_step([], end=[1])
+        again = eng.run_step([(2, ids, range(T))], end=[2])
+        np.testing.assert_allclose(again.float().cpu().numpy(), ref, atol=tol, rtol=0)
+        eng.cm.check()
+        assert eng.cm.free_pages(0) == 12 and eng.cm.free_pages(1) == 12
+
+
+def _window_row(q, k, v, nq, nkv, hd):
+    out = np.zeros((nq, hd), dtype=np.float32)
+    for hh in range(nq):
+        s = (k[:, hh // (nq // nkv)] @ q[hh]) / np.sqrt(np.float32(hd))
+        pr = np.exp(s - s.max())
+        out[hh] = (pr / pr.sum()) @ v[:, hh // (nq // nkv)]
+    return out.reshape(-1)
