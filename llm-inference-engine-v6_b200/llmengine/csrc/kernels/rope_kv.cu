@@ -102,6 +102,62 @@ __global__ void __launch_bounds__(128)
   }
 }
 
+// bfloat16 rows without partial sums, 16 bytes at a time: an item is 8 neighbouring rotation pairs
+// of a q or k head (8 elements of the first half with their 8 partners of the second half), or 8
+// neighbouring elements of v. Needs head_dim % 16 == 0 and 16-byte aligned rows.
+__global__ void __launch_bounds__(128)
+    rope_kv_write_vec_kernel(bf16* __restrict__ qkv, long long ld_qkv, const int* __restrict__ positions,
+                             const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_blocks,
+                             const float* __restrict__ cos_t, const float* __restrict__ sin_t, bf16* __restrict__ kcache,
+                             bf16* __restrict__ vcache, int nq, int nkv, int hd, int page_size) {
+  dep_launch();
+  dep_wait();
+  const int t = blockIdx.x;
+  const int half = hd >> 1, groups = half >> 3;  // groups of 8 pairs per head
+  const int n_rot = (nq + nkv) * groups, n_v = vcache ? nkv * (hd >> 3) : 0;
+  const int item = blockIdx.y * blockDim.x + threadIdx.x;
+  if (item >= n_rot + n_v) return;
+  const int pos = positions[t];
+  bf16* row = qkv + (size_t)t * ld_qkv;
+  size_t cache_base = 0;
+  if (kcache) {
+    const int page = block_table[(size_t)token_seq[t] * max_blocks + pos / page_size];
+    cache_base = ((size_t)page * nkv * page_size + (pos % page_size)) * hd;
+  }
+  const size_t head_stride = (size_t)page_size * hd;
+  if (item >= n_rot) {  // 8 elements of v, copied as they are
+    const int e = (item - n_rot) * 8, vh = e / hd, vi = e - vh * hd;
+    *reinterpret_cast<uint4*>(vcache + cache_base + (size_t)vh * head_stride + vi) =
+        *reinterpret_cast<const uint4*>(row + (size_t)(nq + nkv) * hd + e);
+    return;
+  }
+  const int head = item / groups, i0 = (item - head * groups) * 8;
+  bf16* x = row + (size_t)head * hd;
+  union { uint4 u; __nv_bfloat162 h[4]; } a, b;
+  a.u = *reinterpret_cast<const uint4*>(x + i0);
+  b.u = *reinterpret_cast<const uint4*>(x + i0 + half);
+  if (cos_t) {
+    const float4* c4 = reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + i0);
+    const float4* s4 = reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + i0);
+    float c[8], sn[8];
+    *reinterpret_cast<float4*>(c) = c4[0];
+    *reinterpret_cast<float4*>(c + 4) = c4[1];
+    *reinterpret_cast<float4*>(sn) = s4[0];
+    *reinterpret_cast<float4*>(sn + 4) = s4[1];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 av = __bfloat1622float2(a.h[j]), bv = __bfloat1622float2(b.h[j]);
+      const float ra0 = av.x * c[2 * j] - bv.x * sn[2 * j], rb0 = bv.x * c[2 * j] + av.x * sn[2 * j];
+      const float ra1 = av.y * c[2 * j + 1] - bv.y * sn[2 * j + 1], rb1 = bv.y * c[2 * j + 1] + av.y * sn[2 * j + 1];
+      a.h[j] = __floats2bfloat162_rn(ra0, ra1);
+      b.h[j] = __floats2bfloat162_rn(rb0, rb1);
+    }
+  }
+  bf16* dst = (head < nq || !kcache) ? x : kcache + cache_base + (size_t)(head - nq) * head_stride;
+  *reinterpret_cast<uint4*>(dst + i0) = a.u;
+  *reinterpret_cast<uint4*>(dst + i0 + half) = b.u;
+}
+
 // cos_t/sin_t may be null (no rotation); kcache/vcache may be null (a layer that reads another
 // layer's cache writes nothing, and k is then rotated in place in qkv).
 extern "C" int llm_rope_kv_write(void* qkv, long long ld_qkv, int dtype, const float* parts, int n_parts,
@@ -116,6 +172,16 @@ extern "C" int llm_rope_kv_write(void* qkv, long long ld_qkv, int dtype, const f
   LLM_REQUIRE((kcache == nullptr) == (vcache == nullptr), "rope_kv_write: k and v caches go together");
   LLM_REQUIRE(!parts || (n_parts >= 1 && kcache), "rope_kv_write: partial sums need n_parts >= 1 and a cache to write to");
   const int threads = 128;
+  auto al = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
+  if (dtype == LLM_BF16 && !parts && hd % 16 == 0 && ld_qkv % 8 == 0 && al(qkv) && al(kcache) && al(vcache) && al(cos_t) && al(sin_t)) {
+    const int vitems = (nq + nkv) * (hd / 16) + (vcache ? nkv * (hd / 8) : 0);
+    const dim3 vgrid(n_tokens, ceil_div(vitems, threads));
+    LLM_REQUIRE(vgrid.y <= 65535, "rope_kv_write: too many heads");
+    launch_kernel(rope_kv_write_vec_kernel, vgrid, threads, 0, stream, (bf16*)qkv, ld_qkv, positions, token_seq, block_table,
+                  max_blocks, cos_t, sin_t, (bf16*)kcache, (bf16*)vcache, nq, nkv, hd, page_size);
+    LLM_CHECK_LAUNCH("rope_kv_write");
+    return LLM_OK;
+  }
   const int items = (nq + nkv) * (hd / 2) + (vcache ? nkv * (hd / 2) : 0);
   const dim3 grid(n_tokens, ceil_div(items, threads));
   LLM_REQUIRE(grid.y <= 65535, "rope_kv_write: too many heads");
