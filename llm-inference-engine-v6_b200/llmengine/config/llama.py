@@ -92,6 +92,13 @@ class LlamaConfig:
                 raise ConfigError(f"config.json: '{key}' must be a positive integer, got {v!r}")
             return v
 
+        # options the reference never reads, so their meaning is fixed in its code (and in ours):
+        # refuse a checkpoint that needs something else instead of running it wrongly
+        if j.get("hidden_act", "silu") not in ("silu", "swish"):
+            raise ConfigError(f"hidden_act '{j.get('hidden_act')}' is not supported (the feed-forward is SiLU-gated)")
+        for key in ("attention_bias", "mlp_bias"):
+            if j.get(key):
+                raise ConfigError(f"config.json: '{key}' is set, but linear layers with bias are not supported")
         archs = j.get("architectures") or ["LlamaForCausalLM"]
         hidden = need("hidden_size")
         heads = need("num_attention_heads")

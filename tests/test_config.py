@@ -50,7 +50,8 @@ def test_llama3_scaling_both_layouts_and_eos_merge():
     ({"num_key_value_heads": 3}, "multiple"), ({"head_dim": 15}, "even"), ({"hidden_size": 0}, "hidden_size"),
     ({"vocab_size": None}, "vocab_size"), ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0}}, "yarn"),
     ({"rope_scaling": {"rope_type": "llama3", "factor": 8.0}}, "original_max_position_embeddings"),
-    ({"rms_norm_eps": 0.0}, "eps"),
+    ({"rms_norm_eps": 0.0}, "eps"), ({"hidden_act": "gelu"}, "hidden_act"), ({"attention_bias": True}, "attention_bias"),
+    ({"mlp_bias": True}, "mlp_bias"),
 ])
 def test_config_errors(patch, word):
     with pytest.raises(ConfigError, match=word):

@@ -12,14 +12,15 @@ from tiny import (TINY, make_model_dir, random_ids, round64, run_trace, trace_mi
 
 pytestmark = pytest.mark.gpu
 
-LENS = {"a": [5, 64, 33, 97, 128], "b": [2, 23, 64, 150, 255, 201]}  # short ones first: four are live at once
+LENS = {"a": [5, 64, 33, 97, 128], "b": [2, 23, 64, 150, 255, 201],  # short ones first: four are live at once
+        "c": [3, 40, 64, 130, 299], "d": [7, 50, 64, 200, 511, 300]}
 # float32: the engine's own arithmetic is float32 throughout; the plain implementation differs by
 # summation order only. bfloat16: weights are the same bf16 values on both sides; the difference is
 # the rounding of activations to bf16 between kernels.
 TOL = {"float32": 2e-4, "bfloat16": 6e-2}
 
 
-@pytest.fixture(scope="module", params=[("a", "float32"), ("a", "bfloat16"), ("b", "float32"), ("b", "bfloat16")],
+@pytest.fixture(scope="module", params=[(n, d) for n in ("a", "b", "c", "d") for d in ("float32", "bfloat16")],
                 ids=lambda p: f"{p[0]}-{p[1]}")
 def replayed(request, tmp_path_factory):
     name, dtype = request.param

@@ -1,4 +1,4 @@
-"""Shared helpers of the tests: two tiny Llama configurations that differ in every size and option,
+"""Shared helpers of the tests: tiny Llama configurations that differ in every size and option,
 model folders with random weights in a temporary place, and builders of replay traces.
 """
 from __future__ import annotations
@@ -27,7 +27,19 @@ TINY_B = dict(architectures=["LlamaForCausalLM"], hidden_size=192, intermediate_
               max_position_embeddings=256, rms_norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=True,
               rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
                                 original_max_position_embeddings=64))
-TINY = {"a": (TINY_A, 4), "b": (TINY_B, 16)}  # name -> (config.json, page size)
+# C: sizes that fit nothing: multi-head (5:5), head 48 (so heads * head_dim != hidden), hidden 120,
+#    FF 100 (not a multiple of 8: the tensor-core product refuses it), vocab 1001, one layer, large eps.
+TINY_C = dict(architectures=["LlamaForCausalLM"], hidden_size=120, intermediate_size=100, num_hidden_layers=1,
+              num_attention_heads=5, num_key_value_heads=5, head_dim=48, vocab_size=1001,
+              max_position_embeddings=300, rms_norm_eps=1e-3, rope_theta=1000000.0, tie_word_embeddings=False,
+              hidden_act="silu", attention_bias=False, mlp_bias=False, rope_scaling=None, torch_dtype="bfloat16")
+# D: the shapes the tensor-core kernels are made for: head 64, GQA 8:2, pages of 16, FF a multiple of 128.
+TINY_D = dict(architectures=["LlamaForCausalLM"], hidden_size=256, intermediate_size=384, num_hidden_layers=2,
+              num_attention_heads=8, num_key_value_heads=2, head_dim=64, vocab_size=2000,
+              max_position_embeddings=512, rms_norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=True,
+              rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                original_max_position_embeddings=128))
+TINY = {"a": (TINY_A, 4), "b": (TINY_B, 16), "c": (TINY_C, 16), "d": (TINY_D, 16)}  # name -> (config.json, page size)
 
 # Weights are wider than a trained model's (std 0.05) so that logits are well apart and a wrong
 # key, page or position shows as a large error.
