@@ -1,0 +1,474 @@
+// Decoding attention over the paged cache: every request of the step brings ONE token.
+//
+// A CTA owns (request, key/value head, split of the key range); its 16 rows hold the `group` query
+// heads that share the key/value head, so a key or value is fetched once for all of them. Keys and
+// values arrive by TMA: one producer thread walks the split in tiles of 32 keys (absolute
+// positions), looks the pages up in a copy of the block-table slice in shared memory and issues
+// one box per page into a ring of stages with 128-byte swizzle; the four consumer warps take the
+// tiles in turn (warp w: tiles w, w+4, ...) and never compute an address in global memory. Tiles
+// that hold only keys of earlier steps are requested before the wait on the previous kernel; the
+// tile that holds the token's own key (written just before this kernel) after it. Pages that the
+// table does not hold (beyond the request's last page, or given back behind a window) are read from
+// the pool's null page, so every tile is complete; their scores are masked by position.
+//
+// Scores (bf16 mma.sync, float32 accumulators), the running (max, sum) softmax in log2 units and
+// the output sums are float32 registers. The four warps' partials are merged in warp order, the
+// splits' partials in index order by the CTA that finishes last for its (request, key/value head):
+// a token's result does not depend on the batch or on page numbers.
+//
+// Formula: the reference's attention_f32 (src/kernels.cpp:413-474).
+#include "tc_common.cuh"
+#include "mma_common.cuh"
+
+#include <cmath>
+
+namespace {
+
+constexpr int DEC_THREADS = 160;  // warps 0-3 compute, warp 4 lane 0 issues the copies
+constexpr int DEC_CONSUMERS = 128;
+constexpr int TK = 32;            // keys per tile
+constexpr int ROWS = 16;          // query rows (heads of the group; zeros beyond)
+enum : int { ERR_DEC_PRODUCER = 21, ERR_DEC_CONSUMER = 22, ERR_DEC_DRAIN = 23 };
+
+struct DecParams {
+  const bf16* q; long long ld_q;
+  const int* seq_start; const int* seq_qoff; const int* block_table;
+  int max_blocks, nq, nkv, page_size, page_shift, window, null_page;  // page_shift: log2(page_size), -1 if no power of two
+  float scale;
+  bf16* out; long long ld_out;
+  float* part_o; float* part_ml; int split_keys, n_splits; long long part_stride_tokens;
+  int* done_count;
+  int* error;
+};
+
+template <int HD>
+struct DecLayout {
+  static constexpr int HALVES = HD / 64;               // 64-element (128-byte) column blocks of a row
+  static constexpr int TILE_BYTES = TK * HD * 2;       // one of K or V
+  static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  static constexpr int STAGES = HD == 64 ? 8 : 5;      // 64 KB / 80 KB of ring
+  static constexpr int Q_LD = HD + 8;
+};
+
+// Byte offset of (row, 16-byte chunk) inside a [TK][64] tile written by TMA with 128-byte swizzle.
+__device__ __forceinline__ uint32_t sw128(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
+
+template <int HD>
+__global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                                 const __grid_constant__ CUtensorMap map_v,
+                                                                                 const DecParams p) {
+  using L = DecLayout<HD>;
+  constexpr int KSTEPS = HD / 16, DTILES = HD / 8, NS = L::STAGES;
+  extern __shared__ uint8_t smem_dyn[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  uint8_t* ring = base;                                                     // [NS][K tile | V tile]
+  bf16* q_s = reinterpret_cast<bf16*>(ring + (size_t)NS * L::STAGE_BYTES);  // [ROWS][Q_LD]
+  uint64_t* full = reinterpret_cast<uint64_t*>(q_s + ROWS * L::Q_LD);       // [NS]
+  uint64_t* empty = full + NS;                                              // [NS]
+  int* flags = reinterpret_cast<int*>(empty + NS);                          // [0] abort, [1] tiles issued, [2] is_last
+  int* page_s = flags + 4;                                                  // the split's slice of the block table
+  volatile int* abort_flag = flags;
+
+  dep_launch();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int g = p.nq / p.nkv;
+  // The batch arrays came with the step's host-to-device copy and every key before the token's own
+  // position was written by an earlier step: both may be read before the dependency wait.
+  const int pos = p.seq_start[seq];
+  const int tok = p.seq_qoff[seq];
+  int lo = (p.window > 0) ? max(0, pos - p.window + 1) : 0;
+  int hi = pos;
+  lo = max(lo, split * p.split_keys);
+  hi = min(hi, (split + 1) * p.split_keys - 1);
+  const bool any = hi >= lo;
+  const int kt_first = lo / TK;
+  const int n_tiles = any ? hi / TK - kt_first + 1 : 0;
+  const int page_first = kt_first * TK / p.page_size;  // page of the first tile's first key
+
+  if (tid == 0) {
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    flags[0] = 0;
+    flags[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (any) {
+    const int* table = p.block_table + (size_t)seq * p.max_blocks;
+    const int n_pages = ((kt_first + n_tiles) * TK - 1) / p.page_size - page_first + 1;
+    for (int i = tid; i < n_pages; i += DEC_THREADS) {
+      const int idx = page_first + i;
+      const int page = idx < p.max_blocks ? table[idx] : -1;
+      page_s[i] = page >= 0 ? page : p.null_page;
+    }
+  }
+  __syncthreads();
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ producer
+    // Lane b issues box b of every tile (a box = the tile's keys of one page); lane 0 also waits for
+    // the stage and announces the bytes. Boxes per tile: 32 / page_size for small pages, else 1.
+    const int rows_per_box = min(p.page_size, TK);
+    const int boxes = TK / rows_per_box;
+    bool waited = false, ok = true;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int stage = t % NS;
+      if (t >= NS) {
+        if (lane == 0) ok = mbar_wait(&empty[stage], ((t / NS) - 1) & 1, abort_flag, p.error, ERR_DEC_PRODUCER);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+      }
+      const int key0 = (kt_first + t) * TK;
+      if (!waited && key0 + TK > pos) {  // the tile of the token's own key, written by the kernel before this one
+        dep_wait();
+        waited = true;
+      }
+      if (lane == 0) mbar_expect_tx(&full[stage], L::STAGE_BYTES);
+      __syncwarp();
+      if (lane < boxes) {
+        const int key = key0 + lane * rows_per_box;
+        int page_idx, in_page;
+        if (p.page_shift >= 0) {
+          page_idx = key >> p.page_shift;
+          in_page = key & (p.page_size - 1);
+        } else {
+          page_idx = key / p.page_size;
+          in_page = key - page_idx * p.page_size;
+        }
+        const int row = (page_s[page_idx - page_first] * p.nkv + kvh) * p.page_size + in_page;
+        uint8_t* kb = ring + (size_t)stage * L::STAGE_BYTES + lane * rows_per_box * 128;
+        uint8_t* vb = kb + L::TILE_BYTES;
+#pragma unroll
+        for (int h = 0; h < L::HALVES; ++h) {
+          tma_load_2d(kb + h * (TK * 128), &map_k, h * 64, row, &full[stage]);
+          tma_load_2d(vb + h * (TK * 128), &map_v, h * 64, row, &full[stage]);
+        }
+      }
+      if (lane == 0) flags[1] = t + 1;
+    }
+  } else {
+    // ------------------------------------------------------------------ consumers
+    dep_wait();  // q comes from the kernel before this one
+    for (int c = tid; c < ROWS * (HD / 8); c += DEC_CONSUMERS) {
+      const int r = c / (HD / 8), ch = c % (HD / 8);
+      cp_async16(q_s + r * L::Q_LD + ch * 8, p.q + (size_t)tok * p.ld_q + (size_t)(kvh * g + min(r, g - 1)) * HD + ch * 8, r < g);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    asm volatile("bar.sync 1, %0;" ::"n"(DEC_CONSUMERS) : "memory");
+    uint32_t qa[KSTEPS][4];
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) ldmatrix_x4(qa[ks], q_s + (lane % 16) * L::Q_LD + ks * 16 + (lane / 16) * 8);
+    const int row_a = lane / 4, row_b = row_a + 8;
+    const bool va_row = row_a < g, vb_row = row_b < g;
+
+    float o_acc[DTILES][4];
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) o_acc[d][0] = o_acc[d][1] = o_acc[d][2] = o_acc[d][3] = 0.f;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    const float sl2 = p.scale * 1.4426950408889634f;
+
+    for (int t = warp; t < n_tiles; t += 4) {
+      const int stage = t % NS;
+      if (!mbar_wait(&full[stage], (t / NS) & 1, abort_flag, p.error, ERR_DEC_CONSUMER)) break;
+      const uint32_t kb = smem_u32(ring + (size_t)stage * L::STAGE_BYTES);
+      const uint32_t vb = kb + L::TILE_BYTES;
+
+      float s[TK / 8][4];
+#pragma unroll
+      for (int i = 0; i < TK / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+        for (int j2 = 0; j2 < TK / 16; ++j2) {
+          uint32_t b[4];
+          const int row = j2 * 16 + (lane % 8) + (lane / 16) * 8;
+          const int chunk = (ks % 4) * 2 + ((lane / 8) % 2);
+          ldmatrix_x4_addr(b, kb + (ks / 4) * (TK * 128) + sw128(row, chunk));
+          mma_bf16(s[2 * j2], qa[ks], b[0], b[1]);
+          mma_bf16(s[2 * j2 + 1], qa[ks], b[2], b[3]);
+        }
+      }
+      const int tile_key0 = (kt_first + t) * TK;
+      const int key0 = tile_key0 + 2 * (lane % 4);
+      float mx_a = -INFINITY, mx_b = -INFINITY;
+      if (tile_key0 >= lo && tile_key0 + TK - 1 <= hi) {  // every key of the tile counts: only the rows are masked
+#pragma unroll
+        for (int i = 0; i < TK / 8; ++i) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            s[i][e] = va_row ? s[i][e] * sl2 : -INFINITY;
+            s[i][2 + e] = vb_row ? s[i][2 + e] * sl2 : -INFINITY;
+            mx_a = fmaxf(mx_a, s[i][e]);
+            mx_b = fmaxf(mx_b, s[i][2 + e]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < TK / 8; ++i) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int key = key0 + i * 8 + e;
+            const bool in = key >= lo && key <= hi;
+            s[i][e] = (in && va_row) ? s[i][e] * sl2 : -INFINITY;
+            s[i][2 + e] = (in && vb_row) ? s[i][2 + e] * sl2 : -INFINITY;
+            mx_a = fmaxf(mx_a, s[i][e]);
+            mx_b = fmaxf(mx_b, s[i][2 + e]);
+          }
+        }
+      }
+      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+      const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+      const float base_a = (mn_a == -INFINITY) ? 0.f : mn_a, base_b = (mn_b == -INFINITY) ? 0.f : mn_b;
+      const float al_a = exp2f(m_a - base_a), al_b = exp2f(m_b - base_b);
+      float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+      for (int i = 0; i < TK / 8; ++i) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          s[i][e] = exp2f(s[i][e] - base_a);
+          s[i][2 + e] = exp2f(s[i][2 + e] - base_b);
+          sum_a += s[i][e];
+          sum_b += s[i][2 + e];
+        }
+      }
+      sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
+      sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+      sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
+      sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+      l_a = l_a * al_a + sum_a;
+      l_b = l_b * al_b + sum_b;
+      m_a = mn_a;
+      m_b = mn_b;
+#pragma unroll
+      for (int d = 0; d < DTILES; ++d) {
+        o_acc[d][0] *= al_a; o_acc[d][1] *= al_a;
+        o_acc[d][2] *= al_b; o_acc[d][3] *= al_b;
+      }
+#pragma unroll
+      for (int kk = 0; kk < TK / 16; ++kk) {
+        uint32_t pa[4];
+        pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int d2 = 0; d2 < DTILES / 2; ++d2) {
+          uint32_t b[4];
+          const int row = kk * 16 + (lane % 8) + ((lane / 8) % 2) * 8;
+          const int chunk = d2 * 2 + lane / 16;  // 16-byte chunk of the row over all halves
+          ldmatrix_x4_trans_addr(b, vb + (chunk / 8) * (TK * 128) + sw128(row, chunk % 8));
+          mma_bf16(o_acc[2 * d2], pa, b[0], b[1]);
+          mma_bf16(o_acc[2 * d2 + 1], pa, b[2], b[3]);
+        }
+      }
+      __syncwarp();  // the whole warp has read the stage
+      if (lane == 0) mbar_arrive(&empty[stage]);
+    }
+    // hand the warp's partial to the merge below (after every copy of the ring has landed and been read)
+    asm volatile("bar.sync 1, %0;" ::"n"(DEC_CONSUMERS) : "memory");
+    if (!*abort_flag) {
+      float* mg = reinterpret_cast<float*>(ring);  // [warp][row][HD + 2]
+      constexpr int MLD = HD + 2;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int row = half ? row_b : row_a;
+        float* dst = mg + ((size_t)warp * ROWS + row) * MLD;
+#pragma unroll
+        for (int d = 0; d < DTILES; ++d) {
+          dst[d * 8 + 2 * (lane % 4)] = o_acc[d][2 * half];
+          dst[d * 8 + 2 * (lane % 4) + 1] = o_acc[d][2 * half + 1];
+        }
+        if ((lane % 4) == 0) {
+          dst[HD] = half ? m_b : m_a;
+          dst[HD + 1] = half ? l_b : l_a;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (*abort_flag) {
+    // a wait gave up: let the copies that were issued land (bounded) before the CTA leaves
+    if (tid == 0) {
+      const int issued = flags[1];
+      for (int t = max(0, issued - NS); t < issued; ++t) {
+        const long long t0 = clock64();
+        while (!mbar_try_wait(&full[t % NS], (t / NS) & 1)) {
+          if (clock64() - t0 > WAIT_CYCLES) {
+            atomicCAS(p.error, 0, (int)ERR_DEC_DRAIN);
+            break;
+          }
+        }
+      }
+    }
+    return;
+  }
+  // ---- merge the four warps (in warp order)
+  const float* mg = reinterpret_cast<const float*>(ring);
+  constexpr int MLD = HD + 2;
+  for (int e = tid; e < g * HD; e += DEC_THREADS) {
+    const int row = e / HD, d = e - row * HD;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mx = fmaxf(mx, mg[((size_t)w * ROWS + row) * MLD + HD]);
+    float acc = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float* src = mg + ((size_t)w * ROWS + row) * MLD;
+      const float m = src[HD];
+      if (m == -INFINITY) continue;
+      const float sc = exp2f(m - mx);
+      den += src[HD + 1] * sc;
+      acc = fmaf(sc, src[d], acc);  // src[d] is the warp's unnormalised sum of p * v
+    }
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    const int head = kvh * g + row;
+    if (p.n_splits == 1) {
+      p.out[(size_t)tok * p.ld_out + (size_t)head * HD + d] = __float2bfloat16_rn(acc * inv);
+    } else {
+      const size_t slot = ((size_t)split * p.part_stride_tokens + tok) * p.nq + head;
+      p.part_o[slot * HD + d] = acc * inv;
+      if (d == 0) {
+        p.part_ml[slot * 2] = mx;
+        p.part_ml[slot * 2 + 1] = den;
+      }
+    }
+  }
+  if (p.n_splits == 1) return;
+  // ---- the CTA that finishes last for this (request, key/value head) merges the splits, in index
+  // order whichever CTA that is
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&p.done_count[seq * p.nkv + kvh], 1);
+    flags[2] = (old == p.n_splits - 1);
+    if (flags[2]) p.done_count[seq * p.nkv + kvh] = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!flags[2]) return;
+  __threadfence();
+  const size_t split_stride = (size_t)p.part_stride_tokens * p.nq;
+  float* m_s = reinterpret_cast<float*>(ring);  // [g][n_splits]
+  float* l_s = m_s + ROWS * p.n_splits;         // [g][n_splits]
+  __syncthreads();
+  for (int idx = tid; idx < g * p.n_splits; idx += DEC_THREADS) {
+    const int row = idx / p.n_splits, sp = idx - row * p.n_splits;
+    const size_t slot = (size_t)tok * p.nq + kvh * g + row + sp * split_stride;
+    m_s[row * p.n_splits + sp] = __ldcg(&p.part_ml[slot * 2]);
+    l_s[row * p.n_splits + sp] = __ldcg(&p.part_ml[slot * 2 + 1]);
+  }
+  __syncthreads();
+  for (int e = tid; e < g * HD; e += DEC_THREADS) {
+    const int row = e / HD, d = e - row * HD;
+    const size_t slot0 = (size_t)tok * p.nq + kvh * g + row;
+    float mx = -INFINITY;
+    for (int sp = 0; sp < p.n_splits; ++sp) mx = fmaxf(mx, m_s[row * p.n_splits + sp]);
+    float acc = 0.f, den = 0.f;
+    for (int s0 = 0; s0 < p.n_splits; s0 += 8) {  // eight splits' loads in flight; added in index order
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        v[u] = (s0 + u < p.n_splits) ? __ldcg(&p.part_o[(slot0 + (s0 + u) * split_stride) * HD + d]) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (s0 + u < p.n_splits) {
+          const float m = m_s[row * p.n_splits + s0 + u];
+          if (m != -INFINITY) {
+            const float w = l_s[row * p.n_splits + s0 + u] * exp2f(m - mx);
+            den += w;
+            acc = fmaf(w, v[u], acc);
+          }
+        }
+      }
+    }
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    p.out[(size_t)tok * p.ld_out + (size_t)(kvh * g + row) * HD + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+template <int HD>
+size_t decode_smem_bytes(int keys_per_cta, int page_size) {
+  using L = DecLayout<HD>;
+  return 1024 + (size_t)L::STAGES * L::STAGE_BYTES + (size_t)ROWS * L::Q_LD * 2 + 2 * L::STAGES * 8 + 16 +
+         (size_t)((keys_per_cta + 2 * TK) / page_size + 4) * sizeof(int);
+}
+
+template <int HD>
+int launch_decode(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int n_seqs, cudaStream_t stream) {
+  const int keys_per_cta = p.n_splits > 1 ? p.split_keys : p.max_blocks * p.page_size;
+  const size_t smem = decode_smem_bytes<HD>(keys_per_cta, p.page_size);
+  if (smem > 200 * 1024) return 2;
+  static bool attr_set = false;  // the largest size asked for so far
+  static size_t attr_bytes = 0;
+  if (!attr_set || smem > attr_bytes) {
+    if (cudaFuncSetAttribute(paged_attention_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return 1;
+    attr_set = true;
+    attr_bytes = smem;
+  }
+  launch_kernel(paged_attention_decode_tma_kernel<HD>, dim3(n_seqs, p.nkv, p.n_splits), DEC_THREADS, smem, stream, mk, mv, p);
+  return 0;
+}
+
+}  // namespace
+
+// Whether the TMA decoding kernel takes this geometry: head size 64 or 128, a group of at most 16
+// query heads, pages of 8, 16 or a multiple of 32 keys (a tile of 32 keys is whole pages or lies
+// inside one).
+extern "C" int llm_attention_decode_supported(int nq, int nkv, int hd, int page_size, long long ld_q, long long ld_out) {
+  if (nkv <= 0 || nq % nkv || nq / nkv > ROWS) return 0;
+  if (hd != 64 && hd != 128) return 0;
+  if (!(page_size == 8 || page_size == 16 || (page_size > 0 && page_size % TK == 0))) return 0;
+  return (ld_q % 8) == 0 && (ld_out % 2) == 0 && encode_fn() != nullptr;
+}
+
+// One token per request. q: rows of [nq*hd] bf16 (ld_q elements apart); caches
+// [n_cache_pages, nkv, page_size, hd] bf16, whose LAST page is the null page (finite values, never a
+// request's); seq_start[i]: the token's position; seq_qoff[i]: its row; out [n_seqs, nq*hd] bf16.
+// n_splits > 1: keys are cut every split_keys (a multiple of 64) positions, scratch holds
+// llm_attention_mma_scratch_floats floats and done_count n_seqs * nkv zeroed ints (left at zero).
+extern "C" int llm_paged_attention_decode(const void* q, long long ld_q, const void* kcache, const void* vcache,
+                                          long long n_cache_pages, const int* seq_start, const int* seq_qoff,
+                                          const int* block_table, int max_blocks, void* out, long long ld_out, int n_seqs,
+                                          int nq, int nkv, int hd, int page_size, float scale, int window, int n_splits,
+                                          int split_keys, float* scratch, int* done_count, cudaStream_t stream) {
+  if (n_seqs == 0) return LLM_OK;
+  LLM_REQUIRE(llm_attention_decode_supported(nq, nkv, hd, page_size, ld_q, ld_out),
+              "attention_decode: geometry not supported (nq=%d nkv=%d hd=%d page=%d)", nq, nkv, hd, page_size);
+  LLM_REQUIRE(max_blocks > 0 && window >= 0 && n_cache_pages >= 1, "attention_decode: bad sizes");
+  LLM_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15u) == 0 && (reinterpret_cast<uintptr_t>(kcache) & 15u) == 0 &&
+              (reinterpret_cast<uintptr_t>(vcache) & 15u) == 0, "attention_decode: q and the caches must be 16-byte aligned");
+  LLM_REQUIRE(n_splits >= 1 && n_splits <= 128 &&
+              (n_splits == 1 || (split_keys > 0 && split_keys % 64 == 0 && scratch != nullptr && done_count != nullptr)),
+              "attention_decode: splits need split_keys %% 64 == 0, scratch and counters");
+  LLM_REQUIRE((long long)n_seqs <= 65535 * 32768LL && nkv <= 65535, "attention_decode: batch too large for the grid");
+  const long long rows = n_cache_pages * nkv * page_size;
+  LLM_REQUIRE(rows < (1LL << 31), "attention_decode: the cache has too many rows for a tensor map coordinate");
+  CUtensorMap mk, mv;
+  const int box_rows = page_size < TK ? page_size : TK;
+  LLM_REQUIRE(tensor_map_for(kcache, rows, hd, hd, box_rows, &mk) && tensor_map_for(vcache, rows, hd, hd, box_rows, &mv),
+              "attention_decode: cannot encode the tensor maps of the cache");
+  DecParams p;
+  p.q = (const bf16*)q; p.ld_q = ld_q; p.seq_start = seq_start; p.seq_qoff = seq_qoff; p.block_table = block_table;
+  p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window;
+  p.page_shift = -1;
+  for (int sft = 0; sft < 30; ++sft)
+    if ((1 << sft) == page_size) p.page_shift = sft;
+  p.null_page = (int)(n_cache_pages - 1); p.scale = scale; p.out = (bf16*)out; p.ld_out = ld_out;
+  p.n_splits = n_splits; p.split_keys = n_splits > 1 ? split_keys : max_blocks * page_size + TK;
+  p.part_stride_tokens = n_seqs;
+  p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)n_splits * n_seqs * nq * hd : nullptr;
+  p.done_count = done_count;
+  p.error = error_word();
+  const int rc = hd == 64 ? launch_decode<64>(mk, mv, p, n_seqs, stream) : launch_decode<128>(mk, mv, p, n_seqs, stream);
+  LLM_REQUIRE(rc != 2, "attention_decode: %d keys per split with pages of %d do not fit the block-table copy in shared memory",
+              n_splits > 1 ? split_keys : max_blocks * page_size, page_size);
+  LLM_REQUIRE(rc == 0, "attention_decode: cannot raise the shared memory limit");
+  LLM_CHECK_LAUNCH("paged_attention_decode");
+  return LLM_OK;
+}

@@ -93,10 +93,6 @@ __host__ __device__ constexpr uint32_t instr_desc_att(int n, bool b_mn_major) {
 
 constexpr int ATT_THREADS = 160;  // warps 0-3: one softmax thread per row; warp 4: one thread issues TMA and MMA
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
 __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 200 registers a thread
     paged_attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const AttnTcParams p) {
   extern __shared__ uint8_t smem_raw[];

@@ -3,11 +3,19 @@
     python -m llmengine.kernel_bench gemm --m 8 --n 16384 --k 2048 [--reps 20]
     python -m llmengine.kernel_bench attention --batch 8 --context 2048 --new 1
     python -m llmengine.kernel_bench attention --batch 1 --context 0 --new 2048
+    python -m llmengine.kernel_bench step --batch 8 --context 2048          (timeline of one decode step)
+    python -m llmengine.kernel_bench step --batch 1 --context 2048 --prefill (timeline of one prompt step)
 
-Each run launches ONE kind of kernel a few times on inputs that are larger than the L2 cache
+Each of the first three launches ONE kind of kernel a few times on inputs that are larger than the L2 cache
 (several copies of the operands are used in turn) and prints the mean device time per launch with
 the bytes and flops it implies. The sizes default to the Llama 3.2 1B geometry. Meant to be run
 alone or under a profiler with a small --reps.
+
+`step` runs the whole engine on a model folder with random weights (Llama 3.2 1B sizes unless
+flags say otherwise), records the device timestamps of every kernel of one scheduler step with
+torch.profiler and prints, for each kind of kernel, its launches, its mean duration and its
+"critical" time: how much later it ends than everything launched before it, which is its share of
+the step once the overlap through programmatic dependent launch is taken out.
 """
 from __future__ import annotations
 
@@ -20,15 +28,24 @@ import torch
 
 
 def _time(fn, reps: int) -> float:
-    for _ in range(3):
-        fn(0)
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for i in range(reps):
-        fn(i)
-    b.record()
-    torch.cuda.synchronize()
+    """Mean device time of fn(i), i < reps, launched back to back from one CUDA graph so that the
+    host's launch cost (tens of microseconds from Python) is not what is measured."""
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            fn(0)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(reps):
+                fn(i)
+        graph.replay()
+        stream.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        graph.replay()
+        b.record(stream)
+        stream.synchronize()
     return a.elapsed_time(b) * 1e-3 / reps
 
 
@@ -67,7 +84,8 @@ def run_attention(args) -> dict:
     n_pages = B * blocks
     caches = [(torch.randn(n_pages + 1, nkv, page, hd, device=dev).bfloat16(), torch.randn(n_pages + 1, nkv, page, hd, device=dev).bfloat16())
               for _ in range(layers)]
-    table = torch.randperm(n_pages, device=dev).to(torch.int32).view(B, blocks).contiguous()
+    order = torch.arange(n_pages, device=dev) if args.sequential else torch.randperm(n_pages, device=dev)
+    table = order.to(torch.int32).view(B, blocks).contiguous()  # a request's pages: in a row, or anywhere in the pool
     b = _Batch()
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
     b.seq_start, b.seq_ntok = i32([ctx] * B), i32([new] * B)
@@ -87,6 +105,62 @@ def run_attention(args) -> dict:
             "head_dim": hd, "us": round(sec * 1e6, 2), "tflops": round(flops / sec / 1e12, 2), "kv_gbs": round(nbytes / sec / 1e9, 1)}
 
 
+def run_step_timeline(args) -> dict:
+    import collections
+    import tempfile
+    from torch.profiler import ProfilerActivity, profile
+    import llmengine
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=args.hidden, intermediate_size=args.ffn,
+               num_hidden_layers=args.layers, num_attention_heads=args.heads, num_key_value_heads=args.kv_heads,
+               head_dim=args.head_dim, vocab_size=args.vocab, max_position_embeddings=max(4096, args.context + 512),
+               rms_norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=True)
+    B, ctx = args.batch, args.context
+    gen = torch.Generator().manual_seed(1)
+    prompts = torch.randint(0, args.vocab, (B, ctx), generator=gen).tolist()
+    with tempfile.TemporaryDirectory() as tmp:
+        llmengine.write_random_model(tmp, cfg, seed=0, dtype=torch.bfloat16)
+        eng = llmengine.Engine(tmp, "bf16", block_size=args.page, num_blocks=B * ((ctx + 256) // args.page + 2),
+                               max_concurrent=B)
+        eng._ensure_model()  # the folder is read here; it may go afterwards
+    sch = llmengine.ContinuousBatchScheduler(eng, None, max_concurrent=B, max_prefill_tokens_per_step=ctx)
+
+    if args.prefill:  # one round of prompts as warm-up, then the first step of the next round
+        for p in prompts:
+            sch.enqueue(p, 1)
+        sch.run_until_idle()
+        sch.clear_results()
+        for p in prompts:
+            sch.enqueue(p, 1)
+    else:
+        for p in prompts:
+            sch.enqueue(p, 200)
+        while sch.core.num_running < B:
+            sch.step()
+        for _ in range(5):
+            sch.step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        sch.step()
+        torch.cuda.synchronize()
+    ev = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and "memcpy" not in e.name.lower()
+                 and "memset" not in e.name.lower()), key=lambda e: e.time_range.start)
+    t0, prev_end = ev[0].time_range.start, ev[0].time_range.start
+    agg = collections.OrderedDict()
+    for e in ev:
+        end = e.time_range.end
+        name = e.name.split("(")[0].split("::")[-1].split("<")[0]
+        a = agg.setdefault(name, [0, 0.0, 0.0])
+        a[0] += 1
+        a[1] += max(end - prev_end, 0)
+        a[2] += end - e.time_range.start
+        prev_end = max(prev_end, end)
+    rows = [{"kernel": k, "launches": v[0], "critical_us": round(v[1], 1), "mean_duration_us": round(v[2] / v[0], 2)}
+            for k, v in sorted(agg.items(), key=lambda kv: -kv[1][1])]
+    assert eng.ops.tensor_core_error() == 0
+    return {"step": "prefill" if args.prefill else "decode", "batch": B, "context": ctx, "layers": args.layers,
+            "step_us": round(prev_end - t0, 1), "kernels": rows}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m llmengine.kernel_bench", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -98,7 +172,22 @@ def main(argv=None) -> int:
     a.add_argument("--batch", type=int, default=8); a.add_argument("--context", type=int, default=2048); a.add_argument("--new", type=int, default=1)
     a.add_argument("--heads", type=int, default=32); a.add_argument("--kv-heads", type=int, default=8); a.add_argument("--head-dim", type=int, default=64)
     a.add_argument("--page", type=int, default=16); a.add_argument("--reps", type=int, default=20)
+    a.add_argument("--sequential", action="store_true", help="each request's pages lie in a row (default: scattered over the pool)")
+    t = sub.add_parser("step")
+    t.add_argument("--batch", type=int, default=8); t.add_argument("--context", type=int, default=2048)
+    t.add_argument("--prefill", action="store_true")
+    t.add_argument("--hidden", type=int, default=2048); t.add_argument("--ffn", type=int, default=8192)
+    t.add_argument("--layers", type=int, default=16); t.add_argument("--heads", type=int, default=32)
+    t.add_argument("--kv-heads", type=int, default=8); t.add_argument("--head-dim", type=int, default=64)
+    t.add_argument("--vocab", type=int, default=128256); t.add_argument("--page", type=int, default=16)
     args = ap.parse_args(argv)
+    if args.what == "step":
+        r = run_step_timeline(args)
+        kernels = r.pop("kernels")
+        print(json.dumps(r))
+        for k in kernels:
+            print(f"{k['critical_us']:9.1f} us critical  x{k['launches']:4d}  mean {k['mean_duration_us']:8.2f} us  {k['kernel']}")
+        return 0
     print(json.dumps(run_gemm(args) if args.what == "gemm" else run_attention(args)))
     return 0
 

@@ -56,6 +56,7 @@ class CudaOps:
         self.launches = 0  # kernels launched through this object (a counter for measurements)
         self.tensor_cores = True  # bfloat16 products on tcgen05 where the operands allow it
         self.tcgen05_attention = True  # prompt portions: attention on tcgen05 where the geometry allows it
+        self.tma_decode_attention = True  # single decoded tokens: keys and values by TMA where the geometry allows it
 
     # ------------------------------------------------------------------ loading
     def lib(self, name: str = "core"):
@@ -322,9 +323,12 @@ class CudaOps:
                     c_int(batch.max_new_tokens), c_int(nq), c_int(nkv), c_int(hd), c_int(page), c_float(scale), c_int(window),
                     _stream()), lib)
                 return out
-            if lib.llm_attention_mma_supported(c_int(nq), c_int(nkv), c_int(hd), c_longlong(q.stride(0)), c_longlong(out.stride(0))):
+            decode_only = batch.max_new_tokens == 1 and batch.n_tokens == batch.n_seqs
+            use_tma = decode_only and self.tma_decode_attention and lib.llm_attention_decode_supported(
+                c_int(nq), c_int(nkv), c_int(hd), c_int(page), c_longlong(q.stride(0)), c_longlong(out.stride(0)))
+            if use_tma or lib.llm_attention_mma_supported(c_int(nq), c_int(nkv), c_int(hd), c_longlong(q.stride(0)), c_longlong(out.stride(0))):
                 n_splits, split_keys, scratch, counters = 1, 256, None, None
-                if batch.max_new_tokens == 1 and batch.n_tokens == batch.n_seqs and batch.max_seq_len > 256:
+                if decode_only and batch.max_seq_len > 256:
                     want = max(1, self.ATTENTION_TARGET_CTAS // (batch.n_seqs * nkv))
                     split_keys = -(-max(64, -(-batch.max_seq_len // want)) // 64) * 64
                     n_splits = -(-batch.max_seq_len // split_keys)
@@ -332,6 +336,15 @@ class CudaOps:
                     floats = int(lib.llm_attention_mma_scratch_floats(c_int(n_tokens), c_int(nq), c_int(hd), c_int(n_splits)))
                     scratch = batch.ws.get("attention.splits", (floats,), torch.float32)
                     counters = batch.ws.get_zeroed("attention.split_counters", (batch.n_seqs * nkv,), torch.int32)
+                if use_tma and n_splits <= 128:
+                    # single decoded tokens: keys and values by TMA, one producer thread, four computing warps
+                    self._check(lib.llm_paged_attention_decode(
+                        _ptr(q), c_longlong(q.stride(0)), _ptr(kcache), _ptr(vcache), c_longlong(kcache.shape[0]),
+                        _ptr(batch.seq_start), _ptr(batch.seq_qoff), _ptr(block_table), c_int(block_table.shape[1]), _ptr(out),
+                        c_longlong(out.stride(0)), c_int(batch.n_seqs), c_int(nq), c_int(nkv), c_int(hd), c_int(page),
+                        c_float(scale), c_int(window), c_int(n_splits), c_int(split_keys), _ptr(scratch), _ptr(counters),
+                        _stream()), lib)
+                    return out
                 self._check(lib.llm_paged_attention_mma(
                     _ptr(q), c_longlong(q.stride(0)), _ptr(kcache), _ptr(vcache), _ptr(batch.seq_start), _ptr(batch.seq_ntok),
                     _ptr(batch.seq_qoff), _ptr(block_table), c_int(block_table.shape[1]), _ptr(out), c_longlong(out.stride(0)),

@@ -263,6 +263,57 @@ def test_paged_attention_tcgen05(ops, nq, nkv, window):
         assert not torch.isnan(out.float()).any()
 
 
+@pytest.mark.parametrize("target_ctas", [1, 444, 100000])  # no split, the usual splits, a split every 64 keys
+@pytest.mark.parametrize("nq,nkv,hd,page,window", [(32, 8, 64, 16, 0), (8, 2, 64, 8, 0), (4, 4, 64, 32, 0), (16, 1, 64, 64, 0),
+                                                   (8, 2, 64, 16, 150), (8, 4, 128, 16, 0), (2, 2, 128, 32, 70), (6, 2, 128, 8, 0)])
+def test_paged_attention_decode_by_tma(ops, monkeypatch, nq, nkv, hd, page, window, target_ctas):
+    """The decoding kernel that fetches keys and values by TMA (head sizes 64 and 128): contexts that
+    end at a tile's, a page's and a split's edge, a window whose pages behind it were given back
+    (their table entries are -1), requests of very different lengths in one batch, and every
+    split policy; the same call twice, since the split counters must be left at zero."""
+    dt = torch.bfloat16
+    monkeypatch.setattr(type(ops), "ATTENTION_TARGET_CTAS", target_ctas)
+    seq_lens = [1, 32, 33, 64, 257, 700, 1024, 16]
+    kc, vc, table, dense = _paged_setup(dt, nkv, hd, page, seq_lens, sum((L + page - 1) // page for L in seq_lens) + 3, seed=5)
+    if window:  # pages wholly behind the window are no longer the request's
+        for s_, L in enumerate(seq_lens):
+            for b_ in range(max(0, L - window) // page):
+                kc[int(table[s_, b_])].fill_(float("nan"))  # whoever reads them shows
+                vc[int(table[s_, b_])].fill_(float("nan"))
+                table[s_, b_] = -1
+    scale = 1.0 / math.sqrt(hd)
+    b = Batch([(L - 1, 1) for L in seq_lens])
+    q = rnd(b.n_tokens, nq * hd, dtype=dt, seed=24)
+    for _ in range(2):
+        out = torch.full((b.n_tokens, nq * hd), float("nan"), dtype=dt, device=DEV)
+        ops.paged_attention(q, kc, vc, b, table, out, nq, nkv, hd, scale, window)
+        assert ops.tensor_core_error() == 0
+        for i, (s_, p_) in enumerate(b.tokens):
+            ref = _attention_ref(q[i].cpu().view(nq, hd), dense[s_][0], dense[s_][1], p_, nq, nkv, hd, scale, window)
+            torch.testing.assert_close(out[i].float().cpu(), ref, **tol(dt, 2))
+
+
+def test_decode_attention_kernels_agree(ops):
+    """The TMA decoding kernel against the cp.async one on the same inputs (both bf16 mma.sync with
+    the same tile order): equal up to the order of float32 sums."""
+    nq, nkv, hd, page = 32, 8, 64, 16
+    seq_lens = [2048, 100, 777, 1500]
+    kc, vc, table, dense = _paged_setup(torch.bfloat16, nkv, hd, page, seq_lens, sum((L + page - 1) // page for L in seq_lens) + 3, seed=6)
+    b = Batch([(L - 1, 1) for L in seq_lens])
+    q = rnd(b.n_tokens, nq * hd, dtype=torch.bfloat16, seed=25)
+    outs = []
+    for tma in (True, False):
+        ops.tma_decode_attention = tma
+        try:
+            out = torch.empty(b.n_tokens, nq * hd, dtype=torch.bfloat16, device=DEV)
+            ops.paged_attention(q, kc, vc, b, table, out, nq, nkv, hd, 0.125)
+            outs.append(out.float())
+        finally:
+            ops.tma_decode_attention = True
+    assert ops.tensor_core_error() == 0
+    torch.testing.assert_close(outs[0], outs[1], atol=2e-3, rtol=2e-2)
+
+
 @pytest.mark.parametrize("dt", DTYPES)
 @pytest.mark.parametrize("special", [0, 15, 16, 31, 32, 63, 64, 127, 128, 255, 256, 499])
 @pytest.mark.parametrize("n_new", [1, 3, 40])
