@@ -16,6 +16,15 @@
 // splits' partials in index order by the CTA that finishes last for its (request, key/value head):
 // a token's result does not depend on the batch or on page numbers.
 //
+// Fused form (FUSED): the kernel before this one is the q|k|v product itself, given as float32 K-split
+// partial sums [parts][token][q|k|v]. The computing warps add the parts in index order, rotate q
+// (and k) by the position's cos/sin row as the separate rotation kernel does (half-split form of
+// the reference's apply_rope_inplace, src/kernels.cpp:189-203) and keep q in shared memory only;
+// the CTA whose key range holds the token's own position also writes the new key (rotated) and
+// value to the cache for later steps and patches them into its last tile in shared memory, since
+// the copy of that tile read the cache before they were there. No copy then depends on the kernel
+// before, so all of them are requested ahead of the dependency wait.
+//
 // Formula: the reference's attention_f32 (src/kernels.cpp:413-474).
 #include "tc_common.cuh"
 #include "mma_common.cuh"
@@ -39,6 +48,10 @@ struct DecParams {
   float* part_o; float* part_ml; int split_keys, n_splits; long long part_stride_tokens;
   int* done_count;
   int* error;
+  // fused form only
+  const float* qkv_parts; int n_parts; long long part_stride;  // [n_parts][tokens][(nq + 2 nkv) * hd], parts part_stride floats apart
+  const float* cos_t; const float* sin_t;                       // [positions][hd / 2], or null: no rotation
+  bf16* kcache; bf16* vcache;                                   // where the token's own key and value are written
 };
 
 template <int HD>
@@ -53,7 +66,7 @@ struct DecLayout {
 // Byte offset of (row, 16-byte chunk) inside a [TK][64] tile written by TMA with 128-byte swizzle.
 __device__ __forceinline__ uint32_t sw128(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
 
-template <int HD>
+template <int HD, bool FUSED>
 __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                                  const __grid_constant__ CUtensorMap map_v,
                                                                                  const DecParams p) {
@@ -66,7 +79,8 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
   uint64_t* full = reinterpret_cast<uint64_t*>(q_s + ROWS * L::Q_LD);       // [NS]
   uint64_t* empty = full + NS;                                              // [NS]
   int* flags = reinterpret_cast<int*>(empty + NS);                          // [0] abort, [1] tiles issued, [2] is_last
-  int* page_s = flags + 4;                                                  // the split's slice of the block table
+  bf16* kv_new = reinterpret_cast<bf16*>(flags + 4);                        // [2][HD]: the token's own key and value (fused form)
+  int* page_s = reinterpret_cast<int*>(kv_new + 2 * HD);                    // the split's slice of the block table
   volatile int* abort_flag = flags;
 
   dep_launch();
@@ -121,7 +135,7 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
         if (!ok) break;
       }
       const int key0 = (kt_first + t) * TK;
-      if (!waited && key0 + TK > pos) {  // the tile of the token's own key, written by the kernel before this one
+      if (!FUSED && !waited && key0 + TK > pos) {  // the tile of the token's own key, written by the kernel before this one
         dep_wait();
         waited = true;
       }
@@ -151,12 +165,81 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
   } else {
     // ------------------------------------------------------------------ consumers
     dep_wait();  // q comes from the kernel before this one
-    for (int c = tid; c < ROWS * (HD / 8); c += DEC_CONSUMERS) {
-      const int r = c / (HD / 8), ch = c % (HD / 8);
-      cp_async16(q_s + r * L::Q_LD + ch * 8, p.q + (size_t)tok * p.ld_q + (size_t)(kvh * g + min(r, g - 1)) * HD + ch * 8, r < g);
+    const bool own_key_here = any && pos >= lo && pos <= hi;  // this CTA's range holds the token's own position
+    if constexpr (FUSED) {
+      // items: rotation pairs of the group's q heads, then (own_key_here) of the k head, then pairs of
+      // neighbouring v elements; sums over the parts in index order, eight loads in flight
+      constexpr int HALF = HD / 2;
+      const int n_items = g * HALF + (own_key_here ? 2 * HALF : 0);
+      const int width = (p.nq + 2 * p.nkv) * HD;
+      const float* prow = p.qkv_parts + (size_t)tok * width;
+      for (int c = tid; c < (ROWS - g) * (HD / 8); c += DEC_CONSUMERS)  // rows beyond the group are zeros
+        *reinterpret_cast<uint4*>(q_s + (g + c / (HD / 8)) * L::Q_LD + (c % (HD / 8)) * 8) = make_uint4(0, 0, 0, 0);
+      for (int item = tid; item < n_items; item += DEC_CONSUMERS) {
+        int col_a, col_b, i = 0, kind;  // kind 0: q, 1: k, 2: v
+        int r = 0;
+        if (item < g * HALF) {
+          kind = 0; r = item / HALF; i = item - r * HALF;
+          col_a = (kvh * g + r) * HD + i; col_b = col_a + HALF;
+        } else if (item < g * HALF + HALF) {
+          kind = 1; i = item - g * HALF;
+          col_a = (p.nq + kvh) * HD + i; col_b = col_a + HALF;
+        } else {
+          kind = 2; i = item - g * HALF - HALF;
+          col_a = (p.nq + p.nkv + kvh) * HD + 2 * i; col_b = col_a + 1;
+        }
+        float a = 0.f, b = 0.f;
+        for (int p0 = 0; p0 < p.n_parts; p0 += 8) {
+          float va[8], vb[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const bool in = p0 + u < p.n_parts;
+            va[u] = in ? prow[(size_t)(p0 + u) * p.part_stride + col_a] : 0.f;
+            vb[u] = in ? prow[(size_t)(p0 + u) * p.part_stride + col_b] : 0.f;
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            a += va[u];
+            b += vb[u];
+          }
+        }
+        float ra = a, rb = b;
+        if (kind != 2 && p.cos_t) {
+          const float cs = p.cos_t[(size_t)pos * HALF + i], sn = p.sin_t[(size_t)pos * HALF + i];
+          ra = a * cs - b * sn;
+          rb = b * cs + a * sn;
+        }
+        const bf16 oa = __float2bfloat16_rn(ra), ob = __float2bfloat16_rn(rb);
+        if (kind == 0) {
+          q_s[r * L::Q_LD + i] = oa;
+          q_s[r * L::Q_LD + i + HALF] = ob;
+        } else {
+          int page_idx, in_page;
+          if (p.page_shift >= 0) {
+            page_idx = pos >> p.page_shift;
+            in_page = pos & (p.page_size - 1);
+          } else {
+            page_idx = pos / p.page_size;
+            in_page = pos - page_idx * p.page_size;
+          }
+          const size_t at = ((size_t)(page_s[page_idx - page_first] * p.nkv + kvh) * p.page_size + in_page) * HD;
+          if (kind == 1) {
+            kv_new[i] = oa; kv_new[i + HALF] = ob;
+            p.kcache[at + i] = oa; p.kcache[at + i + HALF] = ob;
+          } else {
+            kv_new[HD + 2 * i] = oa; kv_new[HD + 2 * i + 1] = ob;
+            p.vcache[at + 2 * i] = oa; p.vcache[at + 2 * i + 1] = ob;
+          }
+        }
+      }
+    } else {
+      for (int c = tid; c < ROWS * (HD / 8); c += DEC_CONSUMERS) {
+        const int r = c / (HD / 8), ch = c % (HD / 8);
+        cp_async16(q_s + r * L::Q_LD + ch * 8, p.q + (size_t)tok * p.ld_q + (size_t)(kvh * g + min(r, g - 1)) * HD + ch * 8, r < g);
+      }
+      cp_async_commit();
+      cp_async_wait<0>();
     }
-    cp_async_commit();
-    cp_async_wait<0>();
     asm volatile("bar.sync 1, %0;" ::"n"(DEC_CONSUMERS) : "memory");
     uint32_t qa[KSTEPS][4];
 #pragma unroll
@@ -175,6 +258,16 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
       if (!mbar_wait(&full[stage], (t / NS) & 1, abort_flag, p.error, ERR_DEC_CONSUMER)) break;
       const uint32_t kb = smem_u32(ring + (size_t)stage * L::STAGE_BYTES);
       const uint32_t vb = kb + L::TILE_BYTES;
+      if (FUSED && own_key_here && (kt_first + t) * TK + TK > pos) {
+        // the copy of this tile read the cache before the token's own key and value were there
+        const int r = pos - (kt_first + t) * TK;
+        if (lane < 2 * (HD / 8)) {
+          const int which = lane / (HD / 8), chunk = lane % (HD / 8);  // 0: key, 1: value; 16 bytes each lane
+          uint8_t* dst = ring + (size_t)stage * L::STAGE_BYTES + which * L::TILE_BYTES + (chunk / 8) * (TK * 128) + sw128(r, chunk % 8);
+          *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(kv_new + which * HD + chunk * 8);
+        }
+        __syncwarp();
+      }
 
       float s[TK / 8][4];
 #pragma unroll
@@ -394,24 +487,22 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
 template <int HD>
 size_t decode_smem_bytes(int keys_per_cta, int page_size) {
   using L = DecLayout<HD>;
-  return 1024 + (size_t)L::STAGES * L::STAGE_BYTES + (size_t)ROWS * L::Q_LD * 2 + 2 * L::STAGES * 8 + 16 +
+  return 1024 + (size_t)L::STAGES * L::STAGE_BYTES + (size_t)ROWS * L::Q_LD * 2 + 2 * L::STAGES * 8 + 16 + 2 * HD * 2 +
          (size_t)((keys_per_cta + 2 * TK) / page_size + 4) * sizeof(int);
 }
 
-template <int HD>
+template <int HD, bool FUSED>
 int launch_decode(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int n_seqs, cudaStream_t stream) {
   const int keys_per_cta = p.n_splits > 1 ? p.split_keys : p.max_blocks * p.page_size;
   const size_t smem = decode_smem_bytes<HD>(keys_per_cta, p.page_size);
   if (smem > 200 * 1024) return 2;
-  static bool attr_set = false;  // the largest size asked for so far
-  static size_t attr_bytes = 0;
-  if (!attr_set || smem > attr_bytes) {
-    if (cudaFuncSetAttribute(paged_attention_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+  static size_t attr_bytes = 0;  // the largest size asked for so far
+  if (smem > attr_bytes) {
+    if (cudaFuncSetAttribute(paged_attention_decode_tma_kernel<HD, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return 1;
-    attr_set = true;
     attr_bytes = smem;
   }
-  launch_kernel(paged_attention_decode_tma_kernel<HD>, dim3(n_seqs, p.nkv, p.n_splits), DEC_THREADS, smem, stream, mk, mv, p);
+  launch_kernel(paged_attention_decode_tma_kernel<HD, FUSED>, dim3(n_seqs, p.nkv, p.n_splits), DEC_THREADS, smem, stream, mk, mv, p);
   return 0;
 }
 
@@ -427,6 +518,45 @@ extern "C" int llm_attention_decode_supported(int nq, int nkv, int hd, int page_
   return (ld_q % 8) == 0 && (ld_out % 2) == 0 && encode_fn() != nullptr;
 }
 
+namespace {
+
+int decode_common(DecParams& p, const void* kcache, const void* vcache, long long n_cache_pages, int n_seqs, int hd,
+                  float* scratch, bool fused, cudaStream_t stream) {
+  LLM_REQUIRE(p.max_blocks > 0 && p.window >= 0 && n_cache_pages >= 1, "attention_decode: bad sizes");
+  LLM_REQUIRE((reinterpret_cast<uintptr_t>(kcache) & 15u) == 0 && (reinterpret_cast<uintptr_t>(vcache) & 15u) == 0,
+              "attention_decode: the caches must be 16-byte aligned");
+  LLM_REQUIRE(p.n_splits >= 1 && p.n_splits <= 128 &&
+              (p.n_splits == 1 || (p.split_keys > 0 && p.split_keys % 64 == 0 && scratch != nullptr && p.done_count != nullptr)),
+              "attention_decode: splits need split_keys %% 64 == 0, scratch and counters");
+  LLM_REQUIRE((long long)n_seqs <= 65535 * 32768LL && p.nkv <= 65535, "attention_decode: batch too large for the grid");
+  const long long rows = n_cache_pages * p.nkv * p.page_size;
+  LLM_REQUIRE(rows < (1LL << 31), "attention_decode: the cache has too many rows for a tensor map coordinate");
+  CUtensorMap mk, mv;
+  const int box_rows = p.page_size < TK ? p.page_size : TK;
+  LLM_REQUIRE(tensor_map_for(kcache, rows, hd, hd, box_rows, &mk) && tensor_map_for(vcache, rows, hd, hd, box_rows, &mv),
+              "attention_decode: cannot encode the tensor maps of the cache");
+  p.page_shift = -1;
+  for (int sft = 0; sft < 30; ++sft)
+    if ((1 << sft) == p.page_size) p.page_shift = sft;
+  p.null_page = (int)(n_cache_pages - 1);
+  const int split_keys_asked = p.split_keys;
+  if (p.n_splits == 1) p.split_keys = p.max_blocks * p.page_size + TK;
+  p.part_stride_tokens = n_seqs;
+  p.part_o = scratch;
+  p.part_ml = scratch ? scratch + (size_t)p.n_splits * n_seqs * p.nq * hd : nullptr;
+  p.error = error_word();
+  int rc;
+  if (fused) rc = hd == 64 ? launch_decode<64, true>(mk, mv, p, n_seqs, stream) : launch_decode<128, true>(mk, mv, p, n_seqs, stream);
+  else rc = hd == 64 ? launch_decode<64, false>(mk, mv, p, n_seqs, stream) : launch_decode<128, false>(mk, mv, p, n_seqs, stream);
+  LLM_REQUIRE(rc != 2, "attention_decode: %d keys per split with pages of %d do not fit the block-table copy in shared memory",
+              p.n_splits > 1 ? split_keys_asked : p.max_blocks * p.page_size, p.page_size);
+  LLM_REQUIRE(rc == 0, "attention_decode: cannot raise the shared memory limit");
+  LLM_CHECK_LAUNCH("paged_attention_decode");
+  return LLM_OK;
+}
+
+}  // namespace
+
 // One token per request. q: rows of [nq*hd] bf16 (ld_q elements apart); caches
 // [n_cache_pages, nkv, page_size, hd] bf16, whose LAST page is the null page (finite values, never a
 // request's); seq_start[i]: the token's position; seq_qoff[i]: its row; out [n_seqs, nq*hd] bf16.
@@ -440,35 +570,37 @@ extern "C" int llm_paged_attention_decode(const void* q, long long ld_q, const v
   if (n_seqs == 0) return LLM_OK;
   LLM_REQUIRE(llm_attention_decode_supported(nq, nkv, hd, page_size, ld_q, ld_out),
               "attention_decode: geometry not supported (nq=%d nkv=%d hd=%d page=%d)", nq, nkv, hd, page_size);
-  LLM_REQUIRE(max_blocks > 0 && window >= 0 && n_cache_pages >= 1, "attention_decode: bad sizes");
-  LLM_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15u) == 0 && (reinterpret_cast<uintptr_t>(kcache) & 15u) == 0 &&
-              (reinterpret_cast<uintptr_t>(vcache) & 15u) == 0, "attention_decode: q and the caches must be 16-byte aligned");
-  LLM_REQUIRE(n_splits >= 1 && n_splits <= 128 &&
-              (n_splits == 1 || (split_keys > 0 && split_keys % 64 == 0 && scratch != nullptr && done_count != nullptr)),
-              "attention_decode: splits need split_keys %% 64 == 0, scratch and counters");
-  LLM_REQUIRE((long long)n_seqs <= 65535 * 32768LL && nkv <= 65535, "attention_decode: batch too large for the grid");
-  const long long rows = n_cache_pages * nkv * page_size;
-  LLM_REQUIRE(rows < (1LL << 31), "attention_decode: the cache has too many rows for a tensor map coordinate");
-  CUtensorMap mk, mv;
-  const int box_rows = page_size < TK ? page_size : TK;
-  LLM_REQUIRE(tensor_map_for(kcache, rows, hd, hd, box_rows, &mk) && tensor_map_for(vcache, rows, hd, hd, box_rows, &mv),
-              "attention_decode: cannot encode the tensor maps of the cache");
-  DecParams p;
+  LLM_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15u) == 0, "attention_decode: q must be 16-byte aligned");
+  DecParams p = {};
   p.q = (const bf16*)q; p.ld_q = ld_q; p.seq_start = seq_start; p.seq_qoff = seq_qoff; p.block_table = block_table;
   p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window;
-  p.page_shift = -1;
-  for (int sft = 0; sft < 30; ++sft)
-    if ((1 << sft) == page_size) p.page_shift = sft;
-  p.null_page = (int)(n_cache_pages - 1); p.scale = scale; p.out = (bf16*)out; p.ld_out = ld_out;
-  p.n_splits = n_splits; p.split_keys = n_splits > 1 ? split_keys : max_blocks * page_size + TK;
-  p.part_stride_tokens = n_seqs;
-  p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)n_splits * n_seqs * nq * hd : nullptr;
-  p.done_count = done_count;
-  p.error = error_word();
-  const int rc = hd == 64 ? launch_decode<64>(mk, mv, p, n_seqs, stream) : launch_decode<128>(mk, mv, p, n_seqs, stream);
-  LLM_REQUIRE(rc != 2, "attention_decode: %d keys per split with pages of %d do not fit the block-table copy in shared memory",
-              n_splits > 1 ? split_keys : max_blocks * page_size, page_size);
-  LLM_REQUIRE(rc == 0, "attention_decode: cannot raise the shared memory limit");
-  LLM_CHECK_LAUNCH("paged_attention_decode");
-  return LLM_OK;
+  p.scale = scale; p.out = (bf16*)out; p.ld_out = ld_out;
+  p.n_splits = n_splits; p.split_keys = split_keys; p.done_count = done_count;
+  return decode_common(p, kcache, vcache, n_cache_pages, n_seqs, hd, scratch, false, stream);
+}
+
+// The same with the q|k|v product, rotation and cache write folded in: qkv_parts float32
+// [n_parts][tokens][(nq + 2 nkv) * hd] partial sums (parts part_stride floats apart; the values are
+// their sums in index order), cos/sin float32 [positions][hd / 2] or both null for no rotation. The
+// token's own key (rotated) and value are written into the caches at its position.
+extern "C" int llm_paged_attention_decode_fused(const float* qkv_parts, int n_parts, long long part_stride, const float* cos_t,
+                                                const float* sin_t, void* kcache, void* vcache, long long n_cache_pages,
+                                                const int* seq_start, const int* seq_qoff, const int* block_table,
+                                                int max_blocks, void* out, long long ld_out, int n_seqs, int nq, int nkv, int hd,
+                                                int page_size, float scale, int window, int n_splits, int split_keys,
+                                                float* scratch, int* done_count, cudaStream_t stream) {
+  if (n_seqs == 0) return LLM_OK;
+  LLM_REQUIRE(llm_attention_decode_supported(nq, nkv, hd, page_size, 8, ld_out),
+              "attention_decode: geometry not supported (nq=%d nkv=%d hd=%d page=%d)", nq, nkv, hd, page_size);
+  LLM_REQUIRE(qkv_parts != nullptr && n_parts >= 1 && part_stride >= (long long)n_seqs * (nq + 2 * nkv) * hd,
+              "attention_decode: bad partial sums");
+  LLM_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "attention_decode: cos and sin come together");
+  DecParams p = {};
+  p.seq_start = seq_start; p.seq_qoff = seq_qoff; p.block_table = block_table;
+  p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window;
+  p.scale = scale; p.out = (bf16*)out; p.ld_out = ld_out;
+  p.n_splits = n_splits; p.split_keys = split_keys; p.done_count = done_count;
+  p.qkv_parts = qkv_parts; p.n_parts = n_parts; p.part_stride = part_stride; p.cos_t = cos_t; p.sin_t = sin_t;
+  p.kcache = (bf16*)kcache; p.vcache = (bf16*)vcache;
+  return decode_common(p, kcache, vcache, n_cache_pages, n_seqs, hd, scratch, true, stream);
 }

@@ -57,6 +57,7 @@ class CudaOps:
         self.tensor_cores = True  # bfloat16 products on tcgen05 where the operands allow it
         self.tcgen05_attention = True  # prompt portions: attention on tcgen05 where the geometry allows it
         self.tma_decode_attention = True  # single decoded tokens: keys and values by TMA where the geometry allows it
+        self.fused_decode_attention = True  # ... with the sum of the q|k|v parts, rotation and cache write in the same kernel
 
     # ------------------------------------------------------------------ loading
     def lib(self, name: str = "core"):
@@ -297,6 +298,59 @@ class CudaOps:
     ATTENTION_TARGET_CTAS = 444
     TC_ATTENTION_MIN_TOKENS = 32  # longest portion of the step from which the tcgen05 attention kernel is used
 
+    def _decode_splits(self, lib, batch, nq: int, nkv: int, hd: int):
+        """How a step of single tokens cuts its key ranges -> (n_splits, split_keys, scratch, counters)."""
+        n_splits, split_keys, scratch, counters = 1, 256, None, None
+        if batch.max_seq_len > 256:
+            want = max(1, self.ATTENTION_TARGET_CTAS // (batch.n_seqs * nkv))
+            split_keys = -(-max(64, -(-batch.max_seq_len // want)) // 64) * 64
+            n_splits = -(-batch.max_seq_len // split_keys)
+        if n_splits > 1:
+            floats = int(lib.llm_attention_mma_scratch_floats(c_int(batch.n_tokens), c_int(nq), c_int(hd), c_int(n_splits)))
+            scratch = batch.ws.get("attention.splits", (floats,), torch.float32)
+            counters = batch.ws.get_zeroed("attention.split_counters", (batch.n_seqs * nkv,), torch.int32)
+        return n_splits, split_keys, scratch, counters
+
+    def decode_attention_fusable(self, batch, kcache: torch.Tensor, nq: int, nkv: int, hd: int, out: torch.Tensor) -> bool:
+        """Whether paged_attention_decode_fused takes this step: single tokens only, bfloat16, and a
+        geometry of the TMA decoding kernel."""
+        if not (self.fused_decode_attention and self.tma_decode_attention and self.tensor_cores and kcache.dtype == torch.bfloat16):
+            return False
+        if not (batch.max_new_tokens == 1 and batch.n_tokens == batch.n_seqs):
+            return False
+        lib = self.lib("tensorcore")
+        if not lib.llm_attention_decode_supported(c_int(nq), c_int(nkv), c_int(hd), c_int(kcache.shape[2]), c_longlong(8),
+                                                  c_longlong(out.stride(0))):
+            return False
+        want = max(1, self.ATTENTION_TARGET_CTAS // (batch.n_seqs * nkv))
+        return -(-batch.max_seq_len // (-(-max(64, -(-batch.max_seq_len // want)) // 64) * 64)) <= 128
+
+    def paged_attention_decode_fused(self, parts: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                                     kcache: torch.Tensor, vcache: torch.Tensor, batch, block_table: torch.Tensor,
+                                     out: torch.Tensor, nq: int, nkv: int, hd: int, scale: float, window: int = 0) -> torch.Tensor:
+        """A step of single tokens, from the q|k|v product's partial sums (float32 [p, n, (nq+2nkv)*hd],
+        added in index order): rotation of q and k by cos/sin [positions, hd/2] (none if both are
+        None), the write of k and v into the token's page, and attention over the cache, in one kernel."""
+        _need(parts, "attention.parts", torch.float32); _need(kcache, "attention.kcache", torch.bfloat16)
+        _need(vcache, "attention.vcache", torch.bfloat16); _need(out, "attention.out", torch.bfloat16)
+        _need(block_table, "attention.block_table", torch.int32)
+        assert parts.is_contiguous() and parts.dim() == 3 and parts.shape[2] == (nq + 2 * nkv) * hd and parts.shape[1] >= batch.n_tokens
+        assert kcache.is_contiguous() and vcache.is_contiguous() and block_table.is_contiguous() and kcache.shape == vcache.shape
+        assert kcache.shape[1] == nkv and kcache.shape[3] == hd
+        if cos is not None:
+            _need(cos, "attention.cos", torch.float32); _need(sin, "attention.sin", torch.float32)
+            assert cos.is_contiguous() and sin.is_contiguous() and cos.shape[1] == hd // 2 and cos.shape == sin.shape
+            assert cos.shape[0] >= batch.max_seq_len
+        lib = self.lib("tensorcore")
+        n_splits, split_keys, scratch, counters = self._decode_splits(lib, batch, nq, nkv, hd)
+        self._check(lib.llm_paged_attention_decode_fused(
+            _ptr(parts), c_int(parts.shape[0]), c_longlong(parts.stride(0)), _ptr(cos), _ptr(sin), _ptr(kcache), _ptr(vcache),
+            c_longlong(kcache.shape[0]), _ptr(batch.seq_start), _ptr(batch.seq_qoff), _ptr(block_table),
+            c_int(block_table.shape[1]), _ptr(out), c_longlong(out.stride(0)), c_int(batch.n_seqs), c_int(nq), c_int(nkv),
+            c_int(hd), c_int(kcache.shape[2]), c_float(scale), c_int(window), c_int(n_splits), c_int(split_keys),
+            _ptr(scratch), _ptr(counters), _stream()), lib)
+        return out
+
     def paged_attention(self, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, batch,
                         block_table: torch.Tensor, out: torch.Tensor, nq: int, nkv: int, hd: int, scale: float,
                         window: int = 0) -> torch.Tensor:
@@ -328,14 +382,8 @@ class CudaOps:
                 c_int(nq), c_int(nkv), c_int(hd), c_int(page), c_longlong(q.stride(0)), c_longlong(out.stride(0)))
             if use_tma or lib.llm_attention_mma_supported(c_int(nq), c_int(nkv), c_int(hd), c_longlong(q.stride(0)), c_longlong(out.stride(0))):
                 n_splits, split_keys, scratch, counters = 1, 256, None, None
-                if decode_only and batch.max_seq_len > 256:
-                    want = max(1, self.ATTENTION_TARGET_CTAS // (batch.n_seqs * nkv))
-                    split_keys = -(-max(64, -(-batch.max_seq_len // want)) // 64) * 64
-                    n_splits = -(-batch.max_seq_len // split_keys)
-                if n_splits > 1:
-                    floats = int(lib.llm_attention_mma_scratch_floats(c_int(n_tokens), c_int(nq), c_int(hd), c_int(n_splits)))
-                    scratch = batch.ws.get("attention.splits", (floats,), torch.float32)
-                    counters = batch.ws.get_zeroed("attention.split_counters", (batch.n_seqs * nkv,), torch.int32)
+                if decode_only:
+                    n_splits, split_keys, scratch, counters = self._decode_splits(lib, batch, nq, nkv, hd)
                 if use_tma and n_splits <= 128:
                     # single decoded tokens: keys and values by TMA, one producer thread, four computing warps
                     self._check(lib.llm_paged_attention_decode(

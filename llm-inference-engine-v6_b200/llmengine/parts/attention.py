@@ -48,14 +48,21 @@ class PagedAttention(Mixer):
         s, ops, n = self.spec, self.env.ops, ctx.n_tokens
         dq, dkv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
         qkv = ctx.ws.get("attention.qkv", (n, dq + 2 * dkv), self.env.dtype)
+        att = ctx.ws.get("attention.out", (n, dq), self.env.dtype)
         if n <= 64 and cache.writes and self.position.takes_partial_sums:
             # few tokens: the product comes as K-split partial sums, added by the position kernel
             parts = ops.gemm_partials(x[:n], self.w_qkv, ctx.ws, "attention.qkv_parts")
+            tables = self.position.rotation_tables() if cache.k is not None else None
+            if tables is not None and ops.decode_attention_fusable(ctx, cache.k, s.num_heads, s.num_kv_heads, s.head_dim, att):
+                # single decoded tokens: summing the parts, rotation and the cache write happen inside the attention kernel
+                ops.paged_attention_decode_fused(parts, tables[0], tables[1], cache.k, cache.v, ctx,
+                                                 ctx.block_tables[cache.group], att, s.num_heads, s.num_kv_heads,
+                                                 s.head_dim, self.scale, s.window)
+                return ops.gemm_partials(att, self.w_o, ctx.ws, "attention.delta")
             self.position.rotate_and_store(qkv, ctx, cache, s.num_heads, s.num_kv_heads, s.head_dim, parts=parts)
         else:
             ops.gemm(x[:n], self.w_qkv, qkv, ctx.ws)
             self.position.rotate_and_store(qkv, ctx, cache, s.num_heads, s.num_kv_heads, s.head_dim)
-        att = ctx.ws.get("attention.out", (n, dq), self.env.dtype)
         ops.paged_attention(qkv[:, :dq], cache.k, cache.v, ctx, ctx.block_tables[cache.group], att, s.num_heads,
                             s.num_kv_heads, s.head_dim, self.scale, s.window)
         return ops.gemm_partials(att, self.w_o, ctx.ws, "attention.delta")

@@ -94,6 +94,12 @@ class PositionEncoding(Part):
     # product to be added (in index order) while encoding, instead of finished values in qkv.
     takes_partial_sums = False
 
+    def rotation_tables(self):
+        """For mixers that fold the encoding into their own kernel: (cos, sin) float32 tables
+        [positions, head_dim / 2] of a half-split rotation, (None, None) if nothing is rotated, or
+        None (the default) if the encoding is not of that form and rotate_and_store must be used."""
+        return None
+
     def rotate_and_store(self, qkv: torch.Tensor, ctx, cache: LayerCache, num_heads: int, num_kv_heads: int,
                          head_dim: int, parts: Optional[torch.Tensor] = None) -> None:
         """Encodes positions into q and k of qkv [tokens, (heads + 2 kv_heads) * head_dim] in place

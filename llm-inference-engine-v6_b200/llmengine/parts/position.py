@@ -60,6 +60,9 @@ class RotaryPosition(PositionEncoding):
         self.cos = torch.from_numpy(cos).to(env.device)
         self.sin = torch.from_numpy(sin).to(env.device)
 
+    def rotation_tables(self):
+        return self.cos, self.sin
+
     def rotate_and_store(self, qkv, ctx, cache: LayerCache, num_heads, num_kv_heads, head_dim, parts=None) -> None:
         write = cache.writes and cache.k is not None
         self.env.ops.rope_kv_write(qkv, ctx.positions, ctx.token_seq, ctx.block_tables[cache.group], self.cos, self.sin,
@@ -69,6 +72,9 @@ class RotaryPosition(PositionEncoding):
 
 class NoPosition(PositionEncoding):
     takes_partial_sums = True
+
+    def rotation_tables(self):
+        return None, None
 
     def rotate_and_store(self, qkv, ctx, cache: LayerCache, num_heads, num_kv_heads, head_dim, parts=None) -> None:
         if cache.writes and cache.k is not None:

@@ -104,6 +104,9 @@ class CpuOps:
             else:
                 qkv[t, nq * hd:(nq + nkv) * hd] = k.reshape(-1).to(qkv.dtype)
 
+    def decode_attention_fusable(self, batch, kcache, nq, nkv, hd, out):
+        return False
+
     def paged_attention(self, q, kcache, vcache, batch, block_table, out, nq, nkv, hd, scale, window=0):
         positions, token_seq, n_tokens = batch.positions, batch.token_seq, batch.n_tokens
         ps = kcache.shape[2]

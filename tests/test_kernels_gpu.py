@@ -293,6 +293,50 @@ def test_paged_attention_decode_by_tma(ops, monkeypatch, nq, nkv, hd, page, wind
             torch.testing.assert_close(out[i].float().cpu(), ref, **tol(dt, 2))
 
 
+@pytest.mark.parametrize("nq,nkv,hd,page,window,rotate", [(32, 8, 64, 16, 0, True), (8, 2, 64, 8, 100, True), (16, 1, 64, 32, 0, False),
+                                                          (8, 4, 128, 16, 0, True), (2, 2, 128, 64, 90, True)])
+@pytest.mark.parametrize("n_parts", [1, 11])
+def test_decode_attention_with_rotation_and_cache_write_folded_in(ops, nq, nkv, hd, page, window, rotate, n_parts):
+    """One kernel from the q|k|v partial sums against the two-kernel path (rotation + cache write,
+    then attention) on the same inputs: the same sums in the same order, so the outputs and the
+    caches are equal bit for bit. Positions at the first slot of a fresh page and at a split's edge."""
+    dt = torch.bfloat16
+    seq_lens = [1, 17, 64, 65, 321, 1025, 700]  # the token is the last of each
+    n_pages = sum((L + page - 1) // page for L in seq_lens) + 3
+    kc, vc, table, dense = _paged_setup(dt, nkv, hd, page, seq_lens, n_pages, seed=7)
+    b = Batch([(L - 1, 1) for L in seq_lens])
+    n, width = b.n_tokens, (nq + 2 * nkv) * hd
+    parts = rnd(n_parts, n, width, dtype=torch.float32, seed=26) / math.sqrt(n_parts)
+    max_pos = 1100
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * (10000.0 ** (-torch.arange(hd // 2, dtype=torch.float64) / (hd // 2)))[None]
+    cos, sin = (ang.cos().float().to(DEV), ang.sin().float().to(DEV)) if rotate else (None, None)
+    scale = 1.0 / math.sqrt(hd)
+    # two kernels
+    k1, v1 = kc.clone(), vc.clone()
+    qkv = torch.empty(n, width, dtype=dt, device=DEV)
+    ops.rope_kv_write(qkv, b.positions, b.token_seq, table, cos, sin, k1, v1, n, nq, nkv, hd, parts=parts)
+    out1 = torch.empty(n, nq * hd, dtype=dt, device=DEV)
+    ops.paged_attention(qkv[:, :nq * hd], k1, v1, b, table, out1, nq, nkv, hd, scale, window)
+    # one kernel
+    k2, v2 = kc.clone(), vc.clone()
+    out2 = torch.full((n, nq * hd), float("nan"), dtype=dt, device=DEV)
+    assert ops.decode_attention_fusable(b, k2, nq, nkv, hd, out2)
+    ops.paged_attention_decode_fused(parts, cos, sin, k2, v2, b, table, out2, nq, nkv, hd, scale, window)
+    assert ops.tensor_core_error() == 0
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert torch.equal(out1, out2)
+    # and both are right: the new key/value count
+    summed = parts.sum(0).cpu()
+    for i, (s_, p_) in enumerate(b.tokens):
+        K, V = dense[s_][0].clone(), dense[s_][1].clone()
+        pg, off = int(table[s_, p_ // page]), p_ % page
+        K[p_], V[p_] = k2[pg, :, off].cpu(), v2[pg, :, off].cpu()
+        q = qkv[i, :nq * hd].cpu().view(nq, hd)
+        ref = _attention_ref(q, K, V, p_, nq, nkv, hd, scale, window)
+        torch.testing.assert_close(out2[i].float().cpu(), ref, **tol(dt, 2))
+        torch.testing.assert_close(v2[pg, :, off].float().cpu().reshape(-1), summed[i, (nq + nkv) * hd:], atol=2e-2, rtol=2e-2)
+
+
 def test_decode_attention_kernels_agree(ops):
     """The TMA decoding kernel against the cp.async one on the same inputs (both bf16 mma.sync with
     the same tile order): equal up to the order of float32 sums."""
