@@ -39,8 +39,9 @@ def test_embed(ops, dt):
 
 @pytest.mark.parametrize("dt", DTYPES)
 @pytest.mark.parametrize("dim", [16, 257, 2048, 5000])
-def test_rmsnorm_variants(ops, dt, dim):
-    n, eps = 7, 1e-5
+@pytest.mark.parametrize("n", [7, 70])  # few rows: a cluster of CTAs shares a row; many: one CTA a row
+def test_rmsnorm_variants(ops, dt, dim, n):
+    eps = 1e-5
     h = rnd(n, dim, seed=1)
     w = rnd(dim, seed=2) * 0.1 + 1.0
     ref = torch.from_numpy(P.rmsnorm(h.cpu().numpy(), w.cpu().numpy(), eps)).to(DEV)
