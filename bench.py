@@ -189,7 +189,10 @@ def run_ours(args):
         wall = time.perf_counter() - t_wall
         dev = start.elapsed_time(stop) / 1e3
         launches = eng.ops.launches / k_steps
-        h2d, d2h = eng.buffers.h2d_bytes, 4 * batch
+        if e2e and eng.cuda_graphs and eng.graphs is not None:
+            h2d, d2h = eng.graphs.h2d_bytes, eng.graphs.d2h_bytes
+        else:
+            h2d, d2h = eng.buffers.h2d_bytes, 4 * batch
         # drain: finish the requests and give their pages back
         for r in list(sch._cm.request_ids()):
             sch._cm.release(r)

@@ -79,6 +79,7 @@ class StepBuffers:
         self.dev: Optional[torch.Tensor] = None
         self._copied = None  # event: the last host->device copy has finished reading `host`
         self.h2d_bytes = 0   # bytes of the last transfer (for measurements)
+        self._views = None   # (elements, device view, host view) of the last refill
 
     def _ensure(self, total: int) -> None:
         if self.host is None or self.host.numel() < total:
@@ -86,6 +87,7 @@ class StepBuffers:
             if self._copied is not None:
                 self._copied.synchronize()
             on_gpu = self.device.type == "cuda"
+            self._views = None
             self.host = torch.empty(cap, dtype=torch.int32, pin_memory=on_gpu)
             self.dev = torch.empty(cap, dtype=torch.int32, device=self.device)
 
@@ -110,6 +112,20 @@ class StepBuffers:
             self._copied.record()
         self.h2d_bytes = layout.total * 4
         return self.context(layout, counts, padded=pad_to is not None)
+
+    def refill(self, cm, entries, layout, vocab_size: int, max_positions: int):
+        """The same arrays for the next step of a padded batch whose layout (and so every device
+        address) stays as the last prepare() left it: a captured graph keeps reading the tensors of
+        that call's context, so nothing but the fill and the copy has to happen. -> the step's counts."""
+        self._copied.synchronize()
+        H = host_module()
+        counts = H.fill_step(cm, entries, layout, self.host.data_ptr(), True, vocab_size, max_positions)
+        if self._views is None or self._views[0] != layout.total:
+            self._views = (layout.total, self.dev[:layout.total], self.host[:layout.total])
+        self._views[1].copy_(self._views[2], non_blocking=True)
+        self._copied.record()
+        self.h2d_bytes = layout.total * 4
+        return counts
 
     def context(self, layout, counts, padded: bool) -> StepContext:
         d = self.dev

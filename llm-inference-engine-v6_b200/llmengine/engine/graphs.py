@@ -35,6 +35,7 @@ class DecodeGraphs:
     def __init__(self, engine):
         self.engine = engine
         self.captured: Dict[Tuple[int, int], _Captured] = {}
+        self.h2d_bytes = self.d2h_bytes = 0  # of the last step (for measurements)
 
     def clear(self) -> None:
         self.captured.clear()
@@ -81,7 +82,8 @@ class DecodeGraphs:
         c.kernels = eng.ops.launches - before
         c.graph = graph
         c.host_tokens = torch.empty(cap, dtype=torch.int32, pin_memory=True)
-        c.prepare = prepare
+        layout = H.StepLayout.make(cap, cap, cap, blocks, eng.cm.num_groups)
+        c.refill = lambda entries: c.buffers.refill(eng.cm, entries, layout, eng.spec.vocab_size, eng.max_pos)
         return c
 
     def run(self, entries) -> List[int]:
@@ -95,12 +97,13 @@ class DecodeGraphs:
         if c is None:
             c = self._capture(cap, blocks)
             self.captured[(cap, blocks)] = c
-        c.prepare(entries)
+        c.refill(entries)
         c.graph.replay()
         eng.ops.launches += c.kernels
-        c.host_tokens[:seqs].copy_(c.tokens[:seqs], non_blocking=True)
+        c.host_tokens.copy_(c.tokens, non_blocking=True)  # all `cap` of them: no views to make
         torch.cuda.current_stream().synchronize()
-        return c.host_tokens[:seqs].tolist()
+        self.h2d_bytes, self.d2h_bytes = c.buffers.h2d_bytes, 4 * cap
+        return c.host_tokens.tolist()[:seqs]
 
     def run_device(self, entries) -> torch.Tensor:
         """As run, without reading the tokens back (for device-time measurements)."""
@@ -113,7 +116,7 @@ class DecodeGraphs:
         if c is None:
             c = self._capture(cap, blocks)
             self.captured[(cap, blocks)] = c
-        c.prepare(entries)
+        c.refill(entries)
         c.graph.replay()
         eng.ops.launches += c.kernels
         return c.tokens[:seqs]
