@@ -78,6 +78,8 @@ def run_attention(args) -> dict:
     dev = torch.device("cuda:0")
     nq, nkv, hd, page = args.heads, args.kv_heads, args.head_dim, args.page
     B, ctx, new = args.batch, args.context, args.new
+    if getattr(args, "kernel", "auto") == "mma":
+        ops.tcgen05_attention = ops.tma_decode_attention = False
     total = ctx + new
     blocks = (total + page - 1) // page
     layers = max(2, int(300e6 // max(B * total * nkv * hd * 4, 1)) + 1)  # caches of several "layers" in turn
@@ -148,7 +150,9 @@ def run_step_timeline(args) -> dict:
     agg = collections.OrderedDict()
     for e in ev:
         end = e.time_range.end
-        name = e.name.split("(")[0].split("::")[-1].split("<")[0]
+        name = e.name.replace("(anonymous namespace)::", "").replace("<unnamed>::", "")
+        name = name[5:] if name.startswith("void ") else name
+        name = name.split("(")[0].split("<")[0].split("::")[-1]
         a = agg.setdefault(name, [0, 0.0, 0.0])
         a[0] += 1
         a[1] += max(end - prev_end, 0)
@@ -172,6 +176,8 @@ def main(argv=None) -> int:
     a.add_argument("--batch", type=int, default=8); a.add_argument("--context", type=int, default=2048); a.add_argument("--new", type=int, default=1)
     a.add_argument("--heads", type=int, default=32); a.add_argument("--kv-heads", type=int, default=8); a.add_argument("--head-dim", type=int, default=64)
     a.add_argument("--page", type=int, default=16); a.add_argument("--reps", type=int, default=20)
+    a.add_argument("--kernel", choices=["auto", "mma"], default="auto",
+                   help="mma: the mma.sync kernels also where the tcgen05 / TMA kernels would run")
     a.add_argument("--sequential", action="store_true", help="each request's pages lie in a row (default: scattered over the pool)")
     t = sub.add_parser("step")
     t.add_argument("--batch", type=int, default=8); t.add_argument("--context", type=int, default=2048)
