@@ -14,7 +14,7 @@ from typing import List
 import torch
 
 from .base import KVNeed, LayerCache, Mixer
-from .registry import build_part, register_part
+from .registry import build_part, part_class, register_part
 from .spec import AttentionSpec, TensorNeed
 
 
@@ -34,7 +34,8 @@ class PagedAttention(Mixer):
     def tensor_needs(spec: AttentionSpec) -> List[TensorNeed]:
         dq, dkv = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
         return [TensorNeed(spec.q_weight, (dq, spec.hidden)), TensorNeed(spec.k_weight, (dkv, spec.hidden)),
-                TensorNeed(spec.v_weight, (dkv, spec.hidden)), TensorNeed(spec.o_weight, (spec.hidden, dq))]
+                TensorNeed(spec.v_weight, (dkv, spec.hidden)), TensorNeed(spec.o_weight, (spec.hidden, dq))] + \
+            list(part_class("position", spec.position.kind).tensor_needs(spec.position))
 
     def cache_needs(self):
         return (KVNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window),)
@@ -43,6 +44,7 @@ class PagedAttention(Mixer):
         s = self.spec
         self.w_qkv = torch.cat([tensors[s.q_weight], tensors[s.k_weight], tensors[s.v_weight]], dim=0).contiguous()
         self.w_o = tensors[s.o_weight]
+        self.position.load(tensors)
 
     def forward(self, x: torch.Tensor, ctx, cache: LayerCache) -> torch.Tensor:
         s, ops, n = self.spec, self.env.ops, ctx.n_tokens

@@ -215,6 +215,163 @@ def test_toy_mixer_with_state_can_be_registered_built_and_stepped(tmp_path):
     assert len(out) == 9 and reason == "length" and eng.cm.free_slots == 2
 
 
+# ------------------------------------------------- a toy routed feed-forward, a toy position encoding
+@dataclass(frozen=True)
+class Top1ExpertsSpec:
+    kind: str
+    hidden: int
+    experts: int
+    router: str
+    expert_weights: tuple  # tensor names, one [hidden, hidden] matrix each
+
+
+@dataclass(frozen=True)
+class AddedPositionSpec:
+    kind: str
+    head_dim: int
+    max_positions: int
+    table: str  # [max_positions, head_dim]: added to every q and k head at its position
+
+
+def _register_toy_routing_and_position():
+    """A feed-forward that routes every token to the best of three experts (router logits and their
+    softmax in float32, the step's tokens grouped by expert), and a position encoding that is not a
+    rotation: a learned vector per position added to q and k. Both live in this file only."""
+    from dataclasses import replace
+    from llmengine.config.registry import Architecture, register_architecture
+    from llmengine.config.llama import LlamaConfig
+    from llmengine.models.llama import describe_llama
+    from llmengine.parts import FeedForward, PositionEncoding, TensorNeed, register_part
+
+    class Top1Experts(FeedForward):
+        @staticmethod
+        def tensor_needs(spec):
+            return [TensorNeed(spec.router, (spec.experts, spec.hidden), "float32")] + \
+                   [TensorNeed(n, (spec.hidden, spec.hidden)) for n in spec.expert_weights]
+
+        def load(self, tensors):
+            self.router = tensors[self.spec.router]
+            self.w = [tensors[n] for n in self.spec.expert_weights]
+
+        def forward(self, x, ctx):
+            n = ctx.n_tokens
+            xf = x[:n].float()
+            prob = torch.softmax(xf @ self.router.t(), dim=-1)
+            best = prob.argmax(dim=-1)
+            out = torch.zeros(n, self.spec.hidden, dtype=torch.float32, device=x.device)
+            for e in range(self.spec.experts):  # the step's tokens of expert e, whichever request they are of
+                rows = (best == e).nonzero().squeeze(1)
+                if rows.numel():
+                    out[rows] = prob[rows, e].unsqueeze(1) * (xf[rows] @ self.w[e].float().t())
+            return out
+
+    class AddedPosition(PositionEncoding):
+        @staticmethod
+        def tensor_needs(spec):
+            return [TensorNeed(spec.table, (spec.max_positions, spec.head_dim), "float32")]
+
+        def load(self, tensors):
+            self.table = tensors[self.spec.table]
+
+        def rotate_and_store(self, qkv, ctx, cache, num_heads, num_kv_heads, head_dim, parts=None):
+            assert parts is None  # takes_partial_sums is False: finished values only
+            n = ctx.n_tokens
+            add = self.table[ctx.positions[:n].long()]  # [n, head_dim]
+            qk = qkv[:n, :(num_heads + num_kv_heads) * head_dim].view(n, num_heads + num_kv_heads, head_dim)
+            qk.copy_((qk.float() + add.unsqueeze(1)).to(qkv.dtype))
+            if cache.writes and cache.k is not None:  # the framework's kernel, without tables, stores k and v
+                self.env.ops.rope_kv_write(qkv, ctx.positions, ctx.token_seq, ctx.block_tables[cache.group], None, None,
+                                           cache.k, cache.v, n, num_heads, num_kv_heads, head_dim)
+
+    register_part("feed_forward", "top1_experts", Top1Experts, replace=True)
+    register_part("position", "added", AddedPosition, replace=True)
+
+    def describe(cfg):
+        spec = describe_llama(cfg)
+        layers = list(spec.layers)
+        pos = AddedPositionSpec("added", cfg.head_dim, cfg.max_position_embeddings, "model.toy_positions.weight")
+        layers[0] = replace(layers[0], mixer=replace(layers[0].mixer, position=pos))  # layer 0: added positions, dense MLP
+        layers[1] = replace(layers[1], feed_forward=Top1ExpertsSpec(             # layer 1: rotary, routed experts
+            "top1_experts", cfg.hidden_size, 3, "model.layers.1.toy.router.weight",
+            tuple(f"model.layers.1.toy.experts.{e}.weight" for e in range(3))))
+        return replace(spec, architecture="ToyRoutedModel", layers=tuple(layers))
+
+    register_architecture(Architecture("ToyRoutedModel", LlamaConfig.from_dict, describe,
+                                       lambda c: dict(c.to_dict(), architectures=["ToyRoutedModel"])), replace=True)
+
+
+def _toy_routed_plain(pc, w, ids):
+    T, hd, nq, nkv, eps = len(ids), pc["head_dim"], pc["num_attention_heads"], pc["num_key_value_heads"], pc["rms_norm_eps"]
+    cos, sin = P.rope_tables(P.llama3_inv_freq(hd, pc["rope_theta"], False, 1, 1, 1, 0), T, hd)
+    h = P.embed(w["model.embed_tokens.weight"], ids)
+    # layer 0: attention with added positions, dense MLP
+    p = "model.layers.0."
+    x = P.rmsnorm(h, w[p + "input_layernorm.weight"], eps)
+    add = w["model.toy_positions.weight"][:T][:, None, :]
+    q = P.linear(x, w[p + "self_attn.q_proj.weight"]).reshape(T, nq, hd) + add
+    k = P.linear(x, w[p + "self_attn.k_proj.weight"]).reshape(T, nkv, hd) + add
+    v = P.linear(x, w[p + "self_attn.v_proj.weight"]).reshape(T, nkv, hd)
+    h = h + P.linear(P.causal_gqa_attention(q.astype(np.float32), k.astype(np.float32), v), w[p + "self_attn.o_proj.weight"])
+    x = P.rmsnorm(h, w[p + "post_attention_layernorm.weight"], eps)
+    h = h + P.swiglu_mlp(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    # layer 1: rotary attention, top-1 of three experts
+    p = "model.layers.1."
+    x = P.rmsnorm(h, w[p + "input_layernorm.weight"], eps)
+    h = h + P.attention_block(x, pc, w, 1, cos, sin)
+    x = P.rmsnorm(h, w[p + "post_attention_layernorm.weight"], eps)
+    logits = P.linear(x, w[p + "toy.router.weight"])
+    prob = np.exp(logits - logits.max(-1, keepdims=True))
+    prob = prob / prob.sum(-1, keepdims=True)
+    best = prob.argmax(-1)
+    routed = np.stack([prob[t, best[t]] * P.linear(x[t:t + 1], w[p + f"toy.experts.{best[t]}.weight"])[0] for t in range(T)])
+    h = h + routed.astype(np.float32)
+    top2 = np.sort(prob, axis=-1)[:, -2:]
+    return P.linear(P.rmsnorm(h, w["model.norm.weight"], eps), w["lm_head.weight"]), best, top2[:, 1] - top2[:, 0]
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_toy_routed_feed_forward_and_toy_position_encoding(tmp_path, dtype):
+    """Parts of other kinds than the architecture's, registered from here: a layer with a position
+    encoding that is no rotation beside a rotary one, a routed feed-forward beside a dense one; whole,
+    in portions, and two requests mixed in a step (the experts see tokens of both)."""
+    _register_toy_routing_and_position()
+    cfg = dict(TINY_A, architectures=["ToyRoutedModel"])
+    d = str(tmp_path / "routed")
+    llmengine.write_random_model(d, cfg, seed=8, dtype=torch.float32, std=0.05)
+    pc, pw = P.read_model(d)
+    if dtype == "bf16":  # the plain model gets the weights the engine will hold
+        pw = {k: (torch.from_numpy(v).bfloat16().float().numpy() if v.ndim == 2 and "toy_positions" not in k and "router" not in k else v)
+              for k, v in pw.items()}
+    assert "model.layers.1.toy.experts.2.weight" in pw and "model.layers.1.mlp.gate_proj.weight" not in pw
+    ids_a, ids_b = random_ids(40, 256, 11), random_ids(27, 256, 12)
+    (ref_a, best_a, gap_a), (ref_b, best_b, gap_b) = _toy_routed_plain(pc, pw, ids_a), _toy_routed_plain(pc, pw, ids_b)
+    assert len(set(best_a.tolist()) | set(best_b.tolist())) == 3, "the test wants every expert used"
+    tol_ = dict(atol=2e-4, rtol=0) if dtype == "fp32" else dict(atol=6e-2, rtol=0)
+    # The routed layer is the last one, so a token's choice of expert touches its own logits only.
+    # A token whose two best experts are nearly tied may go either way under bfloat16 rounding of
+    # the router's input; such rows are left out of the comparison (not of the run).
+    min_gap = 1e-4 if dtype == "fp32" else 2e-2
+    keep_a, keep_b = gap_a > min_gap, gap_b > min_gap
+    assert keep_a.sum() > 30 and keep_b.sum() > 20
+    eng = llmengine.Engine(d, dtype, block_size=4, num_blocks=40, max_concurrent=2)
+    np.testing.assert_allclose(eng.forward_logits(ids_a)[keep_a], ref_a[keep_a], **tol_)
+    got_a, got_b = [], []
+    got_a.append(eng.run_step([(1, ids_a[:13], range(13))]).clone())
+    lg = eng.run_step([(2, ids_b[:20], range(20)), (1, ids_a[13:15], range(2))])
+    got_b.append(lg[:20].clone()); got_a.append(lg[20:].clone())
+    for t in range(15, 40):  # request 1 decodes token by token while request 2 ends its prompt
+        batch = [(1, ids_a[t:t + 1], [0])]
+        if t == 15:
+            batch.append((2, ids_b[20:], range(7)))
+        lg = eng.run_step(batch, end=([1] if t == 39 else []) + ([2] if t == 15 else []))
+        got_a.append(lg[:1].clone())
+        if t == 15:
+            got_b.append(lg[1:].clone())
+    np.testing.assert_allclose(torch.cat(got_a).cpu().numpy()[keep_a], ref_a[keep_a], **tol_)
+    np.testing.assert_allclose(torch.cat(got_b).cpu().numpy()[keep_b], ref_b[keep_b], **tol_)
+    assert eng.cm.free_slots == 2
+
+
 def test_layer_order_is_data(tmp_path):
     """The order in which layers run is a list: it may name a layer twice, and a run may read an
     earlier run's cache instead of keeping its own."""
