@@ -230,6 +230,232 @@ __global__ void __launch_bounds__(128)
   }
 }
 
+// Persistent form of the token-tile product with 256 outputs a tile: one CTA per SM walks the tiles
+// blockIdx.x, blockIdx.x + gridDim.x, ... (tiles of one weight column block are neighbours, so the
+// CTAs that run together share it in L2). The accumulator is double: tensor memory holds two tiles
+// of 256 columns, and the four epilogue warps drain one while the tensor cores fill the other, so
+// the tensor pipe does not idle during the 64-128 KB write-out and the ring of operand stages never
+// runs empty between tiles. Warps 0-3: epilogue (a warp reads its own 32 accumulator lanes); warp 4
+// lane 0: TMA; warp 5 lane 0: tcgen05.mma. Waits are bounded as in the one-tile kernel.
+constexpr int PERSIST_THREADS = 192;
+
+template <typename TO, bool SWIGLU>
+__global__ void __launch_bounds__(PERSIST_THREADS)
+    gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                              TO* __restrict__ out, int RA, int RB, int k_tiles, long long ldo, int stages, int m_tiles,
+                              int n_tiles, int* __restrict__ error_out) {
+  constexpr int BN = 256;
+  constexpr int B_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)stages * STAGE_BYTES);
+  uint64_t* empty = full + stages;
+  uint64_t* acc_full = empty + stages;   // [2] the tensor cores have finished a tile in accumulator b
+  uint64_t* acc_empty = acc_full + 2;    // [2] the epilogue warps have read accumulator b
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* issued_slot = const_cast<int*>(abort_flag) + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total = m_tiles * n_tiles;
+  const int my_tiles = (int)blockIdx.x < total ? (total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    *issued_slot = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  dep_launch();
+  if (warp == 4) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- producer: TMA loads
+      // The weight tiles of the first stages are asked for before the wait on the previous kernel.
+      const long long n_iter = (long long)my_tiles * k_tiles;
+      const int early = (int)(n_iter < stages ? n_iter : stages);
+      auto coords = [&](long long it, int& a_row0, int& b_row0, int& kt) {
+        const int t = (int)(it / k_tiles);
+        kt = (int)(it - (long long)t * k_tiles);
+        const int tile = blockIdx.x + t * gridDim.x;
+        a_row0 = (tile % m_tiles) * BM;
+        b_row0 = (tile / m_tiles) * BN;
+      };
+      for (int it = 0; it < early; ++it) {
+        int a_row0, b_row0, kt;
+        coords(it, a_row0, b_row0, kt);
+        mbar_expect_tx(&full[it], STAGE_BYTES);
+        tma_load_2d(smem + (size_t)it * STAGE_BYTES + A_BYTES, &map_b, kt * BK, b_row0, &full[it]);
+      }
+      dep_wait();
+      for (int it = 0; it < early; ++it) {
+        int a_row0, b_row0, kt;
+        coords(it, a_row0, b_row0, kt);
+        tma_load_2d(smem + (size_t)it * STAGE_BYTES, &map_a, kt * BK, a_row0, &full[it]);
+      }
+      long long issued = early;
+      bool ok = true;
+      for (long long it = early; it < n_iter && ok; ++it) {
+        const int s = (int)(it % stages);
+        const uint32_t ph = (uint32_t)(it / stages) & 1u;
+        ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag, error_out, ERR_PRODUCER);
+        if (!ok) break;
+        int a_row0, b_row0, kt;
+        coords(it, a_row0, b_row0, kt);
+        uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
+        mbar_expect_tx(&full[s], STAGE_BYTES);
+        tma_load_2d(sa, &map_a, kt * BK, a_row0, &full[s]);
+        tma_load_2d(sa + A_BYTES, &map_b, kt * BK, b_row0, &full[s]);
+        issued = it + 1;
+      }
+      if (!ok || *abort_flag) {
+        // wait (bounded) for the copies already issued, so that none lands after the CTA has left
+        const long long first = issued > stages ? issued - stages : 0;
+        for (long long it = first; it < issued; ++it) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&full[it % stages], (uint32_t)(it / stages) & 1u)) {
+            if (clock64() - t0 > WAIT_CYCLES) {
+              atomicCAS(error_out, 0, ERR_DRAIN);
+              break;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- tensor-core issue
+      constexpr uint32_t idesc = instr_desc(BN);
+      bool ok = true;
+      long long it = 0;
+      for (int t = 0; t < my_tiles && ok; ++t) {
+        const int b = t & 1;
+        if (t >= 2) {  // the epilogue of the tile that used this accumulator two tiles ago
+          ok = mbar_wait(&acc_empty[b], (uint32_t)((t >> 1) - 1) & 1u, abort_flag, error_out, ERR_MMA);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        const uint32_t acc = tmem_base + (uint32_t)(b * BN);
+        for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
+          const int s = (int)(it % stages);
+          const uint32_t ph = (uint32_t)(it / stages) & 1u;
+          ok = mbar_wait(&full[s], ph, abort_flag, error_out, ERR_MMA);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
+          const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            mma_f16(acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          mma_commit(&empty[s]);
+        }
+        if (ok) mma_commit(&acc_full[b]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue: warps 0-3
+    dep_wait();  // no global write before the previous kernels have finished
+    bool ok = true;
+    for (int t = 0; t < my_tiles; ++t) {
+      const int b = t & 1;
+      ok = mbar_wait(&acc_full[b], (uint32_t)(t >> 1) & 1u, abort_flag, error_out, ERR_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);  // a warp reads tensor memory together or not at all
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int tile = blockIdx.x + t * gridDim.x;
+      const int a_row0 = (tile % m_tiles) * BM, b_row0 = (tile / m_tiles) * BN;
+      const int ra = a_row0 + warp * 32 + lane;
+      const uint32_t acc = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(b * BN);
+      if (SWIGLU) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN / 2; c0 += 16) {
+          float gv[16], uv[16];
+          tmem_load16(acc + (uint32_t)c0, gv);
+          tmem_load16(acc + (uint32_t)(c0 + BN / 2), uv);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) gv[i] = (gv[i] / (1.0f + expf(-gv[i]))) * uv[i];
+          const int col0 = b_row0 / 2 + c0;  // column of the activation matrix [tokens, RB / 2]
+          if (ra < RA && col0 < RB / 2) {
+            TO* dst = out + (size_t)ra * ldo + col0;
+            store_row16<TO>(dst, gv, min(16, RB / 2 - col0), (reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          float v[16];
+          tmem_load16(acc + (uint32_t)c0, v);
+          const int rb0 = b_row0 + c0;
+          if (ra < RA && rb0 < RB) {
+            TO* dst = out + (size_t)ra * ldo + rb0;
+            store_row16<TO>(dst, v, min(16, RB - rb0), (reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[b]);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+template <typename TO, bool SWIGLU>
+int launch_tc_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, long long ldo,
+                         int n_sms, cudaStream_t stream) {
+  constexpr int STAGE_BYTES = A_BYTES + 256 * BK * 2;
+  const int k_tiles = (K + BK - 1) / BK;
+  const int stages = 4;
+  const size_t smem = (size_t)stages * STAGE_BYTES + (2 * stages + 4) * sizeof(uint64_t) + 16 + 1024;
+  auto kernel = gemm_tc_persistent_kernel<TO, SWIGLU>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+      llm_set_error("gemm_tc: cannot raise the shared memory limit");
+      return LLM_ERR_LAUNCH;
+    }
+    attr_set = true;
+  }
+  const int m_tiles = (RA + BM - 1) / BM, n_tiles = (RB + 255) / 256;
+  const int grid = std::min(m_tiles * n_tiles, n_sms);
+  launch_kernel(kernel, grid, PERSIST_THREADS, smem, stream, ma, mb, (TO*)out, RA, RB, k_tiles, ldo, stages, m_tiles, n_tiles,
+                error_word());
+  return LLM_OK;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+  }
+  return n;
+}
+
+// The persistent form pays when an SM gets several tiles.
+inline bool use_persistent(int M, int N) { return ((M + BM - 1) / BM) * ((N + 255) / 256) >= 2 * sm_count(); }
+
 template <int BN, bool SWAP, typename TO, bool SWIGLU = false>
 int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, int splits, long long ldo,
               long long split_stride, int stages, cudaStream_t stream) {
@@ -257,8 +483,10 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, i
 }  // namespace
 
 // Tuning knobs of the token-tile form (0 = built-in choice): width of the output tile and ring depth.
-static int g_force_bn = 0, g_force_stages = 0;
+static int g_force_bn = 0, g_force_stages = 0, g_persistent = 1;
 extern "C" void llm_gemm_tc_tune(int bn, int stages) { g_force_bn = bn; g_force_stages = stages; }
+// 0: never the persistent form (for comparisons); 1: where an SM gets at least two tiles.
+extern "C" void llm_gemm_tc_persistent(int on) { g_persistent = on; }
 
 // Number of K splits llm_gemm_tc will really use for (K, wanted splits).
 extern "C" int llm_gemm_tc_splits(int K, int splits) {
@@ -297,7 +525,10 @@ extern "C" int llm_gemm_tc(const void* a, const void* w, void* out, int M, int N
 #define LLM_TC_CASE(BN_)                                                                                                   \
   rc = (out_dtype == LLM_F32) ? launch_tc<BN_, false, float>(ma, mb, out, M, N, K, 1, ldo, 0, std::min(stages, BN_ == 256 ? 4 : 6), stream) \
                               : launch_tc<BN_, false, bf16>(ma, mb, out, M, N, K, 1, ldo, 0, std::min(stages, BN_ == 256 ? 4 : 6), stream)
-    if (bn == 256) LLM_TC_CASE(256);
+    if (bn == 256 && g_persistent && use_persistent(M, N))
+      rc = (out_dtype == LLM_F32) ? launch_tc_persistent<float, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream)
+                                  : launch_tc_persistent<bf16, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream);
+    else if (bn == 256) LLM_TC_CASE(256);
     else if (bn == 128) LLM_TC_CASE(128);
     else if (bn == 64) LLM_TC_CASE(64);
     else if (bn == 32) LLM_TC_CASE(32);
@@ -332,7 +563,9 @@ extern "C" int llm_gemm_tc_swiglu(const void* a, const void* w, void* act, int M
   LLM_REQUIRE(error_word() != nullptr, "gemm_tc_swiglu: cannot allocate the error word");
   CUtensorMap ma, mb;
   LLM_REQUIRE(tensor_map_for(a, M, K, lda, BM, &ma) && tensor_map_for(w, 2 * FF, K, ldw, 256, &mb), "gemm_tc_swiglu: cuTensorMapEncodeTiled failed");
-  const int rc = launch_tc<256, false, bf16, true>(ma, mb, act, M, 2 * FF, K, 1, ld_act, 0, 4, stream);
+  const int rc = (g_persistent && use_persistent(M, 2 * FF))
+                     ? launch_tc_persistent<bf16, true>(ma, mb, act, M, 2 * FF, K, ld_act, sm_count(), stream)
+                     : launch_tc<256, false, bf16, true>(ma, mb, act, M, 2 * FF, K, 1, ld_act, 0, 4, stream);
   if (rc != LLM_OK) return rc;
   LLM_CHECK_LAUNCH("gemm_tc_swiglu");
   return LLM_OK;

@@ -144,6 +144,53 @@ def test_gemm_with_fused_swiglu(ops, M, FF, K):
     assert ops.tensor_core_error() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 25617, 192), (129, 76000, 64), (1100, 8704, 256)])
+def test_gemm_persistent_form(ops, M, N, K):
+    """Enough output tiles that every SM gets several: the persistent kernel (two accumulators in
+    tensor memory, epilogue beside the next tile's products) against float64, tails in every
+    dimension, and against the one-tile-per-CTA kernel bit for bit (same products in the same order)."""
+    a, w = rnd(M, K, dtype=torch.bfloat16, seed=70), rnd(N, K, dtype=torch.bfloat16, seed=71, std=0.1)
+    lib = ops.lib("tensorcore")
+    scale = math.sqrt(K) * 0.1
+    outs = {}
+    for out_dt in (torch.float32, torch.bfloat16):
+        for persistent in (1, 0):
+            lib.llm_gemm_tc_persistent(persistent)
+            try:
+                out = torch.full((M, N), float("nan"), dtype=out_dt, device=DEV)
+                ops.gemm(a, w, out)
+            finally:
+                lib.llm_gemm_tc_persistent(1)
+            outs[(out_dt, persistent)] = out
+        assert torch.equal(outs[(out_dt, 1)], outs[(out_dt, 0)])
+        rows = torch.tensor([0, 1, 127, 128, M - 1])
+        ref = a[rows.to(DEV)].double() @ w.double().t()
+        torch.testing.assert_close(outs[(out_dt, 1)][rows.to(DEV)].double(), ref, **tol(out_dt, scale))
+    assert ops.tensor_core_error() == 0
+
+
+def test_gemm_persistent_form_with_swiglu(ops):
+    from llmengine.engine.context import Workspace
+    M, FF, K = 300, 12800, 128
+    a = rnd(M, K, dtype=torch.bfloat16, seed=72)
+    g, u = rnd(FF, K, dtype=torch.bfloat16, seed=73, std=0.1), rnd(FF, K, dtype=torch.bfloat16, seed=74, std=0.1)
+    blocked = torch.stack([g.view(-1, 128, K), u.view(-1, 128, K)], dim=1).reshape(2 * FF, K).contiguous()
+    lib = ops.lib("tensorcore")
+    outs = []
+    for persistent in (1, 0):
+        lib.llm_gemm_tc_persistent(persistent)
+        try:
+            out = torch.full((M, FF), float("nan"), dtype=torch.bfloat16, device=DEV)
+            ops.gemm_swiglu(a, blocked, out, Workspace(torch.device(DEV)))
+        finally:
+            lib.llm_gemm_tc_persistent(1)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    gf, uf = (a.float() @ g.float().t()).cpu().numpy(), (a.float() @ u.float().t()).cpu().numpy()
+    torch.testing.assert_close(outs[0].float().cpu(), torch.from_numpy(P.silu(gf) * uf), **tol(torch.bfloat16, math.sqrt(K) * 0.1))
+    assert ops.tensor_core_error() == 0
+
+
 def test_silu_mul_partials(ops):
     parts = rnd(3, 5, 2 * 176, seed=54)
     out = torch.empty(5, 176, dtype=torch.bfloat16, device=DEV)
