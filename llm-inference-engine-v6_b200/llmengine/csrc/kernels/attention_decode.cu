@@ -54,23 +54,26 @@ struct DecParams {
   bf16* kcache; bf16* vcache;                                   // where the token's own key and value are written
 };
 
-template <int HD>
+// DEEP: a longer ring for launches that fill the GPU with fewer, latency-bound CTAs; the short ring
+// lets four CTAs (head size 64) share an SM, which is what streams the cache fastest.
+template <int HD, bool DEEP>
 struct DecLayout {
   static constexpr int HALVES = HD / 64;               // 64-element (128-byte) column blocks of a row
   static constexpr int TILE_BYTES = TK * HD * 2;       // one of K or V
   static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-  static constexpr int STAGES = HD == 64 ? 8 : 5;      // 64 KB / 80 KB of ring
+  static constexpr int STAGES = HD == 64 ? (DEEP ? 8 : 6) : (DEEP ? 5 : 4);  // 64 / 48 KB and 80 / 64 KB of ring
+  static_assert(STAGES >= 4, "the consumers' wait on the stage's previous tile needs a ring of at least four stages");
   static constexpr int Q_LD = HD + 8;
 };
 
 // Byte offset of (row, 16-byte chunk) inside a [TK][64] tile written by TMA with 128-byte swizzle.
 __device__ __forceinline__ uint32_t sw128(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
 
-template <int HD, bool FUSED>
+template <int HD, bool FUSED, bool DEEP>
 __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                                  const __grid_constant__ CUtensorMap map_v,
                                                                                  const DecParams p) {
-  using L = DecLayout<HD>;
+  using L = DecLayout<HD, DEEP>;
   constexpr int KSTEPS = HD / 16, DTILES = HD / 8, NS = L::STAGES;
   extern __shared__ uint8_t smem_dyn[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
@@ -255,6 +258,12 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
 
     for (int t = warp; t < n_tiles; t += 4) {
       const int stage = t % NS;
+      // A parity wait tells the current phase from the one before it, not from older ones. When the
+      // ring length is no multiple of the four warps, the tile that used this stage before (t - NS)
+      // belongs to another warp and may not even have landed: wait until it has been consumed
+      // (that phase is at most one behind, since this warp's own tile t - 4 was issued after tile
+      // t - 4 - NS had been consumed), and only then for this tile's copy.
+      if (NS % 4 != 0 && t >= NS && !mbar_wait(&empty[stage], ((t / NS) - 1) & 1, abort_flag, p.error, ERR_DEC_CONSUMER)) break;
       if (!mbar_wait(&full[stage], (t / NS) & 1, abort_flag, p.error, ERR_DEC_CONSUMER)) break;
       const uint32_t kb = smem_u32(ring + (size_t)stage * L::STAGE_BYTES);
       const uint32_t vb = kb + L::TILE_BYTES;
@@ -484,26 +493,34 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
   }
 }
 
-template <int HD>
+template <int HD, bool DEEP>
 size_t decode_smem_bytes(int keys_per_cta, int page_size) {
-  using L = DecLayout<HD>;
+  using L = DecLayout<HD, DEEP>;
   return 1024 + (size_t)L::STAGES * L::STAGE_BYTES + (size_t)ROWS * L::Q_LD * 2 + 2 * L::STAGES * 8 + 16 + 2 * HD * 2 +
          (size_t)((keys_per_cta + 2 * TK) / page_size + 4) * sizeof(int);
 }
 
-template <int HD, bool FUSED>
-int launch_decode(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int n_seqs, cudaStream_t stream) {
+template <int HD, bool FUSED, bool DEEP>
+int launch_decode_ring(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int n_seqs, cudaStream_t stream) {
   const int keys_per_cta = p.n_splits > 1 ? p.split_keys : p.max_blocks * p.page_size;
-  const size_t smem = decode_smem_bytes<HD>(keys_per_cta, p.page_size);
+  const size_t smem = decode_smem_bytes<HD, DEEP>(keys_per_cta, p.page_size);
   if (smem > 200 * 1024) return 2;
   static size_t attr_bytes = 0;  // the largest size asked for so far
   if (smem > attr_bytes) {
-    if (cudaFuncSetAttribute(paged_attention_decode_tma_kernel<HD, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(paged_attention_decode_tma_kernel<HD, FUSED, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return 1;
     attr_bytes = smem;
   }
-  launch_kernel(paged_attention_decode_tma_kernel<HD, FUSED>, dim3(n_seqs, p.nkv, p.n_splits), DEC_THREADS, smem, stream, mk, mv, p);
+  launch_kernel(paged_attention_decode_tma_kernel<HD, FUSED, DEEP>, dim3(n_seqs, p.nkv, p.n_splits), DEC_THREADS, smem, stream, mk, mv, p);
   return 0;
+}
+
+template <int HD, bool FUSED>
+int launch_decode(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int n_seqs, cudaStream_t stream) {
+  // at most three (head size 64) or two (128) CTAs with the long ring fit an SM of 148
+  const long long ctas = (long long)n_seqs * p.nkv * p.n_splits;
+  return ctas <= (HD == 64 ? 444 : 296) ? launch_decode_ring<HD, FUSED, true>(mk, mv, p, n_seqs, stream)
+                                        : launch_decode_ring<HD, FUSED, false>(mk, mv, p, n_seqs, stream);
 }
 
 }  // namespace

@@ -293,18 +293,28 @@ class CudaOps:
                                           _ptr(vcache), c_int(n_tokens), c_int(nq), c_int(nkv), c_int(hd),
                                           c_int(page_size), _stream()), lib)
 
-    # decoding: the key range is cut at absolute multiples of `split_keys` (a multiple of 64) into as
-    # many splits as still fit the GPU in ONE wave of CTAs (three 76 KB CTAs per SM at head size 64)
-    ATTENTION_TARGET_CTAS = 444
+    # decoding: the key range is cut at absolute multiples of `split_keys` (a multiple of 64); see _split_policy
+    ATTENTION_TARGET_CTAS = 592
+    ATTENTION_MAX_SPLITS = 6
+    ATTENTION_MIN_SPLIT_KEYS = 256
     TC_ATTENTION_MIN_TOKENS = 32  # longest portion of the step from which the tcgen05 attention kernel is used
+
+    def _split_policy(self, pairs: int, max_seq_len: int):
+        """-> (number of key splits, keys per split) of a step of single tokens with `pairs` (request,
+        key/value head) pairs. Measured on B200 (head size 64): the cache streams fastest with four
+        CTAs on each of the 148 SMs (592) and no split; with fewer pairs the range is cut to fill
+        those places, but into at most ATTENTION_MAX_SPLITS pieces of at least ATTENTION_MIN_SPLIT_KEYS keys, since every
+        split ends in a partial output and a merge."""
+        want = min(self.ATTENTION_MAX_SPLITS, self.ATTENTION_TARGET_CTAS // max(pairs, 1), max_seq_len // self.ATTENTION_MIN_SPLIT_KEYS)
+        if want <= 1:
+            return 1, 256
+        split_keys = -(-(-(-max_seq_len // want)) // 64) * 64
+        return -(-max_seq_len // split_keys), split_keys
 
     def _decode_splits(self, lib, batch, nq: int, nkv: int, hd: int):
         """How a step of single tokens cuts its key ranges -> (n_splits, split_keys, scratch, counters)."""
-        n_splits, split_keys, scratch, counters = 1, 256, None, None
-        if batch.max_seq_len > 256:
-            want = max(1, self.ATTENTION_TARGET_CTAS // (batch.n_seqs * nkv))
-            split_keys = -(-max(64, -(-batch.max_seq_len // want)) // 64) * 64
-            n_splits = -(-batch.max_seq_len // split_keys)
+        n_splits, split_keys = self._split_policy(batch.n_seqs * nkv, batch.max_seq_len)
+        scratch = counters = None
         if n_splits > 1:
             floats = int(lib.llm_attention_mma_scratch_floats(c_int(batch.n_tokens), c_int(nq), c_int(hd), c_int(n_splits)))
             scratch = batch.ws.get("attention.splits", (floats,), torch.float32)
@@ -322,8 +332,7 @@ class CudaOps:
         if not lib.llm_attention_decode_supported(c_int(nq), c_int(nkv), c_int(hd), c_int(kcache.shape[2]), c_longlong(8),
                                                   c_longlong(out.stride(0))):
             return False
-        want = max(1, self.ATTENTION_TARGET_CTAS // (batch.n_seqs * nkv))
-        return -(-batch.max_seq_len // (-(-max(64, -(-batch.max_seq_len // want)) // 64) * 64)) <= 128
+        return self._split_policy(batch.n_seqs * nkv, batch.max_seq_len)[0] <= 128
 
     def paged_attention_decode_fused(self, parts: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                                      kcache: torch.Tensor, vcache: torch.Tensor, batch, block_table: torch.Tensor,

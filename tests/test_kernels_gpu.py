@@ -311,7 +311,7 @@ def test_paged_attention_tcgen05(ops, nq, nkv, window):
         assert not torch.isnan(out.float()).any()
 
 
-@pytest.mark.parametrize("target_ctas", [1, 444, 100000])  # no split, the usual splits, a split every 64 keys
+@pytest.mark.parametrize("target_ctas", [1, 592, 100000])  # no split, the usual splits, a split every 64 keys
 @pytest.mark.parametrize("nq,nkv,hd,page,window", [(32, 8, 64, 16, 0), (8, 2, 64, 8, 0), (4, 4, 64, 32, 0), (16, 1, 64, 64, 0),
                                                    (8, 2, 64, 16, 150), (8, 4, 128, 16, 0), (2, 2, 128, 32, 70), (6, 2, 128, 8, 0)])
 def test_paged_attention_decode_by_tma(ops, monkeypatch, nq, nkv, hd, page, window, target_ctas):
@@ -321,6 +321,9 @@ def test_paged_attention_decode_by_tma(ops, monkeypatch, nq, nkv, hd, page, wind
     split policy; the same call twice, since the split counters must be left at zero."""
     dt = torch.bfloat16
     monkeypatch.setattr(type(ops), "ATTENTION_TARGET_CTAS", target_ctas)
+    if target_ctas > 1000:
+        monkeypatch.setattr(type(ops), "ATTENTION_MAX_SPLITS", 1000)
+        monkeypatch.setattr(type(ops), "ATTENTION_MIN_SPLIT_KEYS", 64)
     seq_lens = [1, 32, 33, 64, 257, 700, 1024, 16]
     kc, vc, table, dense = _paged_setup(dt, nkv, hd, page, seq_lens, sum((L + page - 1) // page for L in seq_lens) + 3, seed=5)
     if window:  # pages wholly behind the window are no longer the request's
@@ -383,6 +386,31 @@ def test_decode_attention_with_rotation_and_cache_write_folded_in(ops, nq, nkv, 
         ref = _attention_ref(q, K, V, p_, nq, nkv, hd, scale, window)
         torch.testing.assert_close(out2[i].float().cpu(), ref, **tol(dt, 2))
         torch.testing.assert_close(v2[pg, :, off].float().cpu().reshape(-1), summed[i, (nq + nkv) * hd:], atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("hd,n_req", [(64, 80), (128, 40), (64, 20), (128, 12)])
+def test_decode_attention_many_requests(ops, hd, n_req):
+    """Enough (request, kv head) pairs that the short ring is used (four CTAs an SM), and few enough
+    for the long one; contexts of dozens of tiles, so that every stage of the ring is used many
+    times over by different warps (the ring lengths 6, 5 and 3 are no multiples of the four warps)."""
+    nq, nkv, page, dt = 16, 8, 16, torch.bfloat16
+    g = torch.Generator().manual_seed(hd + n_req)
+    seq_lens = torch.randint(900, 1600, (n_req,), generator=g).tolist()
+    kc, vc, table, dense = _paged_setup(dt, nkv, hd, page, seq_lens, sum((L + page - 1) // page for L in seq_lens) + 3, seed=8)
+    b = Batch([(L - 1, 1) for L in seq_lens])
+    q = rnd(b.n_tokens, nq * hd, dtype=dt, seed=27)
+    scale = 1.0 / math.sqrt(hd)
+    outs = []
+    for _ in range(3):  # timing differs from launch to launch; the result must not
+        out = torch.full((b.n_tokens, nq * hd), float("nan"), dtype=dt, device=DEV)
+        ops.paged_attention(q, kc, vc, b, table, out, nq, nkv, hd, scale)
+        outs.append(out)
+    assert ops.tensor_core_error() == 0
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    for i in list(range(0, n_req, max(1, n_req // 6))) + [n_req - 1]:
+        s_, p_ = b.tokens[i]
+        ref = _attention_ref(q[i].cpu().view(nq, hd), dense[s_][0], dense[s_][1], p_, nq, nkv, hd, scale, 0)
+        torch.testing.assert_close(outs[0][i].float().cpu(), ref, **tol(dt, 2))
 
 
 def test_decode_attention_kernels_agree(ops):
