@@ -420,6 +420,268 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// CTA pairs (cta_group::2). Two CTAs of a cluster, on neighbouring SMs, compute one 256 x 256 output
+// tile with ONE tcgen05.mma stream issued by the even CTA (the leader): the instruction reads the
+// 128 A rows that each CTA holds in its own shared memory and the B tile half from each of them
+// (128 of the 256 weight rows), and writes 128 accumulator rows into each CTA's tensor memory. Per
+// k-block a CTA so loads 16 KB of A and 16 KB of B instead of 16 + 32 KB for the same products per SM:
+// the one-CTA kernel is bound by that traffic (tensor pipe busy about half the time).
+//   * both producers wait for their own `empty` barrier and issue their TMA loads with the leader's
+//     `full` barrier as the completion barrier; the leader's producer announces the bytes of both;
+//   * the leader's MMA thread commits every stage to the `empty` barriers of both CTAs, and every
+//     finished tile to both `acc_full` barriers (tcgen05.commit with a CTA mask);
+//   * the epilogue warps of both CTAs drain their own 128 rows and arrive on the leader's
+//     `acc_empty` barrier (8 arrivals);
+//   * nobody leaves before a cluster barrier: a CTA that has exited cannot be arrived on or read.
+// Persistent and double-buffered like the kernel above; waits are bounded the same way.
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void mma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar) {  // arrives on `bar` of both CTAs of the pair
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+               "h"(both)
+               : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// bf16 x bf16 -> f32, both operands K-major, M = 256 over the pair, N = n.
+__host__ __device__ constexpr uint32_t instr_desc_pair(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+template <typename TO, bool SWIGLU>
+__global__ void __launch_bounds__(PERSIST_THREADS)
+    gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TO* __restrict__ out,
+                        int RA, int RB, int k_tiles, long long ldo, int stages, int mp_tiles, int n_tiles,
+                        int* __restrict__ error_out) {
+  constexpr int BN = 256;                  // outputs per tile; each CTA holds BN / 2 weight rows of it
+  constexpr int B_HALF_BYTES = (BN / 2) * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_HALF_BYTES;  // per CTA
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)stages * STAGE_BYTES);  // used in the leader only
+  uint64_t* empty = full + stages;
+  uint64_t* acc_full = empty + stages;   // [2]
+  uint64_t* acc_empty = acc_full + 2;    // [2] used in the leader only: 8 arrivals
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();  // 0: leader
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int total = mp_tiles * n_tiles;
+  const int my_tiles = pair < total ? (total - 1 - pair) / n_pairs + 1 : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);  // four epilogue warps in each CTA of the pair
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  cluster_sync_all();  // the peer's barriers exist before anything arrives on them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  dep_launch();
+  if (warp == 4) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- producer (both CTAs)
+      const long long n_iter = (long long)my_tiles * k_tiles;
+      auto coords = [&](long long it, int& a_row0, int& b_row0, int& kt) {
+        const int t = (int)(it / k_tiles);
+        kt = (int)(it - (long long)t * k_tiles);
+        const int tile = pair + t * n_pairs;
+        a_row0 = (tile % mp_tiles) * 256 + (int)rank * BM;          // this CTA's 128 token rows
+        b_row0 = (tile / mp_tiles) * BN + (int)rank * (BN / 2);      // this CTA's 128 weight rows
+      };
+      const int early = (int)(n_iter < stages ? n_iter : stages);
+      for (int it = 0; it < early; ++it) {  // weights first: they do not depend on the kernel before
+        int a_row0, b_row0, kt;
+        coords(it, a_row0, b_row0, kt);
+        if (rank == 0) mbar_expect_tx(&full[it], 2 * STAGE_BYTES);
+        tma_load_2d_pair(smem + (size_t)it * STAGE_BYTES + A_BYTES, &map_b, kt * BK, b_row0, map_to_cta(smem_u32(&full[it]), 0));
+      }
+      dep_wait();
+      for (int it = 0; it < early; ++it) {
+        int a_row0, b_row0, kt;
+        coords(it, a_row0, b_row0, kt);
+        tma_load_2d_pair(smem + (size_t)it * STAGE_BYTES, &map_a, kt * BK, a_row0, map_to_cta(smem_u32(&full[it]), 0));
+      }
+      long long issued = early;
+      bool ok = true;
+      for (long long it = early; it < n_iter && ok; ++it) {
+        const int s = (int)(it % stages);
+        const uint32_t ph = (uint32_t)(it / stages) & 1u;
+        ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag, error_out, ERR_PRODUCER);
+        if (!ok) break;
+        int a_row0, b_row0, kt;
+        coords(it, a_row0, b_row0, kt);
+        uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
+        const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
+        if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+        tma_load_2d_pair(sa, &map_a, kt * BK, a_row0, bar);
+        tma_load_2d_pair(sa + A_BYTES, &map_b, kt * BK, b_row0, bar);
+        issued = it + 1;
+      }
+      if (rank == 0 && (!ok || *abort_flag)) {
+        // wait (bounded) for the copies of both CTAs that were announced, before anybody leaves
+        const long long first = issued > stages ? issued - stages : 0;
+        for (long long it = first; it < issued; ++it) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&full[it % stages], (uint32_t)(it / stages) & 1u)) {
+            if (clock64() - t0 > WAIT_CYCLES) {
+              atomicCAS(error_out, 0, ERR_DRAIN);
+              break;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0 && rank == 0) {
+      // ---------------------------------------------------------------- tensor-core issue (leader)
+      constexpr uint32_t idesc = instr_desc_pair(BN);
+      bool ok = true;
+      long long it = 0;
+      for (int t = 0; t < my_tiles && ok; ++t) {
+        const int b = t & 1;
+        if (t >= 2) {
+          ok = mbar_wait(&acc_empty[b], (uint32_t)((t >> 1) - 1) & 1u, abort_flag, error_out, ERR_MMA);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        const uint32_t acc = tmem_base + (uint32_t)(b * BN);
+        for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
+          const int s = (int)(it % stages);
+          const uint32_t ph = (uint32_t)(it / stages) & 1u;
+          ok = mbar_wait(&full[s], ph, abort_flag, error_out, ERR_MMA);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
+          const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            mma_f16_pair(acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          mma_commit_pair(&empty[s]);
+        }
+        if (ok) mma_commit_pair(&acc_full[b]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue: warps 0-3 of both CTAs
+    dep_wait();
+    bool ok = true;
+    for (int t = 0; t < my_tiles; ++t) {
+      const int b = t & 1;
+      ok = mbar_wait(&acc_full[b], (uint32_t)(t >> 1) & 1u, abort_flag, error_out, ERR_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int tile = pair + t * n_pairs;
+      const int a_row0 = (tile % mp_tiles) * 256 + (int)rank * BM, b_row0 = (tile / mp_tiles) * BN;
+      const int ra = a_row0 + warp * 32 + lane;
+      const uint32_t acc = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(b * BN);
+      if (SWIGLU) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN / 2; c0 += 16) {
+          float gv[16], uv[16];
+          tmem_load16(acc + (uint32_t)c0, gv);
+          tmem_load16(acc + (uint32_t)(c0 + BN / 2), uv);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) gv[i] = (gv[i] / (1.0f + expf(-gv[i]))) * uv[i];
+          const int col0 = b_row0 / 2 + c0;
+          if (ra < RA && col0 < RB / 2) {
+            TO* dst = out + (size_t)ra * ldo + col0;
+            store_row16<TO>(dst, gv, min(16, RB / 2 - col0), (reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          float v[16];
+          tmem_load16(acc + (uint32_t)c0, v);
+          const int rb0 = b_row0 + c0;
+          if (ra < RA && rb0 < RB) {
+            TO* dst = out + (size_t)ra * ldo + rb0;
+            store_row16<TO>(dst, v, min(16, RB - rb0), (reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&acc_empty[b]), 0));
+    }
+  }
+  __syncwarp();  // lanes of the producer and issue warps went different ways; the cluster barrier wants whole warps
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  cluster_sync_all();  // both CTAs are done with each other's shared memory, tensor memory and barriers
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+template <typename TO, bool SWIGLU>
+int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, long long ldo, int n_sms,
+                   cudaStream_t stream) {
+  constexpr int STAGE_BYTES = A_BYTES + 128 * BK * 2;
+  const int k_tiles = (K + BK - 1) / BK;
+  const int stages = 6;
+  const size_t smem = (size_t)stages * STAGE_BYTES + (2 * stages + 4) * sizeof(uint64_t) + 16 + 1024;
+  auto kernel = gemm_tc_pair_kernel<TO, SWIGLU>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+      llm_set_error("gemm_tc: cannot raise the shared memory limit");
+      return LLM_ERR_LAUNCH;
+    }
+    attr_set = true;
+  }
+  const int mp_tiles = (RA + 255) / 256, n_tiles = (RB + 255) / 256;
+  const int pairs = std::min(mp_tiles * n_tiles, n_sms / 2);
+  launch_kernel_cluster(kernel, 2 * pairs, PERSIST_THREADS, smem, 2, stream, ma, mb, (TO*)out, RA, RB, k_tiles, ldo, stages, mp_tiles,
+                        n_tiles, error_word());
+  return LLM_OK;
+}
+
 template <typename TO, bool SWIGLU>
 int launch_tc_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, long long ldo,
                          int n_sms, cudaStream_t stream) {
@@ -483,7 +745,9 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, i
 }  // namespace
 
 // Tuning knobs of the token-tile form (0 = built-in choice): width of the output tile and ring depth.
-static int g_force_bn = 0, g_force_stages = 0, g_persistent = 1;
+static int g_force_bn = 0, g_force_stages = 0, g_persistent = 1, g_pair = 0;
+// 1: CTA pairs (cta_group::2) for products of more than 128 tokens and at least 256 outputs.
+extern "C" void llm_gemm_tc_pair(int on) { g_pair = on; }
 extern "C" void llm_gemm_tc_tune(int bn, int stages) { g_force_bn = bn; g_force_stages = stages; }
 // 0: never the persistent form (for comparisons); 1: where an SM gets at least two tiles.
 extern "C" void llm_gemm_tc_persistent(int on) { g_persistent = on; }
@@ -525,7 +789,11 @@ extern "C" int llm_gemm_tc(const void* a, const void* w, void* out, int M, int N
 #define LLM_TC_CASE(BN_)                                                                                                   \
   rc = (out_dtype == LLM_F32) ? launch_tc<BN_, false, float>(ma, mb, out, M, N, K, 1, ldo, 0, std::min(stages, BN_ == 256 ? 4 : 6), stream) \
                               : launch_tc<BN_, false, bf16>(ma, mb, out, M, N, K, 1, ldo, 0, std::min(stages, BN_ == 256 ? 4 : 6), stream)
-    if (bn == 256 && g_persistent && use_persistent(M, N))
+    if (bn == 256 && g_pair && M > BM) {
+      LLM_REQUIRE(tensor_map_for(w, N, K, ldw, 128, &mb), "gemm_tc: cuTensorMapEncodeTiled failed");
+      rc = (out_dtype == LLM_F32) ? launch_tc_pair<float, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream)
+                                  : launch_tc_pair<bf16, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream);
+    } else if (bn == 256 && g_persistent && use_persistent(M, N))
       rc = (out_dtype == LLM_F32) ? launch_tc_persistent<float, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream)
                                   : launch_tc_persistent<bf16, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream);
     else if (bn == 256) LLM_TC_CASE(256);
@@ -563,6 +831,13 @@ extern "C" int llm_gemm_tc_swiglu(const void* a, const void* w, void* act, int M
   LLM_REQUIRE(error_word() != nullptr, "gemm_tc_swiglu: cannot allocate the error word");
   CUtensorMap ma, mb;
   LLM_REQUIRE(tensor_map_for(a, M, K, lda, BM, &ma) && tensor_map_for(w, 2 * FF, K, ldw, 256, &mb), "gemm_tc_swiglu: cuTensorMapEncodeTiled failed");
+  if (g_pair && M > BM) {
+    LLM_REQUIRE(tensor_map_for(w, 2 * FF, K, ldw, 128, &mb), "gemm_tc_swiglu: cuTensorMapEncodeTiled failed");
+    const int rc2 = launch_tc_pair<bf16, true>(ma, mb, act, M, 2 * FF, K, ld_act, sm_count(), stream);
+    if (rc2 != LLM_OK) return rc2;
+    LLM_CHECK_LAUNCH("gemm_tc_swiglu");
+    return LLM_OK;
+  }
   const int rc = (g_persistent && use_persistent(M, 2 * FF))
                      ? launch_tc_persistent<bf16, true>(ma, mb, act, M, 2 * FF, K, ld_act, sm_count(), stream)
                      : launch_tc<256, false, bf16, true>(ma, mb, act, M, 2 * FF, K, 1, ld_act, 0, 4, stream);

@@ -59,11 +59,22 @@ def run_gemm(args) -> dict:
     ws = [(torch.randn(N, K, device=dev) * 0.02).bfloat16() for _ in range(copies)]
     a = torch.randn(M, K, device=dev).bfloat16()
     space = Workspace(dev)
-    sec = _time(lambda i: ops.gemm_partials(a, ws[i % copies], space, "bench"), args.reps)
-    parts = ops.gemm_partials(a, ws[0], space, "bench")
+    out_kind = getattr(args, "out", "partials")
+    if out_kind == "swiglu":  # w as gate|up blocks of 128 rows; the output is silu(gate) * up, bfloat16 [M, N / 2]
+        act = torch.empty(M, N // 2, device=dev, dtype=torch.bfloat16)
+        sec = _time(lambda i: ops.gemm_swiglu(a, ws[i % copies], act, space), args.reps)
+        splits, out_bytes = 1, act.numel() * 2
+    elif out_kind == "bf16":
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        sec = _time(lambda i: ops.gemm(a, ws[i % copies], out, space), args.reps)
+        splits, out_bytes = 1, out.numel() * 2
+    else:  # float32 partial sums [splits, M, N], as the products before a norm are asked for
+        sec = _time(lambda i: ops.gemm_partials(a, ws[i % copies], space, "bench"), args.reps)
+        parts = ops.gemm_partials(a, ws[0], space, "bench")
+        splits, out_bytes = parts.shape[0], parts.numel() * 4
     assert ops.tensor_core_error() == 0
-    flops, nbytes = 2.0 * M * N * K, N * K * 2 + M * K * 2 + parts.numel() * 4
-    return {"kernel": "gemm_tc", "M": M, "N": N, "K": K, "k_splits": parts.shape[0], "us": round(sec * 1e6, 2),
+    flops, nbytes = 2.0 * M * N * K, N * K * 2 + M * K * 2 + out_bytes
+    return {"kernel": "gemm_tc", "out": out_kind, "M": M, "N": N, "K": K, "k_splits": splits, "us": round(sec * 1e6, 2),
             "tflops": round(flops / sec / 1e12, 1), "gbs": round(nbytes / sec / 1e9, 1)}
 
 
@@ -172,6 +183,8 @@ def main(argv=None) -> int:
     g = sub.add_parser("gemm")
     g.add_argument("--m", type=int, default=8); g.add_argument("--n", type=int, default=16384); g.add_argument("--k", type=int, default=2048)
     g.add_argument("--reps", type=int, default=20)
+    g.add_argument("--out", choices=["partials", "bf16", "swiglu"], default="partials",
+                   help="what the product writes: float32 partial sums, bfloat16, or silu(gate)*up in bfloat16")
     a = sub.add_parser("attention")
     a.add_argument("--batch", type=int, default=8); a.add_argument("--context", type=int, default=2048); a.add_argument("--new", type=int, default=1)
     a.add_argument("--heads", type=int, default=32); a.add_argument("--kv-heads", type=int, default=8); a.add_argument("--head-dim", type=int, default=64)

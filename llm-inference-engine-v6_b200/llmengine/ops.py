@@ -73,6 +73,12 @@ class CudaOps:
             self._libs[name] = lib
         return lib
 
+    def use_cta_pairs(self, on: bool) -> None:
+        """Products of more than 128 tokens on CTA pairs (tcgen05 cta_group::2: two SMs share one
+        256 x 256 tile and each loads half of the weight tile). Off by default: measured on B200 it
+        is 0 to 25 % slower than the one-CTA persistent kernel at the sizes of this model."""
+        self.lib("tensorcore").llm_gemm_tc_pair(c_int(1 if on else 0))
+
     def _check(self, rc: int, lib) -> None:
         self.launches += 1
         if rc != 0:

@@ -169,6 +169,42 @@ def test_gemm_persistent_form(ops, M, N, K):
     assert ops.tensor_core_error() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 25617, 192), (1100, 8704, 256), (129, 512, 2048)])
+def test_gemm_on_cta_pairs(ops, M, N, K):
+    """The cta_group::2 kernel (two CTAs of a cluster on one 256 x 256 tile, one MMA stream, each CTA
+    loading half of the weight tile): same products in the same order as the one-CTA kernels, so the
+    float32 results are equal bit for bit; tails in every dimension; an odd number of 128-row tiles."""
+    from llmengine.engine.context import Workspace
+    a, w = rnd(M, K, dtype=torch.bfloat16, seed=75), rnd(N, K, dtype=torch.bfloat16, seed=76, std=0.1)
+    outs = {}
+    for out_dt in (torch.float32, torch.bfloat16):
+        for pairs in (True, False):
+            ops.use_cta_pairs(pairs)
+            try:
+                out = torch.full((M, N), float("nan"), dtype=out_dt, device=DEV)
+                ops.gemm(a, w, out)
+            finally:
+                ops.use_cta_pairs(False)
+            outs[(out_dt, pairs)] = out
+        assert torch.equal(outs[(out_dt, True)], outs[(out_dt, False)])
+    rows = torch.tensor([0, 127, 128, M - 1]).to(DEV)
+    torch.testing.assert_close(outs[(torch.float32, True)][rows].double(), a[rows].double() @ w.double().t(),
+                               **tol(torch.float32, math.sqrt(K) * 0.1))
+    if N % 256 == 0:  # silu(gate) * up from the pair kernel's epilogue
+        FF = N // 2
+        acts = []
+        for pairs in (True, False):
+            ops.use_cta_pairs(pairs)
+            try:
+                act = torch.full((M, FF), float("nan"), dtype=torch.bfloat16, device=DEV)
+                ops.gemm_swiglu(a, w, act, Workspace(torch.device(DEV)))
+            finally:
+                ops.use_cta_pairs(False)
+            acts.append(act)
+        assert torch.equal(acts[0], acts[1])
+    assert ops.tensor_core_error() == 0
+
+
 def test_gemm_persistent_form_with_swiglu(ops):
     from llmengine.engine.context import Workspace
     M, FF, K = 300, 12800, 128
