@@ -13,14 +13,14 @@ from tiny import (TINY, make_model_dir, random_ids, round64, run_trace, trace_mi
 pytestmark = pytest.mark.gpu
 
 LENS = {"a": [5, 64, 33, 97, 128], "b": [2, 23, 64, 150, 255, 201],  # short ones first: four are live at once
-        "c": [3, 40, 64, 130, 299], "d": [7, 50, 64, 200, 511, 300]}
+        "c": [3, 40, 64, 130, 299], "d": [7, 50, 64, 200, 511, 300], "e": [4, 33, 60, 399, 260]}
 # float32: the engine's own arithmetic is float32 throughout; the plain implementation differs by
 # summation order only. bfloat16: weights are the same bf16 values on both sides; the difference is
 # the rounding of activations to bf16 between kernels.
 TOL = {"float32": 2e-4, "bfloat16": 6e-2}
 
 
-@pytest.fixture(scope="module", params=[(n, d) for n in ("a", "b", "c", "d") for d in ("float32", "bfloat16")],
+@pytest.fixture(scope="module", params=[(n, d) for n in ("a", "b", "c", "d", "e") for d in ("float32", "bfloat16")],
                 ids=lambda p: f"{p[0]}-{p[1]}")
 def replayed(request, tmp_path_factory):
     name, dtype = request.param
@@ -79,3 +79,31 @@ def test_mixed_trace_is_really_mixed(replayed):
     assert max(len(s["entries"]) for s in t.steps) == 4
     assert any(len({len(e["tokens"]) == 1 for e in s["entries"]}) == 2 for s in t.steps)
     assert any(len(e["tokens"]) == 2 for s in t.steps for e in s["entries"])
+
+
+def test_requests_that_start_after_others_ended_are_new_requests(tmp_path):
+    """Three live requests, the first ends, a fourth starts beside the two that go on, and the first
+    one's NAME comes back for other tokens: nobody continues anybody else's cache."""
+    cfg, page = TINY["a"]
+    d = str(tmp_path / "m")
+    make_model_dir(d, cfg, torch.float32)
+    pc, pw = P.read_model(d)
+    V = cfg["vocab_size"]
+    ids = {k: random_ids(n, V, 300 + i) for i, (k, n) in enumerate([("a", 9), ("b", 14), ("c", 12), ("d", 10), ("a2", 7)])}
+    plain = {k: P.forward_logits(pc, pw, v) for k, v in ids.items()}
+    t = Trace()
+    t.add([("a", ids["a"][:5], range(5), 0), ("b", ids["b"][:6], range(6), 0), ("c", ids["c"][:4], range(4), 0)])
+    t.add([("a", ids["a"][5:], range(4), 5), ("b", ids["b"][6:8], range(2), 6)], end=["a"])
+    t.add([("d", ids["d"][:7], range(7), 0), ("c", ids["c"][4:], range(8), 4), ("b", ids["b"][8:], range(6), 8)], end=["c"])
+    t.add([("a", ids["a2"], range(7), 0), ("d", ids["d"][7:], range(3), 7)], end=["a", "b", "d"])  # "a" again: a new request
+    t.rows = {}  # read the files by step below: the name "a" stands for two requests
+    run_trace(d, "float32", t, str(tmp_path / "out"), 4 * 64, page, V)
+    import os
+    def step_rows(k):
+        return np.fromfile(os.path.join(str(tmp_path / "out"), f"{k}.f32"), dtype="<f4").reshape(-1, V)
+    s0, s1, s2, s3 = (step_rows(k) for k in range(4))
+    np.testing.assert_allclose(np.concatenate([s0[:5], s1[:4]]), plain["a"], atol=2e-4, rtol=0)
+    np.testing.assert_allclose(np.concatenate([s0[5:11], s1[4:6], s2[15:21]]), plain["b"], atol=2e-4, rtol=0)
+    np.testing.assert_allclose(np.concatenate([s0[11:15], s2[7:15]]), plain["c"], atol=2e-4, rtol=0)
+    np.testing.assert_allclose(np.concatenate([s2[:7], s3[7:10]]), plain["d"], atol=2e-4, rtol=0)
+    np.testing.assert_allclose(s3[:7], plain["a2"], atol=2e-4, rtol=0)

@@ -39,7 +39,11 @@ TINY_D = dict(architectures=["LlamaForCausalLM"], hidden_size=256, intermediate_
               max_position_embeddings=512, rms_norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=True,
               rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
                                 original_max_position_embeddings=128))
-TINY = {"a": (TINY_A, 4), "b": (TINY_B, 16), "c": (TINY_C, 16), "d": (TINY_D, 16)}  # name -> (config.json, page size)
+# E: head 128 (its own instantiations of the attention kernels), a group of 3, pages of 32.
+TINY_E = dict(architectures=["LlamaForCausalLM"], hidden_size=192, intermediate_size=320, num_hidden_layers=2,
+              num_attention_heads=3, num_key_value_heads=1, head_dim=128, vocab_size=777,
+              max_position_embeddings=400, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False)
+TINY = {"a": (TINY_A, 4), "b": (TINY_B, 16), "c": (TINY_C, 16), "d": (TINY_D, 16), "e": (TINY_E, 32)}  # name -> (config.json, page size)
 
 # Weights are wider than a trained model's (std 0.05) so that logits are well apart and a wrong
 # key, page or position shows as a large error.
