@@ -107,3 +107,25 @@ def test_requests_that_start_after_others_ended_are_new_requests(tmp_path):
     np.testing.assert_allclose(np.concatenate([s0[11:15], s2[7:15]]), plain["c"], atol=2e-4, rtol=0)
     np.testing.assert_allclose(np.concatenate([s2[:7], s3[7:10]]), plain["d"], atol=2e-4, rtol=0)
     np.testing.assert_allclose(s3[:7], plain["a2"], atol=2e-4, rtol=0)
+
+
+@pytest.mark.parametrize("name,dtype,seed", [("a", "float32", 1), ("d", "bfloat16", 2), ("b", "float32", 3), ("d", "float32", 4)])
+def test_random_mixed_traces(tmp_path, name, dtype, seed):
+    """Other lengths, orders and cuts than the fixture's: ten requests of random length through a
+    pool that holds about three of them, so that every page is used several times over."""
+    cfg, page = TINY[name]
+    d = str(tmp_path / "m")
+    make_model_dir(d, cfg, torch.float32 if dtype == "float32" else torch.bfloat16, seed=20 + seed)
+    pc, pw = P.read_model(d)
+    rng = np.random.default_rng(seed)
+    top = min(cfg["max_position_embeddings"], 200)
+    lens = [int(n) for n in rng.integers(2, top, 10)]
+    reqs = {f"q{i}": random_ids(n, cfg["vocab_size"], 500 + 10 * seed + i) for i, n in enumerate(lens)}
+    max_tokens = round64(max(lens)) + 2 * 64
+    t = trace_mixed(reqs, max_tokens, seed=seed)
+    rows = run_trace(d, dtype, t, str(tmp_path / "out"), max_tokens, page, cfg["vocab_size"])
+    assert len(rows) == sum(lens)
+    for k, ids in reqs.items():
+        ref = P.forward_logits(pc, pw, ids)
+        got = np.stack([rows[(k, p)] for p in range(len(ids))])
+        np.testing.assert_allclose(got, ref, atol=TOL[dtype], rtol=0, err_msg=f"request {k} of {len(ids)} tokens")
