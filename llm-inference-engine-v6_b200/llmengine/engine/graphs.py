@@ -31,6 +31,7 @@ class _Captured:
 
 class DecodeGraphs:
     BLOCK_BUCKET = 16  # block-table widths are rounded up to this many pages (one graph per width)
+    MAX_GRAPHS = 48    # each graph owns its workspace (75 MB at 64 requests of this model): the oldest go first
 
     def __init__(self, engine):
         self.engine = engine
@@ -86,6 +87,16 @@ class DecodeGraphs:
         c.refill = lambda entries: c.buffers.refill(eng.cm, entries, layout, eng.spec.vocab_size, eng.max_pos)
         return c
 
+    def _graph_for(self, cap: int, blocks: int) -> _Captured:
+        c = self.captured.pop((cap, blocks), None)
+        if c is None:
+            c = self._capture(cap, blocks)  # about 15 ms
+            while len(self.captured) >= self.MAX_GRAPHS:
+                torch.cuda.current_stream().synchronize()  # nothing of the oldest graph is still running
+                del self.captured[next(iter(self.captured))]
+        self.captured[(cap, blocks)] = c  # most recently used last
+        return c
+
     def run(self, entries) -> List[int]:
         """entries: every request brings exactly one token and wants its logits."""
         eng = self.engine
@@ -93,10 +104,7 @@ class DecodeGraphs:
         tokens, seqs, rows, blocks = H.step_caps(eng.cm, entries)
         cap = self._capacity(seqs)
         blocks = (blocks + self.BLOCK_BUCKET - 1) // self.BLOCK_BUCKET * self.BLOCK_BUCKET
-        c = self.captured.get((cap, blocks))
-        if c is None:
-            c = self._capture(cap, blocks)
-            self.captured[(cap, blocks)] = c
+        c = self._graph_for(cap, blocks)
         c.refill(entries)
         c.graph.replay()
         eng.ops.launches += c.kernels
@@ -112,10 +120,7 @@ class DecodeGraphs:
         tokens, seqs, rows, blocks = H.step_caps(eng.cm, entries)
         cap = self._capacity(seqs)
         blocks = (blocks + self.BLOCK_BUCKET - 1) // self.BLOCK_BUCKET * self.BLOCK_BUCKET
-        c = self.captured.get((cap, blocks))
-        if c is None:
-            c = self._capture(cap, blocks)
-            self.captured[(cap, blocks)] = c
+        c = self._graph_for(cap, blocks)
         c.refill(entries)
         c.graph.replay()
         eng.ops.launches += c.kernels
