@@ -1,8 +1,9 @@
 // Causal grouped-query attention of prompt portions on the 5th-generation tensor cores.
 //
 // A CTA owns 128 rows = (query token, query head of the group) pairs that share one key/value
-// head, i.e. 128/group tokens of one request, and walks the request's cached keys in tiles of 128
-// (absolute positions), fetched page by page with TMA through the block table:
+// head, i.e. 128/group tokens of one request, and walks the request's cached keys in tiles of KEYS
+// (absolute positions; 128 keys at head size 64, 64 keys at head size 128, so that two CTAs fit an
+// SM either way), fetched page by page with TMA through the block table:
 //
 //   S = Q K^T        tcgen05.mma, Q and K in shared memory (128-byte swizzle), S in tensor memory
 //   softmax          thread t owns row t: it reads its 128 scores from tensor memory, masks them by
@@ -15,8 +16,10 @@
 // Warps 0-3 are the softmax threads; one thread of a fifth warp issues the TMA loads and the MMAs
 // and runs ahead of them (the next tile's S = Q K^T is queued right behind the current P V), the
 // two sides meeting only at mbarriers; two CTAs per SM fill each other's gaps. Every
-// wait on an mbarrier is bounded (see tc_common.cuh). head_dim 64, page sizes that are multiples
-// of 8 and divide 128, group sizes that divide 128; the caller uses the mma.sync kernel otherwise.
+// wait on an mbarrier is bounded (see tc_common.cuh). head_dim 64 or 128 (rows of 128 dims are two
+// 64-dim blocks of 128-byte swizzled rows: Q K^T runs over both, P V is one product per block),
+// page sizes that are multiples of 8 and divide the tile, groups of up to 128 heads (a CTA takes
+// floor(128 / group) tokens; rows beyond them are padding); the caller uses the mma.sync kernel otherwise.
 //
 // Formula: the reference's attention_f32 (src/kernels.cpp:413-474): kv head = q head / group,
 // score = (q . k) * scale applied after the dot, softmax in float32, weighted sum of values.
@@ -26,11 +29,19 @@
 
 namespace {
 
-constexpr int HD = 64;
-constexpr int ROWS = 128, KEYS = 128;
-constexpr int Q_BYTES = ROWS * HD * 2, KV_BYTES = KEYS * HD * 2;
-constexpr int S_COL = 0, P_COL = 128, O_COL = 192, TMEM_COLS_ATT = 256;
+constexpr int ROWS = 128;
+constexpr int TMEM_COLS_ATT = 256;
 enum : int { ERR_ATT_KV = 11, ERR_ATT_S = 12, ERR_ATT_O = 13 };
+
+template <int HD_>
+struct AttLayout {
+  static constexpr int HD = HD_;
+  static constexpr int KEYS = HD == 64 ? 128 : 64;   // keys per tile
+  static constexpr int DBLK = HD / 64;               // 64-dim blocks of a row
+  static constexpr int Q_BYTES = ROWS * HD * 2, KV_BYTES = KEYS * HD * 2;  // KV_BYTES: one of K or V of a tile
+  static constexpr int S_COL = 0, P_COL = KEYS, O_COL = KEYS + KEYS / 2;   // tensor-memory columns: S f32, P bf16 pairs, O f32
+  static_assert(O_COL + HD <= TMEM_COLS_ATT, "the accumulators do not fit the allocation");
+};
 
 struct AttnTcParams {
   const bf16* q; long long ld_q;
@@ -93,17 +104,21 @@ __host__ __device__ constexpr uint32_t instr_desc_att(int n, bool b_mn_major) {
 
 constexpr int ATT_THREADS = 160;  // warps 0-3: one softmax thread per row; warp 4: one thread issues TMA and MMA
 
+template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 200 registers a thread
     paged_attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const AttnTcParams p) {
+  using L = AttLayout<HD>;
+  constexpr int KEYS = L::KEYS, DBLK = L::DBLK, Q_BYTES = L::Q_BYTES, KV_BYTES = L::KV_BYTES;
+  constexpr int S_COL = L::S_COL, P_COL = L::P_COL, O_COL = L::O_COL;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* q_s = smem;                  // [128 rows][128 B], 128-byte swizzle
-  uint8_t* kv_s = smem + Q_BYTES;       // [2 stages][K 16 KB | V 16 KB], rows of 128 B, 128-byte swizzle
+  uint8_t* q_s = smem;                  // [DBLK blocks][128 rows][128 B], 128-byte swizzle
+  uint8_t* kv_s = smem + Q_BYTES;       // [2 stages][K | V], each [DBLK blocks][KEYS rows][128 B], 128-byte swizzle
   uint64_t* full = reinterpret_cast<uint64_t*>(kv_s + 4 * KV_BYTES);  // [2] keys and values of a tile have landed
   uint64_t* s_bar = full + 2;           // the scores of a tile are in tensor memory
   uint64_t* p_bar = s_bar + 1;          // all 128 rows of P are in tensor memory (128 arrivals)
   uint64_t* o_bar = p_bar + 1;          // the P V product of a tile is done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_bar + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_bar + 2);  // (one spare word keeps the ints after it 16-byte aligned)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* page_s = reinterpret_cast<int*>(tmem_slot + 4);  // the tile range's slice of the block table
 
@@ -156,18 +171,19 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
   // ---- Q rows -> shared memory in the swizzled K-major layout (16-byte chunk c of row r at c ^ (r % 8))
   if (tid < ROWS) {
     const int r = tid;
-    uint4 vals[8];
+    uint4 vals[HD / 8];
     if (r < n_rows) {
       const int tq = r / g, hg = r % g;
       const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)(tok_base + tq) * p.ld_q + (size_t)(kvh * g + hg) * HD);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) vals[c] = src[c];
+      for (int c = 0; c < HD / 8; ++c) vals[c] = src[c];
     } else {
 #pragma unroll
-      for (int c = 0; c < 8; ++c) vals[c] = make_uint4(0, 0, 0, 0);
+      for (int c = 0; c < HD / 8; ++c) vals[c] = make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
-    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(q_s + r * 128 + ((c ^ (r & 7)) << 4)) = vals[c];
+    for (int c = 0; c < HD / 8; ++c)
+      *reinterpret_cast<uint4*>(q_s + (c / 8) * (ROWS * 128) + r * 128 + (((c % 8) ^ (r & 7)) << 4)) = vals[c];
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to TMA / MMA
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -190,16 +206,21 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
         for (int pg = 0; pg < n_pages; ++pg) {
           const int page = page_s[(first_key + pg * p.page_size) / p.page_size - page_lo];
           const int row = (page * p.nkv + kvh) * p.page_size;
-          tma_load_2d(ks + (size_t)pg * p.page_size * 128, &map_k, 0, row, &full[i & 1]);
-          tma_load_2d(vs + (size_t)pg * p.page_size * 128, &map_v, 0, row, &full[i & 1]);
+#pragma unroll
+          for (int b = 0; b < DBLK; ++b) {
+            tma_load_2d(ks + b * (KEYS * 128) + (size_t)pg * p.page_size * 128, &map_k, b * 64, row, &full[i & 1]);
+            tma_load_2d(vs + b * (KEYS * 128) + (size_t)pg * p.page_size * 128, &map_v, b * 64, row, &full[i & 1]);
+          }
         }
       };
       auto issue_scores = [&](int i) {  // S = Q K^T of tile i
-        const uint64_t dq = smem_desc_sw128(smem_u32(q_s));
-        const uint64_t dk = smem_desc_sw128(smem_u32(kv_s + (size_t)(i & 1) * 2 * KV_BYTES));
         constexpr uint32_t idesc_s = instr_desc_att(KEYS, false);
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) mma_f16(tmem_base + S_COL, dq + (uint64_t)(2 * k), dk + (uint64_t)(2 * k), idesc_s, k > 0 ? 1u : 0u);
+        for (int k = 0; k < HD / 16; ++k) {  // 16 dims a step: block k / 4, 32 bytes further along the swizzled row each step
+          const uint64_t dq = smem_desc_sw128(smem_u32(q_s + (k / 4) * (ROWS * 128)));
+          const uint64_t dk = smem_desc_sw128(smem_u32(kv_s + (size_t)(i & 1) * 2 * KV_BYTES + (k / 4) * (KEYS * 128)));
+          mma_f16(tmem_base + S_COL, dq + (uint64_t)(2 * (k % 4)), dk + (uint64_t)(2 * (k % 4)), idesc_s, k > 0 ? 1u : 0u);
+        }
         mma_commit(s_bar);
       };
       issue_tile(0);
@@ -214,12 +235,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
         ok = mbar_wait(p_bar, (uint32_t)i & 1u, abort_flag, p.error_out, ERR_ATT_S);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t dv = smem_desc_sw128(smem_u32(kv_s + (size_t)(i & 1) * 2 * KV_BYTES + KV_BYTES));
-        constexpr uint32_t idesc_o = instr_desc_att(HD, true);
+        constexpr uint32_t idesc_o = instr_desc_att(64, true);
 #pragma unroll
-        for (int k = 0; k < KEYS / 16; ++k)  // 16 keys = 16 rows of 128 B further down the V stage; 8 columns further along P
-          mma_f16_ts(tmem_base + O_COL, tmem_base + P_COL + (uint32_t)(k * 8), dv + (uint64_t)(k * (16 * 128 >> 4)), idesc_o,
-                     (i > 0 || k > 0) ? 1u : 0u);
+        for (int b = 0; b < DBLK; ++b) {  // one product per 64-dim block of V: 64 columns of O each
+          const uint64_t dv = smem_desc_sw128(smem_u32(kv_s + (size_t)(i & 1) * 2 * KV_BYTES + KV_BYTES + b * (KEYS * 128)));
+#pragma unroll
+          for (int k = 0; k < KEYS / 16; ++k)  // 16 keys = 16 rows of 128 B further down the V block; 8 columns further along P
+            mma_f16_ts(tmem_base + O_COL + (uint32_t)(b * 64), tmem_base + P_COL + (uint32_t)(k * 8), dv + (uint64_t)(k * (16 * 128 >> 4)),
+                       idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+        }
         mma_commit(o_bar);
         if (i + 1 < n_tiles) {  // the next tile's scores go to the tensor pipe right behind this product
           ok = mbar_wait(&full[(i + 1) & 1], (uint32_t)((i + 1) >> 1) & 1u, abort_flag, p.error_out, ERR_ATT_KV);
@@ -285,18 +309,21 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
       }
       l_run = l_run * alpha + sum;
       m_run = m_new;
-      tmem_store32(tmem_base + lane_base + P_COL, packed);
-      tmem_store32(tmem_base + lane_base + P_COL + 32, packed + 32);
-      if (i > 0 && __any_sync(0xffffffffu, move)) {  // rescale the warp's rows of O (the previous product is done: s_bar came after it)
-        float o[HD];
-        tmem_load32(tmem_base + lane_base + O_COL, o);
-        tmem_load32(tmem_base + lane_base + O_COL + 32, o + 32);
-        tmem_load_wait();
-        uint32_t ou[HD];
 #pragma unroll
-        for (int d = 0; d < HD; ++d) ou[d] = __float_as_uint(o[d] * alpha);
-        tmem_store32(tmem_base + lane_base + O_COL, ou);
-        tmem_store32(tmem_base + lane_base + O_COL + 32, ou + 32);
+      for (int c = 0; c < KEYS / 64; ++c) tmem_store32(tmem_base + lane_base + P_COL + c * 32, packed + c * 32);
+      if (i > 0 && __any_sync(0xffffffffu, move)) {  // rescale the warp's rows of O (the previous product is done: s_bar came after it)
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c) {  // 64 columns at a time keeps the registers within the two-CTA budget
+          float o[64];
+          tmem_load32(tmem_base + lane_base + O_COL + c * 64, o);
+          tmem_load32(tmem_base + lane_base + O_COL + c * 64 + 32, o + 32);
+          tmem_load_wait();
+          uint32_t ou[64];
+#pragma unroll
+          for (int d = 0; d < 64; ++d) ou[d] = __float_as_uint(o[d] * alpha);
+          tmem_store32(tmem_base + lane_base + O_COL + c * 64, ou);
+          tmem_store32(tmem_base + lane_base + O_COL + c * 64 + 32, ou + 32);
+        }
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -307,23 +334,26 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
     ok = __all_sync(0xffffffffu, ok);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {  // every thread of a warp takes part in the tensor-memory loads; only real rows are stored
-      float o[HD];
-      tmem_load32(tmem_base + lane_base + O_COL, o);
-      tmem_load32(tmem_base + lane_base + O_COL + 32, o + 32);
-      tmem_load_wait();
-      if (tid < n_rows) {
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        const int tq = tid / g, hg = tid % g;
-        uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(tok_base + tq) * p.ld_out + (size_t)(kvh * g + hg) * HD);
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const int tq = tid / g, hg = tid % g;
+      uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(tok_base + tq) * p.ld_out + (size_t)(kvh * g + hg) * HD);
 #pragma unroll
-        for (int c = 0; c < HD / 8; ++c) {
-          uint32_t w[4];
+      for (int b = 0; b < HD / 64; ++b) {
+        float o[64];
+        tmem_load32(tmem_base + lane_base + O_COL + b * 64, o);
+        tmem_load32(tmem_base + lane_base + O_COL + b * 64 + 32, o + 32);
+        tmem_load_wait();
+        if (tid < n_rows) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            __nv_bfloat162 t = __floats2bfloat162_rn(o[c * 8 + 2 * e] * inv, o[c * 8 + 2 * e + 1] * inv);
-            w[e] = *reinterpret_cast<uint32_t*>(&t);
+          for (int c = 0; c < 8; ++c) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 t = __floats2bfloat162_rn(o[c * 8 + 2 * e] * inv, o[c * 8 + 2 * e + 1] * inv);
+              w[e] = *reinterpret_cast<uint32_t*>(&t);
+            }
+            dst[b * 8 + c] = make_uint4(w[0], w[1], w[2], w[3]);
           }
-          dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
     }
@@ -333,18 +363,34 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS_ATT) : "memory");
 }
 
+template <int HD>
+bool launch_att(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, dim3 grid, int max_blocks, cudaStream_t stream) {
+  using L = AttLayout<HD>;
+  // Q, two stages of K and V, six 8-byte words of barriers, four ints, the block-table slice, alignment slack
+  const size_t smem = L::Q_BYTES + 4 * L::KV_BYTES + 6 * sizeof(uint64_t) + 16 + (size_t)max_blocks * sizeof(int) + 1024;
+  static size_t attr_smem = 0;
+  if (smem > attr_smem) {
+    if (cudaFuncSetAttribute(paged_attention_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
+    attr_smem = smem;
+  }
+  launch_kernel(paged_attention_tc_kernel<HD>, grid, ATT_THREADS, smem, stream, mk, mv, p);
+  return true;
+}
+
 }  // namespace
 
 // Whether the tcgen05 attention takes this geometry (else the caller uses the mma.sync kernel).
 extern "C" int llm_attention_tc_supported(int nq, int nkv, int hd, int page_size, long long ld_q, long long ld_out) {
   if (nkv <= 0 || nq % nkv) return 0;
   const int g = nq / nkv;
-  return hd == HD && g <= ROWS && ROWS % g == 0 && page_size % 8 == 0 && KEYS % page_size == 0 && (ld_q % 8) == 0 && (ld_out % 8) == 0 &&
+  if (hd != 64 && hd != 128) return 0;
+  const int keys = hd == 64 ? AttLayout<64>::KEYS : AttLayout<128>::KEYS;
+  return g <= ROWS && page_size % 8 == 0 && keys % page_size == 0 && (ld_q % 8) == 0 && (ld_out % 8) == 0 &&
          encode_fn() != nullptr;
 }
 
-// q: rows of [nq*64] bf16; caches [pages, nkv, page_size, 64] bf16 (n_cache_pages pages each);
-// seq_* and block_table as in the step's batch; out [n_tokens, nq*64] bf16.
+// q: rows of [nq*hd] bf16; caches [pages, nkv, page_size, hd] bf16 (n_cache_pages pages each);
+// seq_* and block_table as in the step's batch; out [n_tokens, nq*hd] bf16.
 extern "C" int llm_paged_attention_tc(const void* q, long long ld_q, const void* kcache, const void* vcache, long long n_cache_pages,
                                       const int* seq_start, const int* seq_ntok, const int* seq_qoff, const int* block_table,
                                       int max_blocks, void* out, long long ld_out, int n_seqs, int max_new_tokens, int nq, int nkv,
@@ -357,23 +403,19 @@ extern "C" int llm_paged_attention_tc(const void* q, long long ld_q, const void*
   LLM_REQUIRE(error_word() != nullptr, "attention_tc: cannot allocate the error word");
   CUtensorMap mk, mv;
   const long long rows = n_cache_pages * nkv * page_size;
-  LLM_REQUIRE(tensor_map_for(kcache, rows, HD, HD, page_size, &mk) && tensor_map_for(vcache, rows, HD, HD, page_size, &mv),
+  LLM_REQUIRE(tensor_map_for(kcache, rows, hd, hd, page_size, &mk) && tensor_map_for(vcache, rows, hd, hd, page_size, &mv),
               "attention_tc: cuTensorMapEncodeTiled failed");
   AttnTcParams p;
   p.q = (const bf16*)q; p.ld_q = ld_q; p.seq_start = seq_start; p.seq_ntok = seq_ntok; p.seq_qoff = seq_qoff; p.block_table = block_table;
   p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.scale = scale;
   p.out = (bf16*)out; p.ld_out = ld_out; p.error_out = error_word();
   LLM_REQUIRE(max_blocks <= 4096, "attention_tc: block tables wider than 4096 pages are not supported");
-  const size_t smem = Q_BYTES + 4 * KV_BYTES + 4 * sizeof(uint64_t) + 16 + (size_t)max_blocks * sizeof(int) + 1024;
-  static size_t attr_smem = 0;
-  if (smem > attr_smem) {
-    LLM_REQUIRE(cudaFuncSetAttribute(paged_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess,
-                "attention_tc: cannot raise the shared memory limit");
-    attr_smem = smem;
-  }
   const int g = nq / nkv, tq_cap = ROWS / g;
   dim3 grid((max_new_tokens + tq_cap - 1) / tq_cap, n_seqs, nkv);
-  launch_kernel(paged_attention_tc_kernel, grid, ATT_THREADS, smem, stream, mk, mv, p);
+  bool attr_ok = true;
+  if (hd == 64) attr_ok = launch_att<64>(mk, mv, p, grid, max_blocks, stream);
+  else attr_ok = launch_att<128>(mk, mv, p, grid, max_blocks, stream);
+  LLM_REQUIRE(attr_ok, "attention_tc: cannot raise the shared memory limit");
   LLM_CHECK_LAUNCH("paged_attention_tc");
   return LLM_OK;
 }

@@ -324,11 +324,15 @@ def test_paged_attention(ops, dt, nq, nkv, hd, page, window):
             torch.testing.assert_close(out[i].float().cpu(), ref, **tol(dt, 2))
 
 
-@pytest.mark.parametrize("nq,nkv,window", [(32, 8, 0), (8, 2, 0), (4, 4, 0), (16, 1, 0), (8, 2, 150)])
-def test_paged_attention_tcgen05(ops, nq, nkv, window):
-    """The tcgen05 kernel for prompt portions (head size 64, pages of 16): portions that start in the
-    middle of a page and of a 128-key tile, span several tiles, stand beside single tokens."""
-    hd, page, dt = 64, 16, torch.bfloat16
+@pytest.mark.parametrize("hd,page", [(64, 16), (128, 16), (128, 32), (64, 64)])
+@pytest.mark.parametrize("nq,nkv,window", [(32, 8, 0), (8, 2, 0), (4, 4, 0), (16, 1, 0), (8, 2, 150), (6, 2, 0), (5, 1, 70)])
+def test_paged_attention_tcgen05(ops, nq, nkv, window, hd, page):
+    """The tcgen05 kernel for prompt portions (head sizes 64 and 128): portions that start in the
+    middle of a page and of a key tile, span several tiles, stand beside single tokens."""
+    dt = torch.bfloat16
+    lib = ops.lib("tensorcore")
+    from ctypes import c_int, c_longlong
+    assert lib.llm_attention_tc_supported(c_int(nq), c_int(nkv), c_int(hd), c_int(page), c_longlong(nq * hd), c_longlong(nq * hd))
     seq_lens = [300, 1, 129, 700, 128]
     kc, vc, table, dense = _paged_setup(dt, nkv, hd, page, seq_lens, sum((L + page - 1) // page for L in seq_lens) + 3, seed=9)
     scale = 1.0 / math.sqrt(hd)
