@@ -41,6 +41,16 @@ GEOMETRY = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermedia
                 rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
                                   original_max_position_embeddings=8192))
 FULL_LAYERS = 16
+# Further sizes for --geometry (the default, and what the headline is quoted on, stays the 1B one):
+# Llama 3.2 3B and Llama 3.1 8B layer sizes.
+GEOMETRIES = {
+    "1b": (GEOMETRY, 16, "llama-3.2-1b-geometry", "Llama 3.2 1B"),
+    "3b": (dict(GEOMETRY, hidden_size=3072, num_attention_heads=24, head_dim=128, num_hidden_layers=28), 28, "llama-3.2-3b-geometry", "Llama 3.2 3B"),
+    "8b": (dict(GEOMETRY, hidden_size=4096, intermediate_size=14336, num_attention_heads=32, head_dim=128, num_hidden_layers=32,
+                tie_word_embeddings=False,
+                rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                  original_max_position_embeddings=8192)), 32, "llama-3.1-8b-geometry", "Llama 3.1 8B"),
+}
 CONTEXT, CONTEXT_LIMIT, PREFILL_TOKENS, BLOCK_SIZE = 2048, 4096, 2048, 16
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
 
@@ -125,8 +135,9 @@ def run_ours(args):
     from llmengine.cache import host_module
 
     torch.cuda.set_device(0)
-    layers = args.layers
-    g = dict(GEOMETRY, num_hidden_layers=layers)
+    base, full_layers, model_name, model_label = GEOMETRIES[args.geometry]
+    layers = args.layers if args.layers > 0 else full_layers
+    g = dict(base, num_hidden_layers=layers)
     pk = peaks()
     K, W = args.steps, args.warmup
     tmp = tempfile.TemporaryDirectory(prefix="llmengine_bench_")
@@ -240,15 +251,15 @@ def run_ours(args):
     achieved = bytes_step / sec / 1e9 if sec != float("inf") else 0.0
     pf = flops_of_prefill(g, layers, PREFILL_TOKENS)
     rec = {
-        "metric": "decode tok/s at batch 8 (Llama 3.2 1B geometry, 2048-token contexts)",
+        "metric": f"decode tok/s at batch {args.batch} ({model_label} geometry, {CONTEXT}-token contexts)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(sec * 1e3, 4) if sec != float("inf") else None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), uniform random token ids", "impl": "ours",
-        "config": {"model": "llama-3.2-1b-geometry", "global_batch": args.batch, "seq_len": CONTEXT,
+        "config": {"model": model_name, "global_batch": args.batch, "seq_len": CONTEXT,
                    "context_limit": CONTEXT_LIMIT, "parallelism": "single-gpu", "layers": layers,
-                   "layers_full_config": FULL_LAYERS, "hidden": g["hidden_size"], "heads": g["num_attention_heads"],
+                   "layers_full_config": full_layers, "hidden": g["hidden_size"], "heads": g["num_attention_heads"],
                    "kv_heads": g["num_key_value_heads"], "head_dim": g["head_dim"], "intermediate": g["intermediate_size"],
-                   "vocab": g["vocab_size"], "tied_embeddings": True, "kv_block_size": BLOCK_SIZE,
+                   "vocab": g["vocab_size"], "tied_embeddings": bool(g["tie_word_embeddings"]), "kv_block_size": BLOCK_SIZE,
                    "prefill_tokens": PREFILL_TOKENS, "l2": "step reads > 2 GB of weights: inputs larger than L2",
                    "peaks": pk["source"]},
         "e2e": {"value": round(args.batch / e2e_sec, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -276,7 +287,7 @@ def run_reference(args):
     # the model folder is written by this repo's random-weights mode in a child process, so that the
     # reference's `llmengine` and this repo's `llmengine` never share an interpreter
     tmp = tempfile.TemporaryDirectory(prefix="llmengine_bench_ref_")
-    g = dict(GEOMETRY, num_hidden_layers=args.layers)
+    g = dict(GEOMETRY, num_hidden_layers=args.layers if args.layers > 0 else FULL_LAYERS)
     code = ("import sys, json, torch; sys.path.insert(0, %r); import llmengine; "
             "llmengine.write_random_model(%r, json.loads(%r), seed=0, dtype=torch.bfloat16)"
             % (os.path.join(ROOT, "llm-inference-engine-v6_b200"), tmp.name, json.dumps(g)))
@@ -318,7 +329,7 @@ def run_reference(args):
         "value": round(B / sec, 3), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(sec * 1e3, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp32 (the reference's stock path; it has no bf16 engine)", "data": "synthetic: same random model folder",
-        "config": {"model": "llama-3.2-1b-geometry", "global_batch": B, "seq_len": CONTEXT, "layers": args.layers,
+        "config": {"model": "llama-3.2-1b-geometry", "global_batch": B, "seq_len": CONTEXT, "layers": args.layers if args.layers > 0 else FULL_LAYERS,
                    "parallelism": "cpu threads (the reference has no GPU code)"},
         "gpu_launches": 0}), flush=True)
     return 0
@@ -331,7 +342,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the full configuration (named in `config`)")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the full configuration (named in `config`); 0: all")
+    ap.add_argument("--geometry", choices=sorted(GEOMETRIES), default="1b", help="layer sizes: Llama 3.2 1B (default), 3.2 3B, 3.1 8B")
     ap.add_argument("--no-points", dest="points", action="store_false", help="skip the batch 1 and 64 points")
     ap.add_argument("--skip", default="", help="comma list of parts to leave out: decode,e2e,prefill,points (for profiling runs)")
     ap.add_argument("--no-cuda-graphs", dest="graphs", action="store_false", help="launch decode steps kernel by kernel")

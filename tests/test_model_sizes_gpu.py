@@ -21,6 +21,10 @@ SIZES = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermediate_
                                original_max_position_embeddings=8192))
 
 
+# Llama 3.2 3B layer sizes: head size 128, a group of three query heads per key/value head
+SIZES_3B = dict(SIZES, hidden_size=3072, num_attention_heads=24, head_dim=128)
+
+
 def _plain_rows(pc, w, ids, rows):
     """Logits of the plain implementation at `rows` only (the head over 128256 entries is the slow part)."""
     T, hd, eps = len(ids), pc["head_dim"], pc["rms_norm_eps"]
@@ -36,12 +40,13 @@ def _plain_rows(pc, w, ids, rows):
     return P.linear(P.rmsnorm(h[rows], w["model.norm.weight"], eps), w["lm_head.weight"])
 
 
-def test_real_layer_sizes_prompt_portions_and_decoding(tmp_path):
+@pytest.mark.parametrize("sizes", [SIZES, SIZES_3B], ids=["1b", "3b"])
+def test_real_layer_sizes_prompt_portions_and_decoding(tmp_path, sizes):
     d = str(tmp_path / "m")
-    llmengine.write_random_model(d, SIZES, seed=3, dtype=torch.bfloat16, std=0.02)
+    llmengine.write_random_model(d, sizes, seed=3, dtype=torch.bfloat16, std=0.02)
     pc, pw = P.read_model(d)
     T, tail = 1000, 6
-    ids = random_ids(T, SIZES["vocab_size"], 41)
+    ids = random_ids(T, sizes["vocab_size"], 41)
     rows = [0, 1, 299, 300, 301, T - tail - 1] + list(range(T - tail, T))
     ref = _plain_rows(pc, pw, ids, rows)
     eng = llmengine.Engine(d, "bf16", block_size=16, num_blocks=80, max_concurrent=2)
