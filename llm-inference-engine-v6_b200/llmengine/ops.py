@@ -301,17 +301,20 @@ class CudaOps:
 
     # decoding: the key range is cut at absolute multiples of `split_keys` (a multiple of 64); see _split_policy
     ATTENTION_TARGET_CTAS = 592
-    ATTENTION_MAX_SPLITS = 6
-    ATTENTION_MIN_SPLIT_KEYS = 256
+    ATTENTION_MAX_SPLITS = 128  # what the kernels' merge takes
+    ATTENTION_MIN_SPLIT_KEYS = 320
     TC_ATTENTION_MIN_TOKENS = 32  # longest portion of the step from which the tcgen05 attention kernel is used
 
-    def _split_policy(self, pairs: int, max_seq_len: int):
+    def _split_policy(self, pairs: int, max_seq_len: int, hd: int = 64):
         """-> (number of key splits, keys per split) of a step of single tokens with `pairs` (request,
         key/value head) pairs. Measured on B200 (head size 64): the cache streams fastest with four
         CTAs on each of the 148 SMs (592) and no split; with fewer pairs the range is cut to fill
-        those places, but into at most ATTENTION_MAX_SPLITS pieces of at least ATTENTION_MIN_SPLIT_KEYS keys, since every
-        split ends in a partial output and a merge."""
-        want = min(self.ATTENTION_MAX_SPLITS, self.ATTENTION_TARGET_CTAS // max(pairs, 1), max_seq_len // self.ATTENTION_MIN_SPLIT_KEYS)
+        those places, but into pieces of at least ATTENTION_MIN_SPLIT_KEYS keys, since every split
+        ends in a partial output and a merge (2,048-token contexts at batch 8: 6 splits of 384 keys
+        take 13.5 us, 9 of 256 keys 15.8 us)."""
+        # head size 128: stages are twice as large, two CTAs with the long ring an SM do best (296 places)
+        places = self.ATTENTION_TARGET_CTAS if hd <= 64 else max(1, self.ATTENTION_TARGET_CTAS // 2)
+        want = min(self.ATTENTION_MAX_SPLITS, places // max(pairs, 1), max_seq_len // self.ATTENTION_MIN_SPLIT_KEYS)
         if want <= 1:
             return 1, 256
         split_keys = -(-(-(-max_seq_len // want)) // 64) * 64
@@ -319,7 +322,7 @@ class CudaOps:
 
     def _decode_splits(self, lib, batch, nq: int, nkv: int, hd: int):
         """How a step of single tokens cuts its key ranges -> (n_splits, split_keys, scratch, counters)."""
-        n_splits, split_keys = self._split_policy(batch.n_seqs * nkv, batch.max_seq_len)
+        n_splits, split_keys = self._split_policy(batch.n_seqs * nkv, batch.max_seq_len, hd)
         scratch = counters = None
         if n_splits > 1:
             floats = int(lib.llm_attention_mma_scratch_floats(c_int(batch.n_tokens), c_int(nq), c_int(hd), c_int(n_splits)))
@@ -338,7 +341,7 @@ class CudaOps:
         if not lib.llm_attention_decode_supported(c_int(nq), c_int(nkv), c_int(hd), c_int(kcache.shape[2]), c_longlong(8),
                                                   c_longlong(out.stride(0))):
             return False
-        return self._split_policy(batch.n_seqs * nkv, batch.max_seq_len)[0] <= 128
+        return self._split_policy(batch.n_seqs * nkv, batch.max_seq_len, hd)[0] <= 128
 
     def paged_attention_decode_fused(self, parts: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                                      kcache: torch.Tensor, vcache: torch.Tensor, batch, block_table: torch.Tensor,

@@ -362,7 +362,6 @@ def test_paged_attention_decode_by_tma(ops, monkeypatch, nq, nkv, hd, page, wind
     dt = torch.bfloat16
     monkeypatch.setattr(type(ops), "ATTENTION_TARGET_CTAS", target_ctas)
     if target_ctas > 1000:
-        monkeypatch.setattr(type(ops), "ATTENTION_MAX_SPLITS", 1000)
         monkeypatch.setattr(type(ops), "ATTENTION_MIN_SPLIT_KEYS", 64)
     seq_lens = [1, 32, 33, 64, 257, 700, 1024, 16]
     kc, vc, table, dense = _paged_setup(dt, nkv, hd, page, seq_lens, sum((L + page - 1) // page for L in seq_lens) + 3, seed=5)
