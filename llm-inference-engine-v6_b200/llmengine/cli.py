@@ -30,10 +30,10 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--prompt-ids", help="comma-separated token ids of one prompt")
     ap.add_argument("--prompt-len", type=int, help="use random prompts of this many token ids instead")
     ap.add_argument("--requests", type=int, default=1, help="number of random prompts (with --prompt-len)")
-    ap.add_argument("--max-new", type=int, default=16, help="tokens to generate per request")
+    ap.add_argument("--max-new", "--max-new-tokens", dest="max_new", type=int, default=16, help="tokens to generate per request")
     ap.add_argument("--temperature", type=float, default=0.0, help="0: greedy")
-    ap.add_argument("--seed", type=int, default=0, help="seed of sampling and of random prompts / weights")
-    ap.add_argument("--budget", type=int, default=256, help="prefill tokens per scheduler step")
+    ap.add_argument("--seed", "--sample-seed", dest="seed", type=int, default=0, help="seed of sampling and of random prompts / weights")
+    ap.add_argument("--budget", "--max-prefill-tokens-per-step", dest="budget", type=int, default=256, help="prefill tokens per scheduler step")
     ap.add_argument("--max-concurrent", type=int, default=64)
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
     ap.add_argument("--num-blocks", type=int, default=None, help="pages in the pool (default: sized from free memory)")
