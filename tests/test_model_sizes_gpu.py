@@ -79,3 +79,26 @@ def test_real_layer_sizes_prompt_portions_and_decoding(tmp_path, sizes):
         lg = eng.run_step([(7, [tok], [0])])
     eng.run_step([], end=[7])
     assert out == seq
+
+
+def test_float32_path_and_bfloat16_drift_at_real_layer_sizes(tmp_path):
+    """A short prompt at the 1B layer sizes through the true 32-bit path (CUDA-core products, no
+    reduced-precision matrix mode: equal to the plain implementation to summation order) and through
+    bfloat16 with the same weights: the drift between the two precisions stays within the bound
+    that the tiny models are held to."""
+    d = str(tmp_path / "m")
+    llmengine.write_random_model(d, SIZES, seed=4, dtype=torch.bfloat16, std=0.02)
+    pc, pw = P.read_model(d)
+    ids = random_ids(24, SIZES["vocab_size"], 43)
+    ref = _plain_rows(pc, pw, ids, list(range(24)))
+    got = {}
+    for dtype in ("fp32", "bf16"):
+        eng = llmengine.Engine(d, dtype, block_size=16, num_blocks=8, max_concurrent=1)
+        a = eng.run_step([(1, ids[:20], range(20))]).clone()
+        rest = [eng.run_step([(1, ids[t:t + 1], [0])], end=[1] if t == 23 else []).clone() for t in range(20, 24)]
+        got[dtype] = torch.cat([a] + rest).cpu().numpy()
+        del eng
+        torch.cuda.empty_cache()
+    assert np.abs(got["fp32"] - ref).max() < 2e-4
+    assert np.abs(got["bf16"] - got["fp32"]).max() < 6e-2
+    assert (got["fp32"].argmax(1) == ref.argmax(1)).all()
