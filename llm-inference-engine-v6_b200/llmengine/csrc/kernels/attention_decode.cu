@@ -13,8 +13,12 @@
 //
 // Scores (bf16 mma.sync, float32 accumulators), the running (max, sum) softmax in log2 units and
 // the output sums are float32 registers. The four warps' partials are merged in warp order, the
-// splits' partials in index order by the CTA that finishes last for its (request, key/value head):
-// a token's result does not depend on the batch or on page numbers.
+// splits' partials in index order: a token's result does not depend on the batch or on page numbers.
+// Up to eight splits of a (request, key/value head) run as ONE thread-block cluster (CLUSTER): each
+// CTA leaves its partial in its own shared memory, and after a cluster barrier the CTAs read all of
+// them through distributed shared memory, each finishing a slice of the output. More splits go
+// through global memory: partials, a fence, a counter, and the CTA that arrives last merges them
+// (about 6 us slower on the step's critical path: two fences and three round trips to L2).
 //
 // Fused form (FUSED): the kernel before this one is the q|k|v product itself, given as float32 K-split
 // partial sums [parts][token][q|k|v]. The computing warps add the parts in index order, rotate q
@@ -69,7 +73,7 @@ struct DecLayout {
 // Byte offset of (row, 16-byte chunk) inside a [TK][64] tile written by TMA with 128-byte swizzle.
 __device__ __forceinline__ uint32_t sw128(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
 
-template <int HD, bool FUSED, bool DEEP>
+template <int HD, bool FUSED, bool DEEP, bool CLUSTER>
 __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                                  const __grid_constant__ CUtensorMap map_v,
                                                                                  const DecParams p) {
@@ -408,11 +412,18 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
         }
       }
     }
+    if (CLUSTER && p.n_splits > 1) {  // the peers wait at two cluster barriers: take part, with nothing to offer
+      __syncthreads();
+      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
     return;
   }
   // ---- merge the four warps (in warp order)
   const float* mg = reinterpret_cast<const float*>(ring);
   constexpr int MLD = HD + 2;
+  constexpr int XCHG_OFFSET = 4 * ROWS * MLD * 4;  // behind the warps' partials in the ring (the ring is longer)
+  static_assert(XCHG_OFFSET + ROWS * MLD * 4 <= NS * L::STAGE_BYTES, "the exchange area does not fit the ring");
   for (int e = tid; e < g * HD; e += DEC_THREADS) {
     const int row = e / HD, d = e - row * HD;
     float mx = -INFINITY;
@@ -432,6 +443,13 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
     const int head = kvh * g + row;
     if (p.n_splits == 1) {
       p.out[(size_t)tok * p.ld_out + (size_t)head * HD + d] = __float2bfloat16_rn(acc * inv);
+    } else if (CLUSTER) {
+      float* mine = reinterpret_cast<float*>(ring + XCHG_OFFSET);  // [row][HD + 2]: this split's partial for its peers
+      mine[row * MLD + d] = acc * inv;
+      if (d == 0) {
+        mine[row * MLD + HD] = mx;
+        mine[row * MLD + HD + 1] = den;
+      }
     } else {
       const size_t slot = ((size_t)split * p.part_stride_tokens + tok) * p.nq + head;
       p.part_o[slot * HD + d] = acc * inv;
@@ -442,6 +460,45 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
     }
   }
   if (p.n_splits == 1) return;
+  if constexpr (CLUSTER) {
+    // ---- the splits are the CTAs of this cluster (rank = split): every CTA finishes the elements
+    // e = rank, rank + n_splits, ... of the output from all partials, in index order
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    const uint32_t mine = smem_u32(ring + XCHG_OFFSET);
+    for (int k = tid; k * p.n_splits + split < g * HD; k += DEC_THREADS) {
+      const int e = k * p.n_splits + split;
+      const int row = e / HD, d = e - row * HD;
+      float m[8], l[8], v[8];
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp) {
+        m[sp] = -INFINITY; l[sp] = 0.f; v[sp] = 0.f;
+        if (sp < p.n_splits) {
+          uint32_t peer;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(mine + (uint32_t)(row * MLD) * 4u), "r"(sp));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(m[sp]) : "r"(peer + (uint32_t)HD * 4u));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(l[sp]) : "r"(peer + (uint32_t)(HD + 1) * 4u));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[sp]) : "r"(peer + (uint32_t)d * 4u));
+        }
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp) mx = fmaxf(mx, m[sp]);
+      float acc = 0.f, den = 0.f;
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp) {
+        if (sp < p.n_splits && m[sp] != -INFINITY) {
+          const float w = l[sp] * exp2f(m[sp] - mx);
+          den += w;
+          acc = fmaf(w, v[sp], acc);
+        }
+      }
+      const float inv = den > 0.f ? 1.f / den : 0.f;
+      p.out[(size_t)tok * p.ld_out + (size_t)(kvh * g + row) * HD + d] = __float2bfloat16_rn(acc * inv);
+    }
+    // nobody leaves while a peer may still read its partial
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    return;
+  }
   // ---- the CTA that finishes last for this (request, key/value head) merges the splits, in index
   // order whichever CTA that is
   __threadfence();
@@ -493,6 +550,8 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
   }
 }
 
+int g_cluster_merge = 1;  // 0: splits always merge through global memory (for comparisons)
+
 template <int HD, bool DEEP>
 size_t decode_smem_bytes(int keys_per_cta, int page_size) {
   using L = DecLayout<HD, DEEP>;
@@ -500,18 +559,20 @@ size_t decode_smem_bytes(int keys_per_cta, int page_size) {
          (size_t)((keys_per_cta + 2 * TK) / page_size + 4) * sizeof(int);
 }
 
-template <int HD, bool FUSED, bool DEEP>
+template <int HD, bool FUSED, bool DEEP, bool CLUSTER>
 int launch_decode_ring(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int n_seqs, cudaStream_t stream) {
   const int keys_per_cta = p.n_splits > 1 ? p.split_keys : p.max_blocks * p.page_size;
   const size_t smem = decode_smem_bytes<HD, DEEP>(keys_per_cta, p.page_size);
   if (smem > 200 * 1024) return 2;
+  auto kernel = paged_attention_decode_tma_kernel<HD, FUSED, DEEP, CLUSTER>;
   static size_t attr_bytes = 0;  // the largest size asked for so far
   if (smem > attr_bytes) {
-    if (cudaFuncSetAttribute(paged_attention_decode_tma_kernel<HD, FUSED, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-      return 1;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 1;
     attr_bytes = smem;
   }
-  launch_kernel(paged_attention_decode_tma_kernel<HD, FUSED, DEEP>, dim3(n_seqs, p.nkv, p.n_splits), DEC_THREADS, smem, stream, mk, mv, p);
+  const dim3 grid(n_seqs, p.nkv, p.n_splits);
+  if (CLUSTER) launch_kernel_cluster(kernel, grid, DEC_THREADS, smem, dim3(1, 1, p.n_splits), stream, mk, mv, p);
+  else launch_kernel(kernel, grid, DEC_THREADS, smem, stream, mk, mv, p);
   return 0;
 }
 
@@ -519,11 +580,17 @@ template <int HD, bool FUSED>
 int launch_decode(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int n_seqs, cudaStream_t stream) {
   // at most three (head size 64) or two (128) CTAs with the long ring fit an SM of 148
   const long long ctas = (long long)n_seqs * p.nkv * p.n_splits;
-  return ctas <= (HD == 64 ? 444 : 296) ? launch_decode_ring<HD, FUSED, true>(mk, mv, p, n_seqs, stream)
-                                        : launch_decode_ring<HD, FUSED, false>(mk, mv, p, n_seqs, stream);
+  const bool deep = ctas <= (HD == 64 ? 444 : 296);
+  const bool cluster = g_cluster_merge && p.n_splits >= 2 && p.n_splits <= 8;  // 8: the portable cluster size
+  if (cluster) return deep ? launch_decode_ring<HD, FUSED, true, true>(mk, mv, p, n_seqs, stream)
+                           : launch_decode_ring<HD, FUSED, false, true>(mk, mv, p, n_seqs, stream);
+  return deep ? launch_decode_ring<HD, FUSED, true, false>(mk, mv, p, n_seqs, stream)
+              : launch_decode_ring<HD, FUSED, false, false>(mk, mv, p, n_seqs, stream);
 }
 
 }  // namespace
+
+extern "C" void llm_attention_decode_cluster_merge(int on) { g_cluster_merge = on; }
 
 // Whether the TMA decoding kernel takes this geometry: head size 64 or 128, a group of at most 16
 // query heads, pages of 8, 16 or a multiple of 32 keys (a tile of 32 keys is whole pages or lies
@@ -543,7 +610,7 @@ int decode_common(DecParams& p, const void* kcache, const void* vcache, long lon
   LLM_REQUIRE((reinterpret_cast<uintptr_t>(kcache) & 15u) == 0 && (reinterpret_cast<uintptr_t>(vcache) & 15u) == 0,
               "attention_decode: the caches must be 16-byte aligned");
   LLM_REQUIRE(p.n_splits >= 1 && p.n_splits <= 128 &&
-              (p.n_splits == 1 || (p.split_keys > 0 && p.split_keys % 64 == 0 && scratch != nullptr && p.done_count != nullptr)),
+              (p.n_splits == 1 || (p.split_keys > 0 && p.split_keys % 64 == 0 && scratch != nullptr && p.done_count != nullptr)),  // (the cluster form uses neither)
               "attention_decode: splits need split_keys %% 64 == 0, scratch and counters");
   LLM_REQUIRE((long long)n_seqs <= 65535 * 32768LL && p.nkv <= 65535, "attention_decode: batch too large for the grid");
   const long long rows = n_cache_pages * p.nkv * p.page_size;

@@ -677,7 +677,7 @@ int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int 
   }
   const int mp_tiles = (RA + 255) / 256, n_tiles = (RB + 255) / 256;
   const int pairs = std::min(mp_tiles * n_tiles, n_sms / 2);
-  launch_kernel_cluster(kernel, 2 * pairs, PERSIST_THREADS, smem, 2, stream, ma, mb, (TO*)out, RA, RB, k_tiles, ldo, stages, mp_tiles,
+  launch_kernel_cluster(kernel, 2 * pairs, PERSIST_THREADS, smem, dim3(2, 1, 1), stream, ma, mb, (TO*)out, RA, RB, k_tiles, ldo, stages, mp_tiles,
                         n_tiles, error_word());
   return LLM_OK;
 }
