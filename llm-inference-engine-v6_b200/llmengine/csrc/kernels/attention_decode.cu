@@ -16,9 +16,11 @@
 // splits' partials in index order: a token's result does not depend on the batch or on page numbers.
 // Up to eight splits of a (request, key/value head) run as ONE thread-block cluster (CLUSTER): each
 // CTA leaves its partial in its own shared memory, and after a cluster barrier the CTAs read all of
-// them through distributed shared memory, each finishing a slice of the output. More splits go
-// through global memory: partials, a fence, a counter, and the CTA that arrives last merges them
-// (about 6 us slower on the step's critical path: two fences and three round trips to L2).
+// them through distributed shared memory, each finishing a slice of the output. More splits run as
+// several clusters of eight: every cluster merges its own splits the same way into ONE partial in
+// global memory, and the cluster that arrives last (a fence and a counter) merges those. Without
+// clusters every split's partial goes through global memory (about 2 us slower at six splits, and
+// growing with their number: the merging CTA reads them all).
 //
 // Fused form (FUSED): the kernel before this one is the q|k|v product itself, given as float32 K-split
 // partial sums [parts][token][q|k|v]. The computing warps add the parts in index order, rotate q
@@ -50,6 +52,7 @@ struct DecParams {
   float scale;
   bf16* out; long long ld_out;
   float* part_o; float* part_ml; int split_keys, n_splits; long long part_stride_tokens;
+  int cluster_size;  // CLUSTER: splits per cluster (n_splits is a multiple of it); more than one cluster -> their results meet in global memory
   int* done_count;
   int* error;
   // fused form only
@@ -460,19 +463,22 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
     }
   }
   if (p.n_splits == 1) return;
+  int n_merge = p.n_splits;  // partials that meet in global memory
   if constexpr (CLUSTER) {
-    // ---- the splits are the CTAs of this cluster (rank = split): every CTA finishes the elements
-    // e = rank, rank + n_splits, ... of the output from all partials, in index order
+    // ---- eight (or fewer) neighbouring splits are the CTAs of this cluster: every CTA finishes the
+    // elements e = rank, rank + size, ... from the cluster's partials, in index order
+    const int csize = p.cluster_size, rank = split % csize, group = split / csize;
+    n_merge = p.n_splits / csize;
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     const uint32_t mine = smem_u32(ring + XCHG_OFFSET);
-    for (int k = tid; k * p.n_splits + split < g * HD; k += DEC_THREADS) {
-      const int e = k * p.n_splits + split;
+    for (int k = tid; k * csize + rank < g * HD; k += DEC_THREADS) {
+      const int e = k * csize + rank;
       const int row = e / HD, d = e - row * HD;
       float m[8], l[8], v[8];
 #pragma unroll
       for (int sp = 0; sp < 8; ++sp) {
         m[sp] = -INFINITY; l[sp] = 0.f; v[sp] = 0.f;
-        if (sp < p.n_splits) {
+        if (sp < csize) {
           uint32_t peer;
           asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(mine + (uint32_t)(row * MLD) * 4u), "r"(sp));
           asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(m[sp]) : "r"(peer + (uint32_t)HD * 4u));
@@ -486,26 +492,37 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
       float acc = 0.f, den = 0.f;
 #pragma unroll
       for (int sp = 0; sp < 8; ++sp) {
-        if (sp < p.n_splits && m[sp] != -INFINITY) {
+        if (sp < csize && m[sp] != -INFINITY) {
           const float w = l[sp] * exp2f(m[sp] - mx);
           den += w;
           acc = fmaf(w, v[sp], acc);
         }
       }
       const float inv = den > 0.f ? 1.f / den : 0.f;
-      p.out[(size_t)tok * p.ld_out + (size_t)(kvh * g + row) * HD + d] = __float2bfloat16_rn(acc * inv);
+      const int head = kvh * g + row;
+      if (n_merge == 1) {
+        p.out[(size_t)tok * p.ld_out + (size_t)head * HD + d] = __float2bfloat16_rn(acc * inv);
+      } else {  // this cluster's partial: slot `group`
+        const size_t slot = ((size_t)group * p.part_stride_tokens + tok) * p.nq + head;
+        p.part_o[slot * HD + d] = acc * inv;
+        if (d == 0) {
+          p.part_ml[slot * 2] = mx;
+          p.part_ml[slot * 2 + 1] = den;
+        }
+      }
     }
+    if (n_merge > 1) __threadfence();  // the cluster's partial is out before its leader counts it
     // nobody leaves while a peer may still read its partial
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    return;
+    if (n_merge == 1 || rank != 0) return;
   }
-  // ---- the CTA that finishes last for this (request, key/value head) merges the splits, in index
-  // order whichever CTA that is
-  __threadfence();
+  // ---- the CTA (the cluster's leader) that arrives last for this (request, key/value head) merges
+  // the partials, in index order whichever one that is
+  if (!CLUSTER) __threadfence();
   __syncthreads();
   if (tid == 0) {
     const int old = atomicAdd(&p.done_count[seq * p.nkv + kvh], 1);
-    flags[2] = (old == p.n_splits - 1);
+    flags[2] = (old == n_merge - 1);
     if (flags[2]) p.done_count[seq * p.nkv + kvh] = 0;  // ready for the next launch
   }
   __syncthreads();
@@ -513,32 +530,32 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
   __threadfence();
   const size_t split_stride = (size_t)p.part_stride_tokens * p.nq;
   float* m_s = reinterpret_cast<float*>(ring);  // [g][n_splits]
-  float* l_s = m_s + ROWS * p.n_splits;         // [g][n_splits]
+  float* l_s = m_s + ROWS * n_merge;         // [g][n_splits]
   __syncthreads();
-  for (int idx = tid; idx < g * p.n_splits; idx += DEC_THREADS) {
-    const int row = idx / p.n_splits, sp = idx - row * p.n_splits;
+  for (int idx = tid; idx < g * n_merge; idx += DEC_THREADS) {
+    const int row = idx / n_merge, sp = idx - row * n_merge;
     const size_t slot = (size_t)tok * p.nq + kvh * g + row + sp * split_stride;
-    m_s[row * p.n_splits + sp] = __ldcg(&p.part_ml[slot * 2]);
-    l_s[row * p.n_splits + sp] = __ldcg(&p.part_ml[slot * 2 + 1]);
+    m_s[row * n_merge + sp] = __ldcg(&p.part_ml[slot * 2]);
+    l_s[row * n_merge + sp] = __ldcg(&p.part_ml[slot * 2 + 1]);
   }
   __syncthreads();
   for (int e = tid; e < g * HD; e += DEC_THREADS) {
     const int row = e / HD, d = e - row * HD;
     const size_t slot0 = (size_t)tok * p.nq + kvh * g + row;
     float mx = -INFINITY;
-    for (int sp = 0; sp < p.n_splits; ++sp) mx = fmaxf(mx, m_s[row * p.n_splits + sp]);
+    for (int sp = 0; sp < n_merge; ++sp) mx = fmaxf(mx, m_s[row * n_merge + sp]);
     float acc = 0.f, den = 0.f;
-    for (int s0 = 0; s0 < p.n_splits; s0 += 8) {  // eight splits' loads in flight; added in index order
+    for (int s0 = 0; s0 < n_merge; s0 += 8) {  // eight splits' loads in flight; added in index order
       float v[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u)
-        v[u] = (s0 + u < p.n_splits) ? __ldcg(&p.part_o[(slot0 + (s0 + u) * split_stride) * HD + d]) : 0.f;
+        v[u] = (s0 + u < n_merge) ? __ldcg(&p.part_o[(slot0 + (s0 + u) * split_stride) * HD + d]) : 0.f;
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        if (s0 + u < p.n_splits) {
-          const float m = m_s[row * p.n_splits + s0 + u];
+        if (s0 + u < n_merge) {
+          const float m = m_s[row * n_merge + s0 + u];
           if (m != -INFINITY) {
-            const float w = l_s[row * p.n_splits + s0 + u] * exp2f(m - mx);
+            const float w = l_s[row * n_merge + s0 + u] * exp2f(m - mx);
             den += w;
             acc = fmaf(w, v[u], acc);
           }
@@ -571,17 +588,21 @@ int launch_decode_ring(const CUtensorMap& mk, const CUtensorMap& mv, const DecPa
     attr_bytes = smem;
   }
   const dim3 grid(n_seqs, p.nkv, p.n_splits);
-  if (CLUSTER) launch_kernel_cluster(kernel, grid, DEC_THREADS, smem, dim3(1, 1, p.n_splits), stream, mk, mv, p);
+  if (CLUSTER) launch_kernel_cluster(kernel, grid, DEC_THREADS, smem, dim3(1, 1, p.cluster_size), stream, mk, mv, p);
   else launch_kernel(kernel, grid, DEC_THREADS, smem, stream, mk, mv, p);
   return 0;
 }
 
 template <int HD, bool FUSED>
-int launch_decode(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int n_seqs, cudaStream_t stream) {
+int launch_decode(const CUtensorMap& mk, const CUtensorMap& mv, DecParams p, int n_seqs, cudaStream_t stream) {
+  const bool cluster = g_cluster_merge && p.n_splits >= 2;
+  if (cluster) {  // 8 is the portable cluster size; more splits: whole clusters of 8 (the splits added are empty)
+    p.cluster_size = p.n_splits <= 8 ? p.n_splits : 8;
+    p.n_splits = (p.n_splits + p.cluster_size - 1) / p.cluster_size * p.cluster_size;
+  }
   // at most three (head size 64) or two (128) CTAs with the long ring fit an SM of 148
   const long long ctas = (long long)n_seqs * p.nkv * p.n_splits;
   const bool deep = ctas <= (HD == 64 ? 444 : 296);
-  const bool cluster = g_cluster_merge && p.n_splits >= 2 && p.n_splits <= 8;  // 8: the portable cluster size
   if (cluster) return deep ? launch_decode_ring<HD, FUSED, true, true>(mk, mv, p, n_seqs, stream)
                            : launch_decode_ring<HD, FUSED, false, true>(mk, mv, p, n_seqs, stream);
   return deep ? launch_decode_ring<HD, FUSED, true, false>(mk, mv, p, n_seqs, stream)

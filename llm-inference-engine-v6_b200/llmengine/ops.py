@@ -305,7 +305,6 @@ class CudaOps:
     ATTENTION_TARGET_CTAS = 592
     ATTENTION_MAX_SPLITS = 128  # what the kernels' merge takes
     ATTENTION_MIN_SPLIT_KEYS = 320
-    ATTENTION_CLUSTER_SPLIT_KEYS = 1024  # contexts up to 8 x this are cut into at most 8 splits (one cluster)
     TC_ATTENTION_MIN_TOKENS = 32  # longest portion of the step from which the tcgen05 attention kernel is used
 
     def _split_policy(self, pairs: int, max_seq_len: int, hd: int = 64):
@@ -314,14 +313,15 @@ class CudaOps:
         CTAs on each of the 148 SMs (592) and no split; with fewer pairs the range is cut to fill
         those places, but into pieces of at least ATTENTION_MIN_SPLIT_KEYS keys, since every split
         ends in a partial output and a merge. Up to 8 splits merge inside a thread-block cluster
-        (2,048-token contexts at batch 8: 11.0 us, against 13.3 us through global memory); more go
-        through global memory, which long contexts at small batches still prefer to fewer, longer
-        splits. Inside a decode step 320 and 384 keys measure the same (0.881 ms), 256 keys 0.898 ms."""
+        (2,048-token contexts at batch 8: 11.0 us, against 13.3 us through global memory); more run
+        as several clusters of 8 whose results meet in global memory (one request of 16,384 tokens:
+        48 splits, 16.4 us against 27.2 us with every split's partial in global memory). Inside a
+        decode step 320 and 384 keys measure the same (0.881 ms), 256 keys 0.898 ms."""
         # head size 128: stages are twice as large, two CTAs with the long ring an SM do best (296 places)
         places = self.ATTENTION_TARGET_CTAS if hd <= 64 else max(1, self.ATTENTION_TARGET_CTAS // 2)
         want = min(self.ATTENTION_MAX_SPLITS, places // max(pairs, 1), max_seq_len // self.ATTENTION_MIN_SPLIT_KEYS)
-        if want > 8 and max_seq_len <= 8 * self.ATTENTION_CLUSTER_SPLIT_KEYS:
-            want = 8  # eight splits still merge inside a cluster; a ninth would send all of them through global memory
+        if want > 8:
+            want = want // 8 * 8  # whole clusters of eight splits: a ninth split would cost a cluster of its own
         if want <= 1:
             return 1, 256
         split_keys = -(-(-(-max_seq_len // want)) // 64) * 64
