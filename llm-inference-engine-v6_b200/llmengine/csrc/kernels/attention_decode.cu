@@ -15,8 +15,9 @@
 // the output sums are float32 registers. The four warps' partials are merged in warp order, the
 // splits' partials in index order: a token's result does not depend on the batch or on page numbers.
 // Up to eight splits of a (request, key/value head) run as ONE thread-block cluster (CLUSTER): each
-// CTA leaves its partial in its own shared memory, and after a cluster barrier the CTAs read all of
-// them through distributed shared memory, each finishing a slice of the output. More splits run as
+// CTA finishes a slice of the output; every CTA stores its partial's shares into the shared memory
+// of the CTAs that finish them (distributed shared memory), and one cluster barrier later each CTA
+// finds all it needs in its own shared memory. More splits run as
 // several clusters of eight: every cluster merges its own splits the same way into ONE partial in
 // global memory, and the cluster that arrives last (a fence and a counter) merges those. Without
 // clusters every split's partial goes through global memory (about 2 us slower at six splits, and
@@ -76,6 +77,13 @@ struct DecLayout {
 // Byte offset of (row, 16-byte chunk) inside a [TK][64] tile written by TMA with 128-byte swizzle.
 __device__ __forceinline__ uint32_t sw128(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
 
+// One float into the shared memory of CTA `rank` of this cluster, at the address `smem_addr` has here.
+__device__ __forceinline__ void store_to_cta(uint32_t smem_addr, int rank, float v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
 template <int HD, bool FUSED, bool DEEP, bool CLUSTER>
 __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                                  const __grid_constant__ CUtensorMap map_v,
@@ -90,7 +98,10 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
   uint64_t* empty = full + NS;                                              // [NS]
   int* flags = reinterpret_cast<int*>(empty + NS);                          // [0] abort, [1] tiles issued, [2] is_last
   bf16* kv_new = reinterpret_cast<bf16*>(flags + 4);                        // [2][HD]: the token's own key and value (fused form)
-  int* page_s = reinterpret_cast<int*>(kv_new + 2 * HD);                    // the split's slice of the block table
+  // CLUSTER: where the peers store their shares of the partials. It must be memory that this CTA
+  // uses for nothing else: a faster peer writes here while this CTA's ring is still in use.
+  float* recv = reinterpret_cast<float*>(kv_new + 2 * HD);                  // [size][epo] outputs, then [size][g][2] (max, sum)
+  int* page_s = reinterpret_cast<int*>(recv + (CLUSTER ? (p.nq / p.nkv) * (HD + 16) + 8 : 0));  // (+8: shares are rounded up per rank)  // the split's slice of the block table
   volatile int* abort_flag = flags;
 
   dep_launch();
@@ -415,18 +426,18 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
         }
       }
     }
-    if (CLUSTER && p.n_splits > 1) {  // the peers wait at two cluster barriers: take part, with nothing to offer
+    if (CLUSTER && p.n_splits > 1) {  // the peers wait at the cluster barriers: take part, with nothing to offer
       __syncthreads();
       asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+      if (p.n_splits > p.cluster_size)
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     return;
   }
   // ---- merge the four warps (in warp order)
   const float* mg = reinterpret_cast<const float*>(ring);
   constexpr int MLD = HD + 2;
-  constexpr int XCHG_OFFSET = 4 * ROWS * MLD * 4;  // behind the warps' partials in the ring (the ring is longer)
-  static_assert(XCHG_OFFSET + ROWS * MLD * 4 <= NS * L::STAGE_BYTES, "the exchange area does not fit the ring");
+  static_assert(4 * ROWS * MLD * 4 <= NS * L::STAGE_BYTES, "the warps' partials do not fit the ring");
   for (int e = tid; e < g * HD; e += DEC_THREADS) {
     const int row = e / HD, d = e - row * HD;
     float mx = -INFINITY;
@@ -447,11 +458,15 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
     if (p.n_splits == 1) {
       p.out[(size_t)tok * p.ld_out + (size_t)head * HD + d] = __float2bfloat16_rn(acc * inv);
     } else if (CLUSTER) {
-      float* mine = reinterpret_cast<float*>(ring + XCHG_OFFSET);  // [row][HD + 2]: this split's partial for its peers
-      mine[row * MLD + d] = acc * inv;
+      // element e of the cluster's output is finished by rank e % size: send it this split's share
+      const int csize = p.cluster_size, rank = split % csize, epo = (g * HD + csize - 1) / csize;
+      const uint32_t recv_a = smem_u32(recv);
+      store_to_cta(recv_a + (uint32_t)(rank * epo + e / csize) * 4u, e % csize, acc * inv);
       if (d == 0) {
-        mine[row * MLD + HD] = mx;
-        mine[row * MLD + HD + 1] = den;
+        for (int c = 0; c < csize; ++c) {
+          store_to_cta(recv_a + (uint32_t)(csize * epo + (rank * g + row) * 2) * 4u, c, mx);
+          store_to_cta(recv_a + (uint32_t)(csize * epo + (rank * g + row) * 2 + 1) * 4u, c, den);
+        }
       }
     } else {
       const size_t slot = ((size_t)split * p.part_stride_tokens + tok) * p.nq + head;
@@ -465,12 +480,15 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
   if (p.n_splits == 1) return;
   int n_merge = p.n_splits;  // partials that meet in global memory
   if constexpr (CLUSTER) {
-    // ---- eight (or fewer) neighbouring splits are the CTAs of this cluster: every CTA finishes the
-    // elements e = rank, rank + size, ... from the cluster's partials, in index order
+    // ---- eight (or fewer) neighbouring splits are the CTAs of this cluster: every CTA has sent each
+    // peer its share (remote shared-memory stores above) and, after the barrier, finishes the
+    // elements e = rank, rank + size, ... from what it received, in index order
     const int csize = p.cluster_size, rank = split % csize, group = split / csize;
     n_merge = p.n_splits / csize;
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    const uint32_t mine = smem_u32(ring + XCHG_OFFSET);
+    const int epo = (g * HD + csize - 1) / csize;
+    const float* recv_o = recv;
+    const float* recv_ml = recv_o + csize * epo;
     for (int k = tid; k * csize + rank < g * HD; k += DEC_THREADS) {
       const int e = k * csize + rank;
       const int row = e / HD, d = e - row * HD;
@@ -479,11 +497,9 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
       for (int sp = 0; sp < 8; ++sp) {
         m[sp] = -INFINITY; l[sp] = 0.f; v[sp] = 0.f;
         if (sp < csize) {
-          uint32_t peer;
-          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(mine + (uint32_t)(row * MLD) * 4u), "r"(sp));
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(m[sp]) : "r"(peer + (uint32_t)HD * 4u));
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(l[sp]) : "r"(peer + (uint32_t)(HD + 1) * 4u));
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[sp]) : "r"(peer + (uint32_t)d * 4u));
+          m[sp] = recv_ml[(sp * g + row) * 2];
+          l[sp] = recv_ml[(sp * g + row) * 2 + 1];
+          v[sp] = recv_o[sp * epo + k];
         }
       }
       float mx = -INFINITY;
@@ -511,10 +527,10 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
         }
       }
     }
-    if (n_merge > 1) __threadfence();  // the cluster's partial is out before its leader counts it
-    // nobody leaves while a peer may still read its partial
+    if (n_merge == 1) return;  // (a CTA may leave at once: its peers read their own shared memory only)
+    __threadfence();  // every CTA's slice of the cluster's partial is out before the leader counts it
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    if (n_merge == 1 || rank != 0) return;
+    if (rank != 0) return;
   }
   // ---- the CTA (the cluster's leader) that arrives last for this (request, key/value head) merges
   // the partials, in index order whichever one that is
@@ -570,16 +586,16 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
 int g_cluster_merge = 1;  // 0: splits always merge through global memory (for comparisons)
 
 template <int HD, bool DEEP>
-size_t decode_smem_bytes(int keys_per_cta, int page_size) {
+size_t decode_smem_bytes(int keys_per_cta, int page_size, int cluster_group) {  // cluster_group: heads per kv head, 0 without clusters
   using L = DecLayout<HD, DEEP>;
-  return 1024 + (size_t)L::STAGES * L::STAGE_BYTES + (size_t)ROWS * L::Q_LD * 2 + 2 * L::STAGES * 8 + 16 + 2 * HD * 2 +
+  return (cluster_group ? (size_t)(cluster_group * (HD + 16) + 8) * sizeof(float) : 0) + 1024 + (size_t)L::STAGES * L::STAGE_BYTES + (size_t)ROWS * L::Q_LD * 2 + 2 * L::STAGES * 8 + 16 + 2 * HD * 2 +
          (size_t)((keys_per_cta + 2 * TK) / page_size + 4) * sizeof(int);
 }
 
 template <int HD, bool FUSED, bool DEEP, bool CLUSTER>
 int launch_decode_ring(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int n_seqs, cudaStream_t stream) {
   const int keys_per_cta = p.n_splits > 1 ? p.split_keys : p.max_blocks * p.page_size;
-  const size_t smem = decode_smem_bytes<HD, DEEP>(keys_per_cta, p.page_size);
+  const size_t smem = decode_smem_bytes<HD, DEEP>(keys_per_cta, p.page_size, CLUSTER ? p.nq / p.nkv : 0);
   if (smem > 200 * 1024) return 2;
   auto kernel = paged_attention_decode_tma_kernel<HD, FUSED, DEEP, CLUSTER>;
   static size_t attr_bytes = 0;  // the largest size asked for so far
