@@ -239,12 +239,14 @@ __global__ void __launch_bounds__(128)
 // lane 0: TMA; warp 5 lane 0: tcgen05.mma. Waits are bounded as in the one-tile kernel.
 constexpr int PERSIST_THREADS = 192;
 
-template <typename TO, bool SWIGLU>
+template <typename TO, bool SWIGLU, int BN>
 __global__ void __launch_bounds__(PERSIST_THREADS)
     gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                               TO* __restrict__ out, int RA, int RB, int k_tiles, long long ldo, int stages, int m_tiles,
                               int n_tiles, int* __restrict__ error_out) {
-  constexpr int BN = 256;
+  static_assert(BN == 256 || BN == 192, "two accumulators of BN columns, 256 columns apart, in 512 columns of tensor memory");
+  static_assert(!SWIGLU || BN == 256, "the gate|up blocks are 256 rows");
+  constexpr int ACC_STRIDE = 256;  // tensor-memory columns from one accumulator to the other
   constexpr int B_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   extern __shared__ uint8_t smem_raw[];
@@ -351,7 +353,7 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
-        const uint32_t acc = tmem_base + (uint32_t)(b * BN);
+        const uint32_t acc = tmem_base + (uint32_t)(b * ACC_STRIDE);
         for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
           const int s = (int)(it % stages);
           const uint32_t ph = (uint32_t)(it / stages) & 1u;
@@ -381,7 +383,7 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
       const int tile = blockIdx.x + t * gridDim.x;
       const int a_row0 = (tile % m_tiles) * BM, b_row0 = (tile / m_tiles) * BN;
       const int ra = a_row0 + warp * 32 + lane;
-      const uint32_t acc = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(b * BN);
+      const uint32_t acc = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(b * ACC_STRIDE);
       if (SWIGLU) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN / 2; c0 += 16) {
@@ -682,14 +684,14 @@ int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int 
   return LLM_OK;
 }
 
-template <typename TO, bool SWIGLU>
+template <typename TO, bool SWIGLU, int BN = 256>
 int launch_tc_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, long long ldo,
                          int n_sms, cudaStream_t stream) {
-  constexpr int STAGE_BYTES = A_BYTES + 256 * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + BN * BK * 2;
   const int k_tiles = (K + BK - 1) / BK;
-  const int stages = 4;
+  const int stages = BN == 256 ? 4 : 5;
   const size_t smem = (size_t)stages * STAGE_BYTES + (2 * stages + 4) * sizeof(uint64_t) + 16 + 1024;
-  auto kernel = gemm_tc_persistent_kernel<TO, SWIGLU>;
+  auto kernel = gemm_tc_persistent_kernel<TO, SWIGLU, BN>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
@@ -698,7 +700,7 @@ int launch_tc_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out
     }
     attr_set = true;
   }
-  const int m_tiles = (RA + BM - 1) / BM, n_tiles = (RB + 255) / 256;
+  const int m_tiles = (RA + BM - 1) / BM, n_tiles = (RB + BN - 1) / BN;
   const int grid = std::min(m_tiles * n_tiles, n_sms);
   launch_kernel(kernel, grid, PERSIST_THREADS, smem, stream, ma, mb, (TO*)out, RA, RB, k_tiles, ldo, stages, m_tiles, n_tiles,
                 error_word());
@@ -717,6 +719,16 @@ int sm_count() {
 
 // The persistent form pays when an SM gets several tiles.
 inline bool use_persistent(int M, int N) { return ((M + BM - 1) / BM) * ((N + 255) / 256) >= 2 * sm_count(); }
+
+// Tiles of 192 outputs instead of 256 when that shortens the last round: the product takes
+// (rounds of tiles over the SMs) x (tile width), e.g. 2,048 tokens x 3,072 outputs: 192 tiles of 256
+// are two rounds (512), 256 tiles of 192 also two (384).
+inline bool prefer_192(int M, int N) {
+  const int m_tiles = (M + BM - 1) / BM, sms = sm_count();
+  const int t256 = m_tiles * ((N + 255) / 256), t192 = m_tiles * ((N + 191) / 192);
+  const int cost256 = (t256 + sms - 1) / sms * 256, cost192 = (t192 + sms - 1) / sms * 192;
+  return t192 > sms && cost192 < cost256;
+}
 
 template <int BN, bool SWAP, typename TO, bool SWIGLU = false>
 int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, int splits, long long ldo,
@@ -793,6 +805,10 @@ extern "C" int llm_gemm_tc(const void* a, const void* w, void* out, int M, int N
       LLM_REQUIRE(tensor_map_for(w, N, K, ldw, 128, &mb), "gemm_tc: cuTensorMapEncodeTiled failed");
       rc = (out_dtype == LLM_F32) ? launch_tc_pair<float, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream)
                                   : launch_tc_pair<bf16, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream);
+    } else if (bn == 256 && g_persistent && prefer_192(M, N)) {
+      LLM_REQUIRE(tensor_map_for(w, N, K, ldw, 192, &mb), "gemm_tc: cuTensorMapEncodeTiled failed");
+      rc = (out_dtype == LLM_F32) ? launch_tc_persistent<float, false, 192>(ma, mb, out, M, N, K, ldo, sm_count(), stream)
+                                  : launch_tc_persistent<bf16, false, 192>(ma, mb, out, M, N, K, ldo, sm_count(), stream);
     } else if (bn == 256 && g_persistent && use_persistent(M, N))
       rc = (out_dtype == LLM_F32) ? launch_tc_persistent<float, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream)
                                   : launch_tc_persistent<bf16, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream);

@@ -144,7 +144,8 @@ def test_gemm_with_fused_swiglu(ops, M, FF, K):
     assert ops.tensor_core_error() == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(300, 25617, 192), (129, 76000, 64), (1100, 8704, 256)])
+@pytest.mark.parametrize("M,N,K", [(300, 25617, 192), (129, 76000, 64), (1100, 8704, 256), (2048, 3072, 128), (1500, 5120, 64),
+                                   (2048, 3000, 64)])  # the last three: tiles of 192 outputs shorten the last round
 def test_gemm_persistent_form(ops, M, N, K):
     """Enough output tiles that every SM gets several: the persistent kernel (two accumulators in
     tensor memory, epilogue beside the next tile's products) against float64, tails in every
