@@ -124,13 +124,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
 
   dep_launch();
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int seq = blockIdx.y, kvh = blockIdx.z;
+  const int seq = blockIdx.y, kvh = blockIdx.x;
   const int g = p.nq / p.nkv;
   const int tq_cap = ROWS / g;
   // the batch arrays came with the step's host-to-device copy: they may be read before the wait
   const int ntok = p.seq_ntok[seq];
-  // late query tiles see the most keys: they are scheduled first so that the grid's tail is short
-  const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * tq_cap;
+  // Late query tiles see the most keys. CTAs start in the order x, y, z, so the query tile is the z
+  // index, latest first: the long CTAs of every head and request run before any short one, and
+  // the grid's tail is made of short CTAs.
+  const int q0 = (int)(gridDim.z - 1 - blockIdx.z) * tq_cap;
   if (q0 >= ntok) return;
   const int n_tq = min(tq_cap, ntok - q0);
   const int n_rows = n_tq * g;
@@ -167,7 +169,32 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
   // key/value stages start as zeros: rows that no copy fills (beyond the request's last page) are
   // multiplied by probabilities of exactly zero and must not hold NaN patterns
   for (int i = tid; i < 4 * KV_BYTES / 16; i += ATT_THREADS) reinterpret_cast<uint4*>(kv_s)[i] = make_uint4(0, 0, 0, 0);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the zeros are in place before any copy lands on them
+  __syncthreads();
+  auto issue_tile = [&](int i) {  // keys and values of tile i -> stage i % 2; pages beyond the newest key are not fetched
+    const int first_key = (kt_first + i) * KEYS;
+    uint8_t* ks = kv_s + (size_t)(i & 1) * 2 * KV_BYTES;
+    uint8_t* vs = ks + KV_BYTES;
+    int n_pages = 0;
+    for (int pg = 0; pg < pages_per_tile; ++pg)
+      if (first_key + pg * p.page_size <= hi) n_pages = pg + 1;
+    mbar_expect_tx(&full[i & 1], (uint32_t)(n_pages * p.page_size * HD * 2 * 2));
+    for (int pg = 0; pg < n_pages; ++pg) {
+      const int page = page_s[(first_key + pg * p.page_size) / p.page_size - page_lo];
+      const int row = (page * p.nkv + kvh) * p.page_size;
+#pragma unroll
+      for (int b = 0; b < DBLK; ++b) {
+        tma_load_2d(ks + b * (KEYS * 128) + (size_t)pg * p.page_size * 128, &map_k, b * 64, row, &full[i & 1]);
+        tma_load_2d(vs + b * (KEYS * 128) + (size_t)pg * p.page_size * 128, &map_v, b * 64, row, &full[i & 1]);
+      }
+    }
+  };
   dep_wait();
+  // the first two tiles are on their way while the query rows are fetched
+  if (tid == 4 * 32) {
+    issue_tile(0);
+    if (n_tiles > 1) issue_tile(1);
+  }
   // ---- Q rows -> shared memory in the swizzled K-major layout (16-byte chunk c of row r at c ^ (r % 8))
   if (tid < ROWS) {
     const int r = tid;
@@ -195,24 +222,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
   if (warp == 4) {
     if (tid == 4 * 32) {
       // ------------------------------------------------------------ the thread that issues TMA and MMA
-      auto issue_tile = [&](int i) {  // keys and values of tile i -> stage i % 2; pages beyond the newest key are not fetched
-        const int first_key = (kt_first + i) * KEYS;
-        uint8_t* ks = kv_s + (size_t)(i & 1) * 2 * KV_BYTES;
-        uint8_t* vs = ks + KV_BYTES;
-        int n_pages = 0;
-        for (int pg = 0; pg < pages_per_tile; ++pg)
-          if (first_key + pg * p.page_size <= hi) n_pages = pg + 1;
-        mbar_expect_tx(&full[i & 1], (uint32_t)(n_pages * p.page_size * HD * 2 * 2));
-        for (int pg = 0; pg < n_pages; ++pg) {
-          const int page = page_s[(first_key + pg * p.page_size) / p.page_size - page_lo];
-          const int row = (page * p.nkv + kvh) * p.page_size;
-#pragma unroll
-          for (int b = 0; b < DBLK; ++b) {
-            tma_load_2d(ks + b * (KEYS * 128) + (size_t)pg * p.page_size * 128, &map_k, b * 64, row, &full[i & 1]);
-            tma_load_2d(vs + b * (KEYS * 128) + (size_t)pg * p.page_size * 128, &map_v, b * 64, row, &full[i & 1]);
-          }
-        }
-      };
       auto issue_scores = [&](int i) {  // S = Q K^T of tile i
         constexpr uint32_t idesc_s = instr_desc_att(KEYS, false);
 #pragma unroll
@@ -223,8 +232,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
         }
         mma_commit(s_bar);
       };
-      issue_tile(0);
-      if (n_tiles > 1) issue_tile(1);
       ok = mbar_wait(&full[0], 0, abort_flag, p.error_out, ERR_ATT_KV);
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -400,6 +407,7 @@ extern "C" int llm_paged_attention_tc(const void* q, long long ld_q, const void*
   auto al = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
   LLM_REQUIRE(al(q) && al(kcache) && al(vcache) && al(out), "attention_tc: q, the caches and out must be 16-byte aligned");
   LLM_REQUIRE(max_blocks > 0 && window >= 0 && n_seqs <= 65535 && nkv <= 65535, "attention_tc: bad sizes");
+  LLM_REQUIRE((long long)max_new_tokens * (nq / nkv) <= 65535LL * ROWS, "attention_tc: portion too long for the grid");
   LLM_REQUIRE(error_word() != nullptr, "attention_tc: cannot allocate the error word");
   CUtensorMap mk, mv;
   const long long rows = n_cache_pages * nkv * page_size;
@@ -411,7 +419,7 @@ extern "C" int llm_paged_attention_tc(const void* q, long long ld_q, const void*
   p.out = (bf16*)out; p.ld_out = ld_out; p.error_out = error_word();
   LLM_REQUIRE(max_blocks <= 4096, "attention_tc: block tables wider than 4096 pages are not supported");
   const int g = nq / nkv, tq_cap = ROWS / g;
-  dim3 grid((max_new_tokens + tq_cap - 1) / tq_cap, n_seqs, nkv);
+  dim3 grid(nkv, n_seqs, (max_new_tokens + tq_cap - 1) / tq_cap);
   bool attr_ok = true;
   if (hd == 64) attr_ok = launch_att<64>(mk, mv, p, grid, max_blocks, stream);
   else attr_ok = launch_att<128>(mk, mv, p, grid, max_blocks, stream);
