@@ -13,7 +13,7 @@ float32 pool for all layers with layout [K l0..][V l0..] per block (src/paged_kv
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 

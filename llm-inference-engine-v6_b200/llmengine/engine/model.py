@@ -7,7 +7,7 @@ for positions whose logits are not asked for, src/engine.cpp:415-433).
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence
+from typing import List, Optional, Sequence
 
 import torch
 

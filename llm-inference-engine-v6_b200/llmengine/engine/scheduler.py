@@ -9,7 +9,7 @@ budget.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import List, Sequence
 
 from ..cache.host import host_module
 

@@ -16,7 +16,7 @@ from typing import Dict
 
 import torch
 
-from ..config.registry import Architecture, get_architecture
+from ..config.registry import get_architecture
 from ..parts.registry import part_class
 from ..parts.spec import ModelSpec, TensorNeed
 from .loader import merge_needs

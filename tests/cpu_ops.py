@@ -7,7 +7,6 @@ llmengine/ops.py, not the kernels' code.
 """
 from __future__ import annotations
 
-import math
 
 import numpy as np
 import torch

@@ -1,10 +1,9 @@
 """Configuration parsing and the architecture registry (no GPU)."""
 import json
-import os
 
 import pytest
 
-from llmengine.config import (Architecture, ConfigError, LlamaConfig, architecture_names, config_from_dir,
+from llmengine.config import (ConfigError, LlamaConfig, architecture_names, config_from_dir,
                               get_architecture, register_architecture)
 from llmengine.models.llama import describe_llama
 from tiny import TINY_A, TINY_B

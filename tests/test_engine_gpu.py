@@ -4,7 +4,6 @@ with state of its own that is registered, built and stepped without touching the
 import json
 import os
 from dataclasses import dataclass
-from typing import Tuple
 
 import numpy as np
 import pytest

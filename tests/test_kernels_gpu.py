@@ -2,7 +2,6 @@
 the engine's tiny models use (non powers of two, tails, strided views)."""
 import math
 
-import numpy as np
 import pytest
 import torch
 

@@ -1,7 +1,6 @@
 """Each part of a layer alone (norm, position encoding, attention mixer, feed-forward, block) on the
 GPU against the plain implementation's function for it, in 32-bit and in bfloat16, at sizes that are
 not the tiny models'."""
-import math
 
 import numpy as np
 import pytest

@@ -2,7 +2,6 @@
 above the step function with a CPU test double of the kernels against the plain implementation.
 No GPU. What happens when pages run out is decided and tested here: the request that cannot
 reserve ends with "capacity" and keeps what it generated; nobody waits, nobody is preempted."""
-import numpy as np
 import pytest
 import torch
 
