@@ -77,12 +77,13 @@ class DecodeGraphs:
         ws.frozen = True
         graph = torch.cuda.CUDAGraph()
         before = eng.ops.launches
+        # the sampled tokens are written straight into pinned host memory: no copy to enqueue afterwards
+        c.host_tokens = torch.zeros(cap, dtype=torch.int32, pin_memory=True)
         with torch.cuda.graph(graph):
             logits = eng.model.forward(ctx)
-            c.tokens = sampler.sample_device(logits, ctx, cap)
+            c.tokens = sampler.sample_device(logits, ctx, cap, out=c.host_tokens)
         c.kernels = eng.ops.launches - before
         c.graph = graph
-        c.host_tokens = torch.empty(cap, dtype=torch.int32, pin_memory=True)
         layout = H.StepLayout.make(cap, cap, cap, blocks, eng.cm.num_groups)
         c.refill = lambda entries: c.buffers.refill(eng.cm, entries, layout, eng.spec.vocab_size, eng.max_pos)
         return c
@@ -108,7 +109,6 @@ class DecodeGraphs:
         c.refill(entries)
         c.graph.replay()
         eng.ops.launches += c.kernels
-        c.host_tokens.copy_(c.tokens, non_blocking=True)  # all `cap` of them: no views to make
         torch.cuda.current_stream().synchronize()
         self.h2d_bytes, self.d2h_bytes = c.buffers.h2d_bytes, 4 * cap
         return c.host_tokens.tolist()[:seqs]

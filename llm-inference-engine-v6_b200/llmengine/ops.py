@@ -443,7 +443,9 @@ class CudaOps:
                n_rows: Optional[int] = None, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
         """out[r] (int32) = greedy or temperature choice for logits row r (float32). scratch: int32
         tensor of sample_scratch_words(rows, vocab) elements (made here when not given)."""
-        _need(logits, "sample.logits", torch.float32); _need(out, "sample.out", torch.int32)
+        _need(logits, "sample.logits", torch.float32)
+        if not (out.is_cuda or out.is_pinned()) or out.dtype != torch.int32 or not out.is_contiguous():
+            raise KernelError("sample.out: expected a contiguous int32 tensor on the device or in pinned host memory")
         n = logits.shape[0] if n_rows is None else n_rows
         for t, nm in ((temperature, "temperature"), (seeds, "seeds"), (draws, "draws")):
             if t is not None:

@@ -34,10 +34,13 @@ class Sampler:
             self._scratch = torch.empty(max(words, 1024), dtype=torch.int32, device=self.device)
         return self._scratch
 
-    def sample_device(self, logits: torch.Tensor, ctx, n_rows: Optional[int] = None) -> torch.Tensor:
-        """-> int32 device tensor [rows]; the rows' parameters come from the step's batch."""
+    def sample_device(self, logits: torch.Tensor, ctx, n_rows: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """-> int32 tensor [rows]; the rows' parameters come from the step's batch. `out` may be given:
+        a device tensor, or pinned host memory that the kernel writes through its mapped address (the
+        host then needs no copy, only to wait for the stream)."""
         n = logits.shape[0] if n_rows is None else n_rows
-        out, _ = self._buffers(max(n, 1))
+        if out is None:
+            out, _ = self._buffers(max(n, 1))
         if n:
             self.ops.sample(logits, out, ctx.row_temperature, ctx.row_seed, ctx.row_draw, n_rows=n,
                             scratch=self._scratch_for(n, logits.shape[1]))
