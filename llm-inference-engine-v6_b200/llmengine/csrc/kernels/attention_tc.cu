@@ -283,21 +283,19 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
       tmem_load_wait();  // four loads in flight, one wait
       const int key0 = (kt_first + i) * KEYS;
       const bool full_tile = (key0 + KEYS - 1 <= pos_r) && (key0 >= lo_r);
+      // s stays unscaled: max(s * c) = c * max(s) for c > 0, and the scale folds into the exponent's
+      // multiply-add below, which saves an instruction per score in a loop that is bound by issue slots
       float mx = -INFINITY;
-      if (full_tile) {
-#pragma unroll
-        for (int j = 0; j < KEYS; ++j) {
-          s[j] *= sl2;
-          mx = fmaxf(mx, s[j]);
-        }
-      } else {
+      if (!full_tile) {
 #pragma unroll
         for (int j = 0; j < KEYS; ++j) {
           const int key = key0 + j;
-          s[j] = (key <= pos_r && key >= lo_r) ? s[j] * sl2 : -INFINITY;
-          mx = fmaxf(mx, s[j]);
+          s[j] = (key <= pos_r && key >= lo_r) ? s[j] : -INFINITY;
         }
       }
+#pragma unroll
+      for (int j = 0; j < KEYS; ++j) mx = fmaxf(mx, s[j]);
+      mx *= sl2;  // (-inf stays -inf)
       // The running max is only moved when it would grow by more than 2^8: until then the row keeps
       // its older, smaller reference (probabilities up to 256 instead of 1, harmless in float32 and
       // bfloat16) and its sum and output need no rescaling. Sum and output always share one reference.
@@ -309,7 +307,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
       uint32_t packed[KEYS / 2];
 #pragma unroll
       for (int j = 0; j < KEYS; j += 2) {
-        const float p0 = fast_exp2(s[j] - base), p1 = fast_exp2(s[j + 1] - base);
+        const float p0 = fast_exp2(fmaf(s[j], sl2, -base)), p1 = fast_exp2(fmaf(s[j + 1], sl2, -base));
         sum += p0 + p1;
         __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
         packed[j / 2] = *reinterpret_cast<uint32_t*>(&t);

@@ -61,8 +61,15 @@ def test_real_layer_sizes_prompt_portions_and_decoding(tmp_path, sizes):
         got.append(eng.run_step([(1, ids[t:t + 1], [0])], end=[1] if t == T - 1 else []).clone())
     got = torch.cat(got).cpu().numpy()
     assert eng.ops.tensor_core_error() == 0
-    err = np.abs(got - ref).max(axis=1)
-    assert err.max() < 6e-2, f"largest difference per row: {err}"
+    # 12 rows x 128,256 logits of standard deviation ~1.1: the bfloat16 path differs from the plain
+    # float32 one by rounding noise of root mean square 0.0107 (both layer sizes, every kernel version
+    # so far), whose largest of 1.5 million samples is about 5.3 sigma = 0.057 and moves by +-0.005
+    # with any reordering of sums. So the bound on the noise is on its root mean square; the largest
+    # difference only has to stay where noise of that size can reach (a lost key, page or position
+    # moves a whole row by the order of the logits themselves).
+    diff = got - ref
+    assert np.sqrt((diff ** 2).mean()) < 1.3e-2, f"rms difference {np.sqrt((diff ** 2).mean())}"
+    assert np.abs(diff).max() < 8 * 1.3e-2, f"largest difference per row: {np.abs(diff).max(axis=1)}"
     # the same tokens chosen by both
     assert (got.argmax(1) == ref.argmax(1)).all()
 
