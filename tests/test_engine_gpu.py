@@ -422,15 +422,21 @@ def test_layer_order_is_data(tmp_path):
     np.testing.assert_allclose(torch.cat([first, second]).cpu().numpy(), ref, atol=2e-4, rtol=0)
 
 
-def test_window_layers_share_the_engine_with_full_layers(tmp_path):
-    """A model whose first layer reads a window of the last 9 keys and whose second reads all of
+@pytest.mark.parametrize("which", ["a", "d"])
+def test_window_layers_share_the_engine_with_full_layers(tmp_path, which):
+    """A model whose first layer reads a window of the last W keys and whose second reads all of
     them: two cache groups with their own pages; the window group gives pages back while a request
-    is still running, and they are used again by the next one."""
+    is still running, and they are used again by the next one. Configuration A (head size 16, pages
+    of 4, W = 9) and D (head size 64, pages of 16, W = 70: the tensor-core kernels, with block-table
+    entries of pages that were given back)."""
     from dataclasses import replace
     from llmengine.config.registry import Architecture, register_architecture
     from llmengine.config.llama import LlamaConfig
     from llmengine.models.llama import describe_llama
-    W = 9
+    from tiny import TINY_D
+    base, page, W, T, cuts = {"a": (TINY_A, 4, 9, 41, (6, 2, 13, 1, 1, 9, 9)),
+                              "d": (TINY_D, 16, 70, 300, (40, 2, 90, 1, 1, 100, 33, 1, 1, 1, 30))}[which]
+    assert sum(cuts) == T
 
     def describe(cfg):
         spec = describe_llama(cfg)
@@ -440,14 +446,17 @@ def test_window_layers_share_the_engine_with_full_layers(tmp_path):
 
     register_architecture(Architecture("WindowedModel", LlamaConfig.from_dict, describe,
                                        lambda c: dict(c.to_dict(), architectures=["WindowedModel"])), replace=True)
-    cfg = dict(TINY_A, architectures=["WindowedModel"])
-    T, hd, nq, nkv = 41, 16, 4, 2
+    cfg = dict(base, architectures=["WindowedModel"])
+    hd, nq, nkv, V = base["head_dim"], base["num_attention_heads"], base["num_key_value_heads"], base["vocab_size"]
+    n_pages = (T + page - 1) // page + 2
     for dtype, wdt, tol in (("fp32", torch.float32, 2e-4), ("bf16", torch.bfloat16, 6e-2)):
         d = str(tmp_path / f"windowed_{dtype}")
         llmengine.write_random_model(d, cfg, seed=8, dtype=wdt, std=0.05)
         pc, w = P.read_model(d)
-        ids = random_ids(T, 256, 12)
-        cos, sin = P.rope_tables(P.llama3_inv_freq(hd, pc["rope_theta"], False, 1, 1, 1, 0), T, hd)
+        ids = random_ids(T, V, 12)
+        inv = P.llama3_inv_freq(hd, pc["rope_theta"], pc["rope_has_scaling"], pc["rope_factor"], pc["rope_low_freq_factor"],
+                                pc["rope_high_freq_factor"], pc["rope_original_max_pos"])
+        cos, sin = P.rope_tables(inv, T, hd)
         h = P.embed(w["model.embed_tokens.weight"], ids)
         for l in range(2):
             p = f"model.layers.{l}."
@@ -462,25 +471,26 @@ def test_window_layers_share_the_engine_with_full_layers(tmp_path):
             h = h + P.linear(a, w[p + "self_attn.o_proj.weight"])
             x = P.rmsnorm(h, w[p + "post_attention_layernorm.weight"], pc["rms_norm_eps"])
             h = h + P.swiglu_mlp(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
-        ref = P.linear(P.rmsnorm(h, w["model.norm.weight"], pc["rms_norm_eps"]), w["lm_head.weight"])
-        eng = llmengine.Engine(d, dtype, block_size=4, num_blocks=12, max_concurrent=2)  # 48 tokens of pages per group
+        head = w["model.embed_tokens.weight"] if pc["tie_word_embeddings"] else w["lm_head.weight"]
+        ref = P.linear(P.rmsnorm(h, w["model.norm.weight"], pc["rms_norm_eps"]), head)
+        eng = llmengine.Engine(d, dtype, block_size=page, num_blocks=n_pages, max_concurrent=2)  # a little more than one request's pages per group
         eng.configure_cache()
         assert eng.cm.num_groups == 2 and sorted(eng.cm.window(g) for g in range(2)) == [0, W]
         gw = [g for g in range(2) if eng.cm.window(g) == W][0]
         got, pos = [], 0
-        for n in (6, 2, 13, 1, 1, 9, 9):
+        for n in cuts:
             got.append(eng.run_step([(1, ids[pos:pos + n], range(n))]).clone())
             pos += n
             held = sum(pg >= 0 for pg in eng.cm.block_table(1, gw))
-            assert held <= (W + 3) // 4 + 1  # the window group never holds more than the window needs
-        assert sum(pg >= 0 for pg in eng.cm.block_table(1, 1 - gw)) == (T + 3) // 4
+            assert held <= (W + page - 1) // page + 1  # the window group never holds more than the window needs
+        assert sum(pg >= 0 for pg in eng.cm.block_table(1, 1 - gw)) == (T + page - 1) // page
         np.testing.assert_allclose(torch.cat(got).float().cpu().numpy(), ref, atol=tol, rtol=0)
-        # a second request of 41 tokens fits beside the first only because window pages came back
+        # a second request of the same length goes through the pages that came back
         eng.run_step([], end=[1])
         again = eng.run_step([(2, ids, range(T))], end=[2])
         np.testing.assert_allclose(again.float().cpu().numpy(), ref, atol=tol, rtol=0)
         eng.cm.check()
-        assert eng.cm.free_pages(0) == 12 and eng.cm.free_pages(1) == 12
+        assert eng.cm.free_pages(0) == n_pages and eng.cm.free_pages(1) == n_pages
 
 
 def _window_row(q, k, v, nq, nkv, hd):
