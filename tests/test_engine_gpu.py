@@ -11,16 +11,17 @@ import torch
 
 import llmengine
 import plain_llama as P
-from tiny import TINY_A, TINY_B, make_model_dir, random_ids
+from tiny import TINY_A, TINY_B, TINY_D, make_model_dir, random_ids
 
 pytestmark = pytest.mark.gpu
 TOL = {"fp32": 2e-4, "bf16": 6e-2}
 
 
-@pytest.fixture(scope="module", params=[("a", "fp32"), ("a", "bf16"), ("b", "fp32"), ("b", "bf16")], ids=lambda p: f"{p[0]}-{p[1]}")
+@pytest.fixture(scope="module", params=[("a", "fp32"), ("a", "bf16"), ("b", "fp32"), ("b", "bf16"), ("d", "fp32"), ("d", "bf16")],
+                ids=lambda p: f"{p[0]}-{p[1]}")
 def setup(request, tmp_path_factory):
     name, dtype = request.param
-    cfg = {"a": TINY_A, "b": TINY_B}[name]
+    cfg = {"a": TINY_A, "b": TINY_B, "d": TINY_D}[name]  # d: head size 64, pages of 16: the tensor-core attention kernels
     d = str(tmp_path_factory.mktemp(f"eng_{name}_{dtype}"))
     make_model_dir(d, cfg, torch.float32 if dtype == "fp32" else torch.bfloat16)
     pc, pw = P.read_model(d)
@@ -433,7 +434,6 @@ def test_window_layers_share_the_engine_with_full_layers(tmp_path, which):
     from llmengine.config.registry import Architecture, register_architecture
     from llmengine.config.llama import LlamaConfig
     from llmengine.models.llama import describe_llama
-    from tiny import TINY_D
     base, page, W, T, cuts = {"a": (TINY_A, 4, 9, 41, (6, 2, 13, 1, 1, 9, 9)),
                               "d": (TINY_D, 16, 70, 300, (40, 2, 90, 1, 1, 100, 33, 1, 1, 1, 30))}[which]
     assert sum(cuts) == T
