@@ -306,6 +306,7 @@ class CudaOps:
     ATTENTION_MAX_SPLITS = 128  # what the kernels' merge takes
     ATTENTION_MIN_SPLIT_KEYS = 320
     TC_ATTENTION_MIN_TOKENS = 32  # longest portion of the step from which the tcgen05 attention kernel is used
+    TC_ATTENTION_MAX_BLOCKS = 4096  # widest block table whose slice it keeps in shared memory (wider: the mma.sync kernel)
 
     def _split_policy(self, pairs: int, max_seq_len: int, hd: int = 64):
         """-> (number of key splits, keys per split) of a step of single tokens with `pairs` (request,
@@ -392,6 +393,7 @@ class CudaOps:
         if q.dtype == torch.bfloat16 and self.tensor_cores:
             lib = self.lib("tensorcore")
             if (self.tcgen05_attention and batch.max_new_tokens >= self.TC_ATTENTION_MIN_TOKENS and
+                    block_table.shape[1] <= self.TC_ATTENTION_MAX_BLOCKS and
                     lib.llm_attention_tc_supported(c_int(nq), c_int(nkv), c_int(hd), c_int(page), c_longlong(q.stride(0)),
                                                    c_longlong(out.stride(0)))):
                 # prompt portions: tcgen05 kernel (128 rows per CTA, scores and output in tensor memory)
