@@ -500,3 +500,49 @@ def _window_row(q, k, v, nq, nkv, hd):
         pr = np.exp(s - s.max())
         out[hh] = (pr / pr.sum()) @ v[:, hh // (nq // nkv)]
     return out.reshape(-1)
+
+
+@pytest.mark.parametrize("name,dtype,seed", [("d", "fp32", 1), ("a", "fp32", 2), ("e", "fp32", 3), ("d", "bf16", 4)])
+def test_scheduler_under_random_load_and_page_pressure(tmp_path, name, dtype, seed):
+    """Forty requests of random lengths, budgets and temperatures arrive while others run, through a
+    pool that holds about three of them: many end with "capacity". Every request's tokens are the
+    plain implementation's for the same prompt (32-bit; a token may differ only at a provable near
+    tie), "length" means exactly max_new_tokens, and no page is lost."""
+    from tiny import TINY
+    rng = np.random.default_rng(seed)
+    cfg, page = TINY[name]
+    d = str(tmp_path / "m")
+    make_model_dir(d, cfg, torch.float32 if dtype == "fp32" else torch.bfloat16)
+    pc, pw = P.read_model(d)
+    maxpos = cfg["max_position_embeddings"]
+    n_pages = (3 * maxpos // 2) // page
+    eng = llmengine.Engine(d, dtype, block_size=page, num_blocks=n_pages, max_concurrent=6)
+    sch = llmengine.ContinuousBatchScheduler(eng, None, max_concurrent=6, max_prefill_tokens_per_step=int(rng.integers(8, 100)))
+    reqs = {}
+    for i in range(40):
+        L = int(rng.integers(1, maxpos // 2))
+        new = int(rng.integers(0, min(60, maxpos - L)))
+        temp = float(rng.choice([0.0, 0.0, 1.0]))
+        prompt = rng.integers(0, cfg["vocab_size"], L).tolist()
+        reqs[sch.enqueue(prompt, new, temp, i)] = (prompt, new, temp, i)
+        if rng.random() < 0.5:
+            for _ in range(int(rng.integers(1, 6))):
+                sch.step()
+    sch.run_until_idle()
+    assert len(sch.results) == 40
+    reasons = set()
+    for r in sch.results:
+        prompt, new, temp, sd = reqs[r.seq_id]
+        toks = list(r.token_ids)
+        reasons.add(r.finish_reason)
+        assert toks[:len(prompt)] == prompt and r.finish_reason in ("length", "capacity")
+        gen = toks[len(prompt):]
+        if r.finish_reason == "length":
+            assert len(gen) == new
+        else:  # pages ran out during the prompt or before the last token
+            assert len(gen) < max(new, 1)
+        if gen:
+            check_stream(pc, pw, prompt, toks, TOL[dtype] if dtype == "bf16" else 5e-4, temperature=temp, seed=sd)
+    assert reasons == {"length", "capacity"}
+    eng.cm.check()
+    assert eng.cm.free_pages(0) == n_pages and eng.cm.free_slots == 6
