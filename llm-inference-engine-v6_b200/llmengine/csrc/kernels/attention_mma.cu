@@ -32,7 +32,6 @@ struct AttnParams {
   bf16* out; long long ld_out;
   // split mode (decode): partial outputs [split][token][head][HD] and (max, sum) [split][token][head][2]
   float* part_o; float* part_ml; int split_keys, n_splits; long long part_stride_tokens;
-  int* done_count;  // decoding form: one zeroed counter per (request, key/value head); left at zero again
 };
 
 template <int HD, bool SPLIT>
@@ -242,298 +241,6 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Attn
   }
 }
 
-// Decoding form: every request brings ONE token. A CTA owns (request, key/value head, split of the
-// key range); its 16 rows hold the `group` query heads of that key/value head. The four warps take
-// the split's 32-key tiles in turn (warp w: tiles w, w+4, ...); every warp has its own ring of two
-// tile buffers, so it computes on one tile while the next is on its way, and the first two tiles of
-// every warp are requested before the wait on the previous kernel (keys written by earlier steps
-// do not depend on it). The warps' partial (max, sum, output) are merged through shared memory in
-// warp order. Result: a normalised partial per split with its (max, sum), merged by the CTA that
-// finishes last for its (request, key/value head); or the final output when there is one split.
-template <int HD>
-__global__ void __launch_bounds__(THREADS) paged_attention_decode_kernel(const AttnParams p) {
-  constexpr int LD = HD + 8;
-  constexpr int KSTEPS = HD / 16, DTILES = HD / 8;
-  constexpr int ROWS = 16, TK = 32;  // query rows per CTA, keys per tile
-  extern __shared__ __align__(16) uint8_t smem_raw[];
-  bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [ROWS][LD]
-  bf16* kv_s = q_s + ROWS * LD;                    // [4 warps][2 stages][2 (k, v)][TK][LD]
-  int* page_s = reinterpret_cast<int*>(kv_s + 16 * TK * LD);  // the split's slice of the block table
-  dep_launch();
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
-  const int g = p.nq / p.nkv;
-  // The batch arrays came with the step's host-to-device copy, and every key before the token's
-  // own position was written by an earlier step: both may be read before the dependency wait.
-  // Only q and the key/value at `pos` come from the kernels just before this one.
-  const int pos = p.seq_start[seq];  // the token's position = number of keys before it
-  const int tok = p.seq_qoff[seq];
-  int lo = (p.window > 0) ? max(0, pos - p.window + 1) : 0;
-  int hi = pos;
-  lo = max(lo, split * p.split_keys);
-  hi = min(hi, (split + 1) * p.split_keys - 1);
-  const int* table = p.block_table + (size_t)seq * p.max_blocks;
-  const size_t head_stride = (size_t)p.page_size * HD;
-  bf16* ring = kv_s + (size_t)warp * 4 * TK * LD;
-  const bool any = hi >= lo;
-  const int kt_first = lo / TK, kt_last = hi / TK;
-  const int n_my = (any && kt_first + warp <= kt_last) ? (kt_last - (kt_first + warp)) / 4 + 1 : 0;  // this warp's tiles
-  // The pages of the split, read once by the whole CTA: a copy that looked its page up in global
-  // memory would wait for that read before it could even be issued, row after row.
-  const int page_lo = lo / p.page_size;
-  if (any) {
-    const int n_pages = hi / p.page_size - page_lo + 1;
-    for (int i = tid; i < n_pages; i += THREADS) page_s[i] = table[page_lo + i];
-  }
-  __syncthreads();
-
-  auto fetch_tile = [&](int j, int newest_excluded) {
-    // tile j of this warp -> stage j % 2; rows of keys in [lo, hi]; the row of key
-    // `newest_excluded` (if >= 0) is left for later
-    const int kt = kt_first + warp + 4 * j;
-    bf16* kb = ring + (size_t)(j & 1) * 2 * TK * LD;
-    bf16* vb = kb + TK * LD;
-    for (int c = lane; c < TK * (HD / 8); c += 32) {
-      const int r = c / (HD / 8), ch = c % (HD / 8);
-      const int key = kt * TK + r;
-      if (key == newest_excluded) continue;
-      const bool valid = key >= lo && key <= hi;
-      size_t off = 0;
-      if (valid) {
-        const int page = page_s[key / p.page_size - page_lo];
-        off = ((size_t)page * p.nkv + kvh) * head_stride + (size_t)(key % p.page_size) * HD + ch * 8;
-      }
-      cp_async16(kb + r * LD + ch * 8, p.kcache + off, valid);
-      cp_async16(vb + r * LD + ch * 8, p.vcache + off, valid);
-    }
-  };
-  if (n_my > 0) fetch_tile(0, pos);
-  cp_async_commit();
-  if (n_my > 1) fetch_tile(1, pos);
-  cp_async_commit();
-  dep_wait();
-  if (any && pos >= lo && pos <= hi) {  // the newest key, written just before: only if its tile is already under way
-    const int kt_pos = pos / TK;
-    const int j = (kt_pos - kt_first - warp) / 4;
-    if (kt_pos >= kt_first + warp && (kt_pos - kt_first - warp) % 4 == 0 && j < 2) {
-      bf16* kb = ring + (size_t)(j & 1) * 2 * TK * LD;
-      bf16* vb = kb + TK * LD;
-      const int r = pos - kt_pos * TK;
-      const int page = page_s[pos / p.page_size - page_lo];
-      const size_t off = ((size_t)page * p.nkv + kvh) * head_stride + (size_t)(pos % p.page_size) * HD;
-      for (int c = lane; c < 2 * (HD / 8); c += 32) {
-        const int ch = c % (HD / 8);
-        if (c < HD / 8) cp_async16(kb + r * LD + ch * 8, p.kcache + off + ch * 8, true);
-        else cp_async16(vb + r * LD + ch * 8, p.vcache + off + ch * 8, true);
-      }
-    }
-  }
-  for (int c = tid; c < ROWS * (HD / 8); c += THREADS) {  // q rows (zeros beyond the group), in flight with the keys
-    const int r = c / (HD / 8), ch = c % (HD / 8);
-    cp_async16(q_s + r * LD + ch * 8, p.q + (size_t)tok * p.ld_q + (size_t)(kvh * g + min(r, g - 1)) * HD + ch * 8, r < g);
-  }
-  cp_async_commit();
-  cp_async_wait<0>();
-  __syncthreads();
-  uint32_t qa[KSTEPS][4];
-#pragma unroll
-  for (int ks = 0; ks < KSTEPS; ++ks) ldmatrix_x4(qa[ks], q_s + (lane % 16) * LD + ks * 16 + (lane / 16) * 8);
-  const int row_a = lane / 4, row_b = row_a + 8;
-  const bool va_row = row_a < g, vb_row = row_b < g;
-
-  float o_acc[DTILES][4];
-#pragma unroll
-  for (int d = 0; d < DTILES; ++d) o_acc[d][0] = o_acc[d][1] = o_acc[d][2] = o_acc[d][3] = 0.f;
-  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
-  const float sl2 = p.scale * 1.4426950408889634f;
-
-  for (int j = 0; j < n_my; ++j) {
-    if (j > 0) {
-      cp_async_wait<1>();  // tile j has landed; tile j + 1 may still be on its way
-      __syncwarp();
-    }
-    const int kt = kt_first + warp + 4 * j;
-    const bf16* kb = ring + (size_t)(j & 1) * 2 * TK * LD;
-    const bf16* vb = kb + TK * LD;
-
-    float s[TK / 8][4];
-#pragma unroll
-    for (int i = 0; i < TK / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < KSTEPS; ++ks) {
-#pragma unroll
-      for (int j2 = 0; j2 < TK / 16; ++j2) {
-        uint32_t b[4];
-        ldmatrix_x4(b, kb + (j2 * 16 + (lane % 8) + (lane / 16) * 8) * LD + ks * 16 + ((lane / 8) % 2) * 8);
-        mma_bf16(s[2 * j2], qa[ks], b[0], b[1]);
-        mma_bf16(s[2 * j2 + 1], qa[ks], b[2], b[3]);
-      }
-    }
-    const int key0 = kt * TK + 2 * (lane % 4);
-    float mx_a = -INFINITY, mx_b = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < TK / 8; ++i) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int key = key0 + i * 8 + e;
-        const bool in = key >= lo && key <= hi;
-        s[i][e] = (in && va_row) ? s[i][e] * sl2 : -INFINITY;
-        s[i][2 + e] = (in && vb_row) ? s[i][2 + e] * sl2 : -INFINITY;
-        mx_a = fmaxf(mx_a, s[i][e]);
-        mx_b = fmaxf(mx_b, s[i][2 + e]);
-      }
-    }
-    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
-    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
-    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
-    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-    const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
-    const float base_a = (mn_a == -INFINITY) ? 0.f : mn_a, base_b = (mn_b == -INFINITY) ? 0.f : mn_b;
-    const float al_a = exp2f(m_a - base_a), al_b = exp2f(m_b - base_b);
-    float sum_a = 0.f, sum_b = 0.f;
-#pragma unroll
-    for (int i = 0; i < TK / 8; ++i) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        s[i][e] = exp2f(s[i][e] - base_a);
-        s[i][2 + e] = exp2f(s[i][2 + e] - base_b);
-        sum_a += s[i][e];
-        sum_b += s[i][2 + e];
-      }
-    }
-    sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
-    sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
-    sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
-    sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
-    l_a = l_a * al_a + sum_a;
-    l_b = l_b * al_b + sum_b;
-    m_a = mn_a;
-    m_b = mn_b;
-#pragma unroll
-    for (int d = 0; d < DTILES; ++d) {
-      o_acc[d][0] *= al_a; o_acc[d][1] *= al_a;
-      o_acc[d][2] *= al_b; o_acc[d][3] *= al_b;
-    }
-#pragma unroll
-    for (int kk = 0; kk < TK / 16; ++kk) {
-      uint32_t pa[4];
-      pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-      pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-      pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-      pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-#pragma unroll
-      for (int d2 = 0; d2 < DTILES / 2; ++d2) {
-        uint32_t b[4];
-        ldmatrix_x4_trans(b, vb + (kk * 16 + (lane % 8) + ((lane / 8) % 2) * 8) * LD + d2 * 16 + (lane / 16) * 8);
-        mma_bf16(o_acc[2 * d2], pa, b[0], b[1]);
-        mma_bf16(o_acc[2 * d2 + 1], pa, b[2], b[3]);
-      }
-    }
-    __syncwarp();  // the warp has finished reading this stage
-    if (j + 2 < n_my) fetch_tile(j + 2, -1);
-    cp_async_commit();
-  }
-  cp_async_wait<0>();
-  // ---- merge the four warps (in warp order) through shared memory: [warp][row][HD + 2] floats
-  __syncthreads();  // all tiles consumed: the key/value buffers can be reused
-  float* mg = reinterpret_cast<float*>(kv_s);
-  constexpr int MLD = HD + 2;
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int row = half ? row_b : row_a;
-    float* dst = mg + ((size_t)warp * ROWS + row) * MLD;
-#pragma unroll
-    for (int d = 0; d < DTILES; ++d) {
-      dst[d * 8 + 2 * (lane % 4)] = o_acc[d][2 * half];
-      dst[d * 8 + 2 * (lane % 4) + 1] = o_acc[d][2 * half + 1];
-    }
-    if ((lane % 4) == 0) {
-      dst[HD] = half ? m_b : m_a;
-      dst[HD + 1] = half ? l_b : l_a;
-    }
-  }
-  __syncthreads();
-  for (int e = tid; e < g * HD; e += THREADS) {
-    const int row = e / HD, d = e - row * HD;
-    float mx = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) mx = fmaxf(mx, mg[((size_t)w * ROWS + row) * MLD + HD]);
-    float acc = 0.f, den = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float* src = mg + ((size_t)w * ROWS + row) * MLD;
-      const float m = src[HD];
-      if (m == -INFINITY) continue;
-      const float sc = exp2f(m - mx);
-      den += src[HD + 1] * sc;
-      acc = fmaf(sc, src[d], acc);  // src[d] is the warp's unnormalised sum of p * v
-    }
-    const float inv = den > 0.f ? 1.f / den : 0.f;
-    const int head = kvh * g + row;
-    if (p.n_splits == 1) {
-      p.out[(size_t)tok * p.ld_out + (size_t)head * HD + d] = __float2bfloat16_rn(acc * inv);
-    } else {
-      const size_t slot = ((size_t)split * p.part_stride_tokens + tok) * p.nq + head;
-      p.part_o[slot * HD + d] = acc * inv;
-      if (d == 0) {
-        p.part_ml[slot * 2] = mx;
-        p.part_ml[slot * 2 + 1] = den;
-      }
-    }
-  }
-  if (p.n_splits == 1) return;
-  // ---- the CTA that finishes last for this (request, key/value head) merges the splits, in index
-  // order whichever CTA that is
-  __shared__ int is_last;
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const int old = atomicAdd(&p.done_count[seq * p.nkv + kvh], 1);
-    is_last = (old == p.n_splits - 1);
-    if (is_last) p.done_count[seq * p.nkv + kvh] = 0;  // ready for the next launch
-  }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  const size_t split_stride = (size_t)p.part_stride_tokens * p.nq;
-  // (max, sum) of every (row, split) -> shared memory, all loads in flight at once
-  float* m_s = mg;                      // [g][n_splits]
-  float* l_s = mg + ROWS * p.n_splits;  // [g][n_splits]
-  for (int idx = tid; idx < g * p.n_splits; idx += THREADS) {
-    const int row = idx / p.n_splits, sp = idx - row * p.n_splits;
-    const size_t slot = (size_t)tok * p.nq + kvh * g + row + sp * split_stride;
-    m_s[row * p.n_splits + sp] = __ldcg(&p.part_ml[slot * 2]);
-    l_s[row * p.n_splits + sp] = __ldcg(&p.part_ml[slot * 2 + 1]);
-  }
-  __syncthreads();
-  for (int e = tid; e < g * HD; e += THREADS) {
-    const int row = e / HD, d = e - row * HD;
-    const size_t slot0 = (size_t)tok * p.nq + kvh * g + row;
-    float mx = -INFINITY;
-    for (int sp = 0; sp < p.n_splits; ++sp) mx = fmaxf(mx, m_s[row * p.n_splits + sp]);
-    float acc = 0.f, den = 0.f;
-    for (int s0 = 0; s0 < p.n_splits; s0 += 8) {  // eight splits' loads in flight; added in index order
-      float v[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-        v[u] = (s0 + u < p.n_splits) ? __ldcg(&p.part_o[(slot0 + (s0 + u) * split_stride) * HD + d]) : 0.f;
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        if (s0 + u < p.n_splits) {
-          const float m = m_s[row * p.n_splits + s0 + u];
-          if (m != -INFINITY) {
-            const float w = l_s[row * p.n_splits + s0 + u] * exp2f(m - mx);
-            den += w;
-            acc = fmaf(w, v[u], acc);
-          }
-        }
-      }
-    }
-    const float inv = den > 0.f ? 1.f / den : 0.f;
-    p.out[(size_t)tok * p.ld_out + (size_t)(kvh * g + row) * HD + d] = __float2bfloat16_rn(acc * inv);
-  }
-}
-
 // Merges the splits of every (token, head) in index order: out = sum_s w_s o_s / sum_s w_s,
 // w_s = l_s * 2^(m_s - max m).
 template <int HD>
@@ -591,35 +298,25 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
 }
 
 template <int HD>
-int launch(const AttnParams& p, int n_seqs, int max_new_tokens, int n_tokens, bool split, bool decode, cudaStream_t stream) {
+int launch(const AttnParams& p, int n_seqs, int max_new_tokens, int n_tokens, bool split, cudaStream_t stream) {
   constexpr int LD = HD + 8;
   const int g = p.nq / p.nkv;
   auto set_attr = [&](auto kernel, size_t smem) {
     if (smem > 48 * 1024) return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
     return true;
   };
-  if (decode) {  // one token per request, group <= 16
-    const int keys_per_cta = p.n_splits > 1 ? p.split_keys : p.max_blocks * p.page_size;
-    const size_t smem = (size_t)(16 + 8 * N_TILE) * LD * sizeof(bf16) + (size_t)(keys_per_cta / p.page_size + 2) * sizeof(int);
-    if (smem > 200 * 1024) return 2;  // an absurdly long split of tiny pages: the caller must split more
-    if (!set_attr(paged_attention_decode_kernel<HD>, smem)) return 1;
-    launch_kernel(paged_attention_decode_kernel<HD>, dim3(n_seqs, p.nkv, p.n_splits), THREADS, smem, stream, p);
-  } else {
-    const size_t smem = (size_t)(M_TILE + 4 * N_TILE) * LD * sizeof(bf16);
-    const int tq_cap = M_TILE / g;
-    dim3 grid((max_new_tokens + tq_cap - 1) / tq_cap, n_seqs, p.nkv * (split ? p.n_splits : 1));
-    if (split) {
-      if (!set_attr(paged_attention_mma_kernel<HD, true>, smem)) return 1;
-      launch_kernel(paged_attention_mma_kernel<HD, true>, grid, THREADS, smem, stream, p);
-    } else {
-      if (!set_attr(paged_attention_mma_kernel<HD, false>, smem)) return 1;
-      launch_kernel(paged_attention_mma_kernel<HD, false>, grid, THREADS, smem, stream, p);
-    }
-  }
-  if (split && !decode) {
+  const size_t smem = (size_t)(M_TILE + 4 * N_TILE) * LD * sizeof(bf16);
+  const int tq_cap = M_TILE / g;
+  dim3 grid((max_new_tokens + tq_cap - 1) / tq_cap, n_seqs, p.nkv * (split ? p.n_splits : 1));
+  if (split) {
+    if (!set_attr(paged_attention_mma_kernel<HD, true>, smem)) return 1;
+    launch_kernel(paged_attention_mma_kernel<HD, true>, grid, THREADS, smem, stream, p);
     const int items = n_tokens * p.nq;
     launch_kernel(attention_combine_kernel<HD>, (items + 3) / 4, 128, 0, stream, (const float*)p.part_o, (const float*)p.part_ml,
                   p.n_splits, p.part_stride_tokens, p.nq, p.out, p.ld_out, n_tokens);
+  } else {
+    if (!set_attr(paged_attention_mma_kernel<HD, false>, smem)) return 1;
+    launch_kernel(paged_attention_mma_kernel<HD, false>, grid, THREADS, smem, stream, p);
   }
   return 0;
 }
@@ -640,15 +337,14 @@ extern "C" long long llm_attention_mma_scratch_floats(int n_tokens, int nq, int 
 
 // q: rows of [nq*hd] bf16 (ld_q elements apart); caches [pages, nkv, page_size, hd] bf16;
 // seq_* and block_table as in the step's batch; out [n_tokens, nq*hd] bf16.
-// n_splits > 1: keys are cut every split_keys (a multiple of 64) positions; scratch holds
-// llm_attention_mma_scratch_floats floats. max_new_tokens: longest portion of the batch.
-// done_count: n_seqs * nkv ints that are zero before the first call (the kernel leaves them zero);
-// with it, a step of single tokens merges its splits inside the attention kernel.
+// n_splits > 1: keys are cut every split_keys (a multiple of 64) positions; every split writes a
+// partial into scratch (llm_attention_mma_scratch_floats floats) and a second kernel merges them.
+// max_new_tokens: longest portion of the batch.
 extern "C" int llm_paged_attention_mma(const void* q, long long ld_q, const void* kcache, const void* vcache, const int* seq_start,
                                        const int* seq_ntok, const int* seq_qoff, const int* block_table, int max_blocks, void* out,
                                        long long ld_out, int n_seqs, int n_tokens, int max_new_tokens, int nq, int nkv, int hd,
                                        int page_size, float scale, int window, int n_splits, int split_keys, float* scratch,
-                                       int* done_count, cudaStream_t stream) {
+                                       cudaStream_t stream) {
   if (n_tokens == 0 || n_seqs == 0) return LLM_OK;
   LLM_REQUIRE(llm_attention_mma_supported(nq, nkv, hd, ld_q, ld_out), "attention_mma: geometry not supported (nq=%d nkv=%d hd=%d)", nq, nkv, hd);
   LLM_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && max_new_tokens > 0, "attention_mma: bad sizes");
@@ -664,18 +360,12 @@ extern "C" int llm_paged_attention_mma(const void* q, long long ld_q, const void
   p.out = (bf16*)out; p.ld_out = ld_out;
   p.n_splits = n_splits; p.split_keys = split_keys; p.part_stride_tokens = n_tokens;
   p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)n_splits * n_tokens * nq * hd : nullptr;
-  p.done_count = done_count;
   const bool split = n_splits > 1;
-  // the decoding form: one token per request (the caller says so with max_new_tokens == 1 and
-  // n_tokens == n_seqs) and a group that fits 16 rows
-  const bool decode = max_new_tokens == 1 && n_tokens == n_seqs && nq / nkv <= 16 && n_splits <= 65535 && nkv <= 65535 &&
-                      (n_splits == 1 || (done_count != nullptr && n_splits <= 128));
   int rc = 0;
-  if (hd == 16) rc = launch<16>(p, n_seqs, max_new_tokens, n_tokens, split, decode, stream);
-  else if (hd == 32) rc = launch<32>(p, n_seqs, max_new_tokens, n_tokens, split, decode, stream);
-  else if (hd == 64) rc = launch<64>(p, n_seqs, max_new_tokens, n_tokens, split, decode, stream);
-  else rc = launch<128>(p, n_seqs, max_new_tokens, n_tokens, split, decode, stream);
-  LLM_REQUIRE(rc != 2, "attention_mma: %d keys per split with pages of %d do not fit the block-table copy in shared memory", n_splits > 1 ? split_keys : max_blocks * page_size, page_size);
+  if (hd == 16) rc = launch<16>(p, n_seqs, max_new_tokens, n_tokens, split, stream);
+  else if (hd == 32) rc = launch<32>(p, n_seqs, max_new_tokens, n_tokens, split, stream);
+  else if (hd == 64) rc = launch<64>(p, n_seqs, max_new_tokens, n_tokens, split, stream);
+  else rc = launch<128>(p, n_seqs, max_new_tokens, n_tokens, split, stream);
   LLM_REQUIRE(rc == 0, "attention_mma: cannot raise the shared memory limit");
   LLM_CHECK_LAUNCH("paged_attention_mma");
   return LLM_OK;

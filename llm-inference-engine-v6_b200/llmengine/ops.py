@@ -425,7 +425,9 @@ class CudaOps:
                     _ptr(batch.seq_qoff), _ptr(block_table), c_int(block_table.shape[1]), _ptr(out), c_longlong(out.stride(0)),
                     c_int(batch.n_seqs), c_int(n_tokens), c_int(batch.max_new_tokens), c_int(nq), c_int(nkv), c_int(hd),
                     c_int(page), c_float(scale), c_int(window), c_int(n_splits), c_int(split_keys),
-                    _ptr(scratch), _ptr(counters), _stream()), lib)
+                    _ptr(scratch), _stream()), lib)
+                if n_splits > 1:
+                    self.launches += 1  # the kernel that merges the splits
                 return out
         lib = self.lib()
         self._check(lib.llm_paged_attention_simt(_ptr(q), c_longlong(q.stride(0)), _ptr(kcache), _ptr(vcache),

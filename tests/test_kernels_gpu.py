@@ -453,8 +453,8 @@ def test_decode_attention_many_requests(ops, hd, n_req):
 
 
 def test_decode_attention_kernels_agree(ops):
-    """The TMA decoding kernel against the cp.async one on the same inputs (both bf16 mma.sync with
-    the same tile order): equal up to the order of float32 sums."""
+    """The TMA decoding kernel against the general mma.sync kernel (cp.async, tiles of 64 keys, a
+    second kernel merging the splits) on the same inputs: equal up to the order of float32 sums."""
     nq, nkv, hd, page = 32, 8, 64, 16
     seq_lens = [2048, 100, 777, 1500]
     kc, vc, table, dense = _paged_setup(torch.bfloat16, nkv, hd, page, seq_lens, sum((L + page - 1) // page for L in seq_lens) + 3, seed=6)
