@@ -756,11 +756,9 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, i
 
 }  // namespace
 
-// Tuning knobs of the token-tile form (0 = built-in choice): width of the output tile and ring depth.
-static int g_force_bn = 0, g_force_stages = 0, g_persistent = 1, g_pair = 0;
+static int g_persistent = 1, g_pair = 0;
 // 1: CTA pairs (cta_group::2) for products of more than 128 tokens and at least 256 outputs.
 extern "C" void llm_gemm_tc_pair(int on) { g_pair = on; }
-extern "C" void llm_gemm_tc_tune(int bn, int stages) { g_force_bn = bn; g_force_stages = stages; }
 // 0: never the persistent form (for comparisons); 1: where an SM gets at least two tiles.
 extern "C" void llm_gemm_tc_persistent(int on) { g_persistent = on; }
 
@@ -794,9 +792,7 @@ extern "C" int llm_gemm_tc(const void* a, const void* w, void* out, int M, int N
   CUtensorMap ma, mb;
   int rc = LLM_OK;
   if (!swap) {
-    int bn = N >= 256 ? 256 : (N > 64 ? 128 : (N > 32 ? 64 : (N > 16 ? 32 : 16)));
-    if (g_force_bn) bn = g_force_bn;
-    if (g_force_stages) stages = g_force_stages;
+    const int bn = N >= 256 ? 256 : (N > 64 ? 128 : (N > 32 ? 64 : (N > 16 ? 32 : 16)));
     LLM_REQUIRE(tensor_map_for(a, M, K, lda, BM, &ma) && tensor_map_for(w, N, K, ldw, bn, &mb), "gemm_tc: cuTensorMapEncodeTiled failed");
 #define LLM_TC_CASE(BN_)                                                                                                   \
   rc = (out_dtype == LLM_F32) ? launch_tc<BN_, false, float>(ma, mb, out, M, N, K, 1, ldo, 0, std::min(stages, BN_ == 256 ? 4 : 6), stream) \

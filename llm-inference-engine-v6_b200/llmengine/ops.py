@@ -79,6 +79,13 @@ class CudaOps:
         is 0 to 25 % slower than the one-CTA persistent kernel at the sizes of this model."""
         self.lib("tensorcore").llm_gemm_tc_pair(c_int(1 if on else 0))
 
+    def merge_splits_in_cluster(self, on: bool) -> None:
+        """Decoding attention split over the keys: the CTAs of one (request, kv head) form a thread-block
+        cluster and send their partial results to its first CTA through shared memory (on, the
+        default), or write them to global memory where the last CTA to arrive adds them (off; more
+        than eight splits always end that way, cluster by cluster)."""
+        self.lib("tensorcore").llm_attention_decode_cluster_merge(c_int(1 if on else 0))
+
     def _check(self, rc: int, lib) -> None:
         self.launches += 1
         if rc != 0:

@@ -351,15 +351,19 @@ def test_paged_attention_tcgen05(ops, nq, nkv, window, hd, page):
         assert not torch.isnan(out.float()).any()
 
 
+@pytest.mark.parametrize("cluster_merge", [True, False])
 @pytest.mark.parametrize("target_ctas", [1, 592, 100000])  # no split, the usual splits, a split every 64 keys
 @pytest.mark.parametrize("nq,nkv,hd,page,window", [(32, 8, 64, 16, 0), (8, 2, 64, 8, 0), (4, 4, 64, 32, 0), (16, 1, 64, 64, 0),
                                                    (8, 2, 64, 16, 150), (8, 4, 128, 16, 0), (2, 2, 128, 32, 70), (6, 2, 128, 8, 0)])
-def test_paged_attention_decode_by_tma(ops, monkeypatch, nq, nkv, hd, page, window, target_ctas):
+def test_paged_attention_decode_by_tma(ops, monkeypatch, nq, nkv, hd, page, window, target_ctas, cluster_merge):
     """The decoding kernel that fetches keys and values by TMA (head sizes 64 and 128): contexts that
     end at a tile's, a page's and a split's edge, a window whose pages behind it were given back
     (their table entries are -1), requests of very different lengths in one batch, and every
-    split policy; the same call twice, since the split counters must be left at zero."""
+    split policy, merged inside a cluster and through global memory; the same call twice, since
+    the split counters must be left at zero."""
     dt = torch.bfloat16
+    if not cluster_merge and target_ctas == 1:
+        pytest.skip("nothing to merge without splits")
     monkeypatch.setattr(type(ops), "ATTENTION_TARGET_CTAS", target_ctas)
     if target_ctas > 1000:
         monkeypatch.setattr(type(ops), "ATTENTION_MIN_SPLIT_KEYS", 64)
@@ -374,13 +378,17 @@ def test_paged_attention_decode_by_tma(ops, monkeypatch, nq, nkv, hd, page, wind
     scale = 1.0 / math.sqrt(hd)
     b = Batch([(L - 1, 1) for L in seq_lens])
     q = rnd(b.n_tokens, nq * hd, dtype=dt, seed=24)
-    for _ in range(2):
-        out = torch.full((b.n_tokens, nq * hd), float("nan"), dtype=dt, device=DEV)
-        ops.paged_attention(q, kc, vc, b, table, out, nq, nkv, hd, scale, window)
-        assert ops.tensor_core_error() == 0
-        for i, (s_, p_) in enumerate(b.tokens):
-            ref = _attention_ref(q[i].cpu().view(nq, hd), dense[s_][0], dense[s_][1], p_, nq, nkv, hd, scale, window)
-            torch.testing.assert_close(out[i].float().cpu(), ref, **tol(dt, 2))
+    ops.merge_splits_in_cluster(cluster_merge)
+    try:
+        for _ in range(2):
+            out = torch.full((b.n_tokens, nq * hd), float("nan"), dtype=dt, device=DEV)
+            ops.paged_attention(q, kc, vc, b, table, out, nq, nkv, hd, scale, window)
+            assert ops.tensor_core_error() == 0
+            for i, (s_, p_) in enumerate(b.tokens):
+                ref = _attention_ref(q[i].cpu().view(nq, hd), dense[s_][0], dense[s_][1], p_, nq, nkv, hd, scale, window)
+                torch.testing.assert_close(out[i].float().cpu(), ref, **tol(dt, 2))
+    finally:
+        ops.merge_splits_in_cluster(True)
 
 
 @pytest.mark.parametrize("nq,nkv,hd,page,window,rotate", [(32, 8, 64, 16, 0, True), (8, 2, 64, 8, 100, True), (16, 1, 64, 32, 0, False),
