@@ -35,6 +35,45 @@ int* llm_tc_error_word() {
 
 namespace {
 
+// Walks the (tile, k-block) pairs of a persistent CTA: tiles first, first + step, ...; inside a tile
+// the k-blocks in order. The one thread that issues copies or products has a k-block's time for
+// each of its iterations, so the loop holds no division: the tile's rows are worked out once a tile.
+struct TileWalk {
+  int tile, kt, a_row0, b_row0;
+  int step, k_tiles, m_tiles, a_rows, b_rows, a_off, b_off;
+  __device__ __forceinline__ TileWalk(int first, int step_, int k_tiles_, int m_tiles_, int a_rows_, int b_rows_, int a_off_ = 0,
+                                      int b_off_ = 0)
+      : kt(0), step(step_), k_tiles(k_tiles_), m_tiles(m_tiles_), a_rows(a_rows_), b_rows(b_rows_), a_off(a_off_), b_off(b_off_) {
+    set_tile(first);
+  }
+  __device__ __forceinline__ void set_tile(int t) {
+    tile = t;
+    const int n = t / m_tiles;
+    a_row0 = (t - n * m_tiles) * a_rows + a_off;
+    b_row0 = n * b_rows + b_off;
+  }
+  __device__ __forceinline__ void next() {
+    if (++kt == k_tiles) {
+      kt = 0;
+      set_tile(tile + step);
+    }
+  }
+};
+
+// Stage and phase of a ring, stepped without a division.
+struct RingPos {
+  int s;
+  uint32_t ph;
+  int stages;
+  __device__ __forceinline__ RingPos(int stages_, int s_ = 0, uint32_t ph_ = 0) : s(s_), ph(ph_), stages(stages_) {}
+  __device__ __forceinline__ void next() {
+    if (++s == stages) {
+      s = 0;
+      ph ^= 1u;
+    }
+  }
+};
+
 template <typename TO>
 __device__ __forceinline__ void store_row16(TO* dst, const float* v, int valid, bool aligned);
 
@@ -128,10 +167,10 @@ __global__ void __launch_bounds__(128)
       tma_load_2d(smem + (size_t)it * STAGE_BYTES + ACT_OFF, act_map, (kt_begin + it) * BK, act_row0, &full[it]);
     int issued = early;
     bool ok = true;
-    for (int it = early; it < n_iter && ok; ++it) {
-      const int s = it % stages;
-      const uint32_t ph = (uint32_t)(it / stages) & 1u;
-      ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag, error_out, ERR_PRODUCER);
+    RingPos ring(stages, 0, 1u);  // iteration `stages` is the first to use a stage again
+    for (int it = early; it < n_iter && ok; ++it, ring.next()) {
+      const int s = ring.s;
+      ok = mbar_wait(&empty[s], ring.ph ^ 1u, abort_flag, error_out, ERR_PRODUCER);
       if (!ok) break;
       uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
       mbar_expect_tx(&full[s], STAGE_BYTES);
@@ -156,10 +195,10 @@ __global__ void __launch_bounds__(128)
     // ---------------------------------------------------------------- tensor-core issue
     constexpr uint32_t idesc = instr_desc(BN);
     bool ok = true;
-    for (int it = 0; it < n_iter && ok; ++it) {
-      const int s = it % stages;
-      const uint32_t ph = (uint32_t)(it / stages) & 1u;
-      ok = mbar_wait(&full[s], ph, abort_flag, error_out, ERR_MMA);
+    RingPos ring(stages);
+    for (int it = 0; it < n_iter && ok; ++it, ring.next()) {
+      const int s = ring.s;
+      ok = mbar_wait(&full[s], ring.ph, abort_flag, error_out, ERR_MMA);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
@@ -292,38 +331,25 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
       // The weight tiles of the first stages are asked for before the wait on the previous kernel.
       const long long n_iter = (long long)my_tiles * k_tiles;
       const int early = (int)(n_iter < stages ? n_iter : stages);
-      auto coords = [&](long long it, int& a_row0, int& b_row0, int& kt) {
-        const int t = (int)(it / k_tiles);
-        kt = (int)(it - (long long)t * k_tiles);
-        const int tile = blockIdx.x + t * gridDim.x;
-        a_row0 = (tile % m_tiles) * BM;
-        b_row0 = (tile / m_tiles) * BN;
-      };
-      for (int it = 0; it < early; ++it) {
-        int a_row0, b_row0, kt;
-        coords(it, a_row0, b_row0, kt);
+      TileWalk first(blockIdx.x, gridDim.x, k_tiles, m_tiles, BM, BN), walk = first;
+      for (int it = 0; it < early; ++it, first.next()) {
         mbar_expect_tx(&full[it], STAGE_BYTES);
-        tma_load_2d(smem + (size_t)it * STAGE_BYTES + A_BYTES, &map_b, kt * BK, b_row0, &full[it]);
+        tma_load_2d(smem + (size_t)it * STAGE_BYTES + A_BYTES, &map_b, first.kt * BK, first.b_row0, &full[it]);
       }
       dep_wait();
-      for (int it = 0; it < early; ++it) {
-        int a_row0, b_row0, kt;
-        coords(it, a_row0, b_row0, kt);
-        tma_load_2d(smem + (size_t)it * STAGE_BYTES, &map_a, kt * BK, a_row0, &full[it]);
-      }
+      for (int it = 0; it < early; ++it, walk.next())
+        tma_load_2d(smem + (size_t)it * STAGE_BYTES, &map_a, walk.kt * BK, walk.a_row0, &full[it]);
       long long issued = early;
       bool ok = true;
-      for (long long it = early; it < n_iter && ok; ++it) {
-        const int s = (int)(it % stages);
-        const uint32_t ph = (uint32_t)(it / stages) & 1u;
-        ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag, error_out, ERR_PRODUCER);
+      RingPos ring(stages, 0, 1u);  // iteration `stages` is the first to use a stage again
+      for (long long it = early; it < n_iter && ok; ++it, ring.next(), walk.next()) {
+        const int s = ring.s;
+        ok = mbar_wait(&empty[s], ring.ph ^ 1u, abort_flag, error_out, ERR_PRODUCER);
         if (!ok) break;
-        int a_row0, b_row0, kt;
-        coords(it, a_row0, b_row0, kt);
         uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
         mbar_expect_tx(&full[s], STAGE_BYTES);
-        tma_load_2d(sa, &map_a, kt * BK, a_row0, &full[s]);
-        tma_load_2d(sa + A_BYTES, &map_b, kt * BK, b_row0, &full[s]);
+        tma_load_2d(sa, &map_a, walk.kt * BK, walk.a_row0, &full[s]);
+        tma_load_2d(sa + A_BYTES, &map_b, walk.kt * BK, walk.b_row0, &full[s]);
         issued = it + 1;
       }
       if (!ok || *abort_flag) {
@@ -345,7 +371,7 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
       // ---------------------------------------------------------------- tensor-core issue
       constexpr uint32_t idesc = instr_desc(BN);
       bool ok = true;
-      long long it = 0;
+      RingPos ring(stages);
       for (int t = 0; t < my_tiles && ok; ++t) {
         const int b = t & 1;
         if (t >= 2) {  // the epilogue of the tile that used this accumulator two tiles ago
@@ -354,10 +380,9 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
         const uint32_t acc = tmem_base + (uint32_t)(b * ACC_STRIDE);
-        for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
-          const int s = (int)(it % stages);
-          const uint32_t ph = (uint32_t)(it / stages) & 1u;
-          ok = mbar_wait(&full[s], ph, abort_flag, error_out, ERR_MMA);
+        for (int kt = 0; kt < k_tiles && ok; ++kt, ring.next()) {
+          const int s = ring.s;
+          ok = mbar_wait(&full[s], ring.ph, abort_flag, error_out, ERR_MMA);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
@@ -528,40 +553,28 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
     if (lane == 0) {
       // ---------------------------------------------------------------- producer (both CTAs)
       const long long n_iter = (long long)my_tiles * k_tiles;
-      auto coords = [&](long long it, int& a_row0, int& b_row0, int& kt) {
-        const int t = (int)(it / k_tiles);
-        kt = (int)(it - (long long)t * k_tiles);
-        const int tile = pair + t * n_pairs;
-        a_row0 = (tile % mp_tiles) * 256 + (int)rank * BM;          // this CTA's 128 token rows
-        b_row0 = (tile / mp_tiles) * BN + (int)rank * (BN / 2);      // this CTA's 128 weight rows
-      };
+      // this CTA's 128 token rows and 128 weight rows of each tile of 256 x 256
+      TileWalk first(pair, n_pairs, k_tiles, mp_tiles, 256, BN, (int)rank * BM, (int)rank * (BN / 2)), walk = first;
       const int early = (int)(n_iter < stages ? n_iter : stages);
-      for (int it = 0; it < early; ++it) {  // weights first: they do not depend on the kernel before
-        int a_row0, b_row0, kt;
-        coords(it, a_row0, b_row0, kt);
+      for (int it = 0; it < early; ++it, first.next()) {  // weights first: they do not depend on the kernel before
         if (rank == 0) mbar_expect_tx(&full[it], 2 * STAGE_BYTES);
-        tma_load_2d_pair(smem + (size_t)it * STAGE_BYTES + A_BYTES, &map_b, kt * BK, b_row0, map_to_cta(smem_u32(&full[it]), 0));
+        tma_load_2d_pair(smem + (size_t)it * STAGE_BYTES + A_BYTES, &map_b, first.kt * BK, first.b_row0, map_to_cta(smem_u32(&full[it]), 0));
       }
       dep_wait();
-      for (int it = 0; it < early; ++it) {
-        int a_row0, b_row0, kt;
-        coords(it, a_row0, b_row0, kt);
-        tma_load_2d_pair(smem + (size_t)it * STAGE_BYTES, &map_a, kt * BK, a_row0, map_to_cta(smem_u32(&full[it]), 0));
-      }
+      for (int it = 0; it < early; ++it, walk.next())
+        tma_load_2d_pair(smem + (size_t)it * STAGE_BYTES, &map_a, walk.kt * BK, walk.a_row0, map_to_cta(smem_u32(&full[it]), 0));
       long long issued = early;
       bool ok = true;
-      for (long long it = early; it < n_iter && ok; ++it) {
-        const int s = (int)(it % stages);
-        const uint32_t ph = (uint32_t)(it / stages) & 1u;
-        ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag, error_out, ERR_PRODUCER);
+      RingPos ring(stages, 0, 1u);
+      for (long long it = early; it < n_iter && ok; ++it, ring.next(), walk.next()) {
+        const int s = ring.s;
+        ok = mbar_wait(&empty[s], ring.ph ^ 1u, abort_flag, error_out, ERR_PRODUCER);
         if (!ok) break;
-        int a_row0, b_row0, kt;
-        coords(it, a_row0, b_row0, kt);
         uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
         const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
         if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
-        tma_load_2d_pair(sa, &map_a, kt * BK, a_row0, bar);
-        tma_load_2d_pair(sa + A_BYTES, &map_b, kt * BK, b_row0, bar);
+        tma_load_2d_pair(sa, &map_a, walk.kt * BK, walk.a_row0, bar);
+        tma_load_2d_pair(sa + A_BYTES, &map_b, walk.kt * BK, walk.b_row0, bar);
         issued = it + 1;
       }
       if (rank == 0 && (!ok || *abort_flag)) {
@@ -583,7 +596,7 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
       // ---------------------------------------------------------------- tensor-core issue (leader)
       constexpr uint32_t idesc = instr_desc_pair(BN);
       bool ok = true;
-      long long it = 0;
+      RingPos ring(stages);
       for (int t = 0; t < my_tiles && ok; ++t) {
         const int b = t & 1;
         if (t >= 2) {
@@ -592,10 +605,9 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
         const uint32_t acc = tmem_base + (uint32_t)(b * BN);
-        for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
-          const int s = (int)(it % stages);
-          const uint32_t ph = (uint32_t)(it / stages) & 1u;
-          ok = mbar_wait(&full[s], ph, abort_flag, error_out, ERR_MMA);
+        for (int kt = 0; kt < k_tiles && ok; ++kt, ring.next()) {
+          const int s = ring.s;
+          ok = mbar_wait(&full[s], ring.ph, abort_flag, error_out, ERR_MMA);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
@@ -730,6 +742,23 @@ inline bool prefer_192(int M, int N) {
   return t192 > sms && cost192 < cost256;
 }
 
+// CTA pairs (tiles of 256 x 256 on two SMs) against one-CTA tiles. Measured on B200, a pair spends
+// about 0.92 of the time of two single CTAs on the same k-blocks (each SM loads a third less), but
+// starts and ends later (cluster launch, barriers across the pair), which short products of one
+// round do not earn back; and 256 x 256 tiles can leave more of the last round empty.
+// mode: 0 never, 1 wherever the shape allows, -1 by this estimate.
+inline bool prefer_pairs(int mode, int M, int N, int K) {
+  if (mode == 0 || M <= BM || N < 256) return false;
+  if (mode == 1) return true;
+  const int sms = sm_count(), k_tiles = (K + BK - 1) / BK, m_tiles = (M + BM - 1) / BM;
+  const int t_pair = ((M + 255) / 256) * ((N + 255) / 256), pairs = sms / 2 > 0 ? sms / 2 : 1;
+  const int rounds_pair = (t_pair + pairs - 1) / pairs;
+  const int t256 = m_tiles * ((N + 255) / 256), t192 = m_tiles * ((N + 191) / 192);
+  int cost_single = (t256 + sms - 1) / sms * 256;
+  if (prefer_192(M, N)) cost_single = (t192 + sms - 1) / sms * 192;
+  return rounds_pair * 256 * 0.92f < (float)cost_single && rounds_pair * k_tiles >= 64;
+}
+
 template <int BN, bool SWAP, typename TO, bool SWIGLU = false>
 int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, int splits, long long ldo,
               long long split_stride, int stages, cudaStream_t stream) {
@@ -756,9 +785,10 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, i
 
 }  // namespace
 
-static int g_persistent = 1, g_pair = 0;
-// 1: CTA pairs (cta_group::2) for products of more than 128 tokens and at least 256 outputs.
-extern "C" void llm_gemm_tc_pair(int on) { g_pair = on; }
+static int g_persistent = 1, g_pair = -1;
+// CTA pairs (cta_group::2) for products of more than 128 tokens and at least 256 outputs:
+// 1 always, 0 never, -1 where they are estimated to be faster (the default).
+extern "C" void llm_gemm_tc_pair(int mode) { g_pair = mode; }
 // 0: never the persistent form (for comparisons); 1: where an SM gets at least two tiles.
 extern "C" void llm_gemm_tc_persistent(int on) { g_persistent = on; }
 
@@ -797,7 +827,7 @@ extern "C" int llm_gemm_tc(const void* a, const void* w, void* out, int M, int N
 #define LLM_TC_CASE(BN_)                                                                                                   \
   rc = (out_dtype == LLM_F32) ? launch_tc<BN_, false, float>(ma, mb, out, M, N, K, 1, ldo, 0, std::min(stages, BN_ == 256 ? 4 : 6), stream) \
                               : launch_tc<BN_, false, bf16>(ma, mb, out, M, N, K, 1, ldo, 0, std::min(stages, BN_ == 256 ? 4 : 6), stream)
-    if (bn == 256 && g_pair && M > BM) {
+    if (bn == 256 && prefer_pairs(g_pair, M, N, K)) {
       LLM_REQUIRE(tensor_map_for(w, N, K, ldw, 128, &mb), "gemm_tc: cuTensorMapEncodeTiled failed");
       rc = (out_dtype == LLM_F32) ? launch_tc_pair<float, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream)
                                   : launch_tc_pair<bf16, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream);
@@ -843,7 +873,7 @@ extern "C" int llm_gemm_tc_swiglu(const void* a, const void* w, void* act, int M
   LLM_REQUIRE(error_word() != nullptr, "gemm_tc_swiglu: cannot allocate the error word");
   CUtensorMap ma, mb;
   LLM_REQUIRE(tensor_map_for(a, M, K, lda, BM, &ma) && tensor_map_for(w, 2 * FF, K, ldw, 256, &mb), "gemm_tc_swiglu: cuTensorMapEncodeTiled failed");
-  if (g_pair && M > BM) {
+  if (prefer_pairs(g_pair, M, 2 * FF, K)) {
     LLM_REQUIRE(tensor_map_for(w, 2 * FF, K, ldw, 128, &mb), "gemm_tc_swiglu: cuTensorMapEncodeTiled failed");
     const int rc2 = launch_tc_pair<bf16, true>(ma, mb, act, M, 2 * FF, K, ld_act, sm_count(), stream);
     if (rc2 != LLM_OK) return rc2;

@@ -51,6 +51,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait. Returns false if the phase did not complete in time or another role aborted.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* error_out, int code) {
+  if (mbar_try_wait(bar, parity)) return true;  // the usual case costs one instruction
   const long long t0 = clock64();
   for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;

@@ -60,6 +60,7 @@ def run_gemm(args) -> dict:
     a = torch.randn(M, K, device=dev).bfloat16()
     space = Workspace(dev)
     out_kind = getattr(args, "out", "partials")
+    ops.use_cta_pairs({"auto": None, "on": True, "off": False}[getattr(args, "pairs", "auto")])
     if out_kind == "swiglu":  # w as gate|up blocks of 128 rows; the output is silu(gate) * up, bfloat16 [M, N / 2]
         act = torch.empty(M, N // 2, device=dev, dtype=torch.bfloat16)
         sec = _time(lambda i: ops.gemm_swiglu(a, ws[i % copies], act, space), args.reps)
@@ -183,6 +184,8 @@ def main(argv=None) -> int:
     g = sub.add_parser("gemm")
     g.add_argument("--m", type=int, default=8); g.add_argument("--n", type=int, default=16384); g.add_argument("--k", type=int, default=2048)
     g.add_argument("--reps", type=int, default=20)
+    g.add_argument("--pairs", choices=["auto", "on", "off"], default="auto",
+                   help="products of more than 128 tokens on CTA pairs (tcgen05 cta_group::2): where estimated faster, always, never")
     g.add_argument("--out", choices=["partials", "bf16", "swiglu"], default="partials",
                    help="what the product writes: float32 partial sums, bfloat16, or silu(gate)*up in bfloat16")
     a = sub.add_parser("attention")

@@ -73,11 +73,12 @@ class CudaOps:
             self._libs[name] = lib
         return lib
 
-    def use_cta_pairs(self, on: bool) -> None:
+    def use_cta_pairs(self, on: Optional[bool]) -> None:
         """Products of more than 128 tokens on CTA pairs (tcgen05 cta_group::2: two SMs share one
-        256 x 256 tile and each loads half of the weight tile). Off by default: measured on B200 it
-        is 0 to 25 % slower than the one-CTA persistent kernel at the sizes of this model."""
-        self.lib("tensorcore").llm_gemm_tc_pair(c_int(1 if on else 0))
+        256 x 256 tile and each loads half of the weight tile): always, never, or (None, the
+        default) where the kernel library estimates them to be faster: long products and those of
+        many rounds of tiles, e.g. gate|up and down of a 2,048-token prompt, not q|k|v or o."""
+        self.lib("tensorcore").llm_gemm_tc_pair(c_int(-1 if on is None else (1 if on else 0)))
 
     def merge_splits_in_cluster(self, on: bool) -> None:
         """Decoding attention split over the keys: the CTAs of one (request, kv head) form a thread-block

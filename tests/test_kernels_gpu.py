@@ -143,9 +143,17 @@ def test_gemm_with_fused_swiglu(ops, M, FF, K):
     assert ops.tensor_core_error() == 0
 
 
+@pytest.fixture
+def one_cta_products(ops):
+    """No CTA pairs during the test: it is about the kernels that give a tile to one CTA."""
+    ops.use_cta_pairs(False)
+    yield
+    ops.use_cta_pairs(None)
+
+
 @pytest.mark.parametrize("M,N,K", [(300, 25617, 192), (129, 76000, 64), (1100, 8704, 256), (2048, 3072, 128), (1500, 5120, 64),
                                    (2048, 3000, 64)])  # the last three: tiles of 192 outputs shorten the last round
-def test_gemm_persistent_form(ops, M, N, K):
+def test_gemm_persistent_form(ops, one_cta_products, M, N, K):
     """Enough output tiles that every SM gets several: the persistent kernel (two accumulators in
     tensor memory, epilogue beside the next tile's products) against float64, tails in every
     dimension, and against the one-tile-per-CTA kernel bit for bit (same products in the same order)."""
@@ -169,7 +177,7 @@ def test_gemm_persistent_form(ops, M, N, K):
     assert ops.tensor_core_error() == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 25617, 192), (1100, 8704, 256), (129, 512, 2048)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 25617, 192), (1100, 8704, 256), (129, 512, 2048), (700, 1024, 4160)])
 def test_gemm_on_cta_pairs(ops, M, N, K):
     """The cta_group::2 kernel (two CTAs of a cluster on one 256 x 256 tile, one MMA stream, each CTA
     loading half of the weight tile): same products in the same order as the one-CTA kernels, so the
@@ -184,7 +192,7 @@ def test_gemm_on_cta_pairs(ops, M, N, K):
                 out = torch.full((M, N), float("nan"), dtype=out_dt, device=DEV)
                 ops.gemm(a, w, out)
             finally:
-                ops.use_cta_pairs(False)
+                ops.use_cta_pairs(None)
             outs[(out_dt, pairs)] = out
         assert torch.equal(outs[(out_dt, True)], outs[(out_dt, False)])
     rows = torch.tensor([0, 127, 128, M - 1]).to(DEV)
@@ -199,13 +207,13 @@ def test_gemm_on_cta_pairs(ops, M, N, K):
                 act = torch.full((M, FF), float("nan"), dtype=torch.bfloat16, device=DEV)
                 ops.gemm_swiglu(a, w, act, Workspace(torch.device(DEV)))
             finally:
-                ops.use_cta_pairs(False)
+                ops.use_cta_pairs(None)
             acts.append(act)
         assert torch.equal(acts[0], acts[1])
     assert ops.tensor_core_error() == 0
 
 
-def test_gemm_persistent_form_with_swiglu(ops):
+def test_gemm_persistent_form_with_swiglu(ops, one_cta_products):
     from llmengine.engine.context import Workspace
     M, FF, K = 300, 12800, 128
     a = rnd(M, K, dtype=torch.bfloat16, seed=72)
