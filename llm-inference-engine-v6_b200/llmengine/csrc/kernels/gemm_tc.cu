@@ -746,8 +746,9 @@ inline bool prefer_192(int M, int N) {
 // about 0.92 of the time of two single CTAs on the same k-blocks (each SM loads a third less), but
 // starts and ends later (cluster launch, barriers across the pair), which short products of one
 // round do not earn back; and 256 x 256 tiles can leave more of the last round empty.
-// mode: 0 never, 1 wherever the shape allows, -1 by this estimate.
-inline bool prefer_pairs(int mode, int M, int N, int K) {
+// mode: 0 never, 1 wherever the shape allows, -1 by this estimate. allow_192: the one-CTA kernels
+// may use tiles of 192 outputs (not with SwiGLU in the epilogue).
+inline bool prefer_pairs(int mode, int M, int N, int K, bool allow_192 = true) {
   if (mode == 0 || M <= BM || N < 256) return false;
   if (mode == 1) return true;
   const int sms = sm_count(), k_tiles = (K + BK - 1) / BK, m_tiles = (M + BM - 1) / BM;
@@ -755,7 +756,7 @@ inline bool prefer_pairs(int mode, int M, int N, int K) {
   const int rounds_pair = (t_pair + pairs - 1) / pairs;
   const int t256 = m_tiles * ((N + 255) / 256), t192 = m_tiles * ((N + 191) / 192);
   int cost_single = (t256 + sms - 1) / sms * 256;
-  if (prefer_192(M, N)) cost_single = (t192 + sms - 1) / sms * 192;
+  if (allow_192 && prefer_192(M, N)) cost_single = (t192 + sms - 1) / sms * 192;
   return rounds_pair * 256 * 0.92f < (float)cost_single && rounds_pair * k_tiles >= 64;
 }
 
@@ -792,6 +793,19 @@ extern "C" void llm_gemm_tc_pair(int mode) { g_pair = mode; }
 // 0: never the persistent form (for comparisons); 1: where an SM gets at least two tiles.
 extern "C" void llm_gemm_tc_persistent(int on) { g_persistent = on; }
 
+enum : int { FORM_ONE_TILE = 0, FORM_PERSISTENT_256 = 1, FORM_PERSISTENT_192 = 2, FORM_PAIRS = 3 };
+
+// Which kernel the token-tile form (tiles of 128 tokens) runs for these sizes: one output tile a
+// CTA, the persistent kernel with tiles of 256 or of 192 outputs, or CTA pairs. swiglu: the gate|up
+// product with the activation in the epilogue (N counts gate and up rows).
+extern "C" int llm_gemm_tc_form(int M, int N, int K, int swiglu) {
+  if (N < 256) return FORM_ONE_TILE;
+  if (prefer_pairs(g_pair, M, N, K, !swiglu)) return FORM_PAIRS;
+  if (!g_persistent) return FORM_ONE_TILE;
+  if (!swiglu && prefer_192(M, N)) return FORM_PERSISTENT_192;
+  return use_persistent(M, N) ? FORM_PERSISTENT_256 : FORM_ONE_TILE;
+}
+
 // Number of K splits llm_gemm_tc will really use for (K, wanted splits).
 extern "C" int llm_gemm_tc_splits(int K, int splits) {
   const int k_tiles = (K + BK - 1) / BK;
@@ -827,15 +841,16 @@ extern "C" int llm_gemm_tc(const void* a, const void* w, void* out, int M, int N
 #define LLM_TC_CASE(BN_)                                                                                                   \
   rc = (out_dtype == LLM_F32) ? launch_tc<BN_, false, float>(ma, mb, out, M, N, K, 1, ldo, 0, std::min(stages, BN_ == 256 ? 4 : 6), stream) \
                               : launch_tc<BN_, false, bf16>(ma, mb, out, M, N, K, 1, ldo, 0, std::min(stages, BN_ == 256 ? 4 : 6), stream)
-    if (bn == 256 && prefer_pairs(g_pair, M, N, K)) {
+    const int form = llm_gemm_tc_form(M, N, K, 0);
+    if (form == FORM_PAIRS) {
       LLM_REQUIRE(tensor_map_for(w, N, K, ldw, 128, &mb), "gemm_tc: cuTensorMapEncodeTiled failed");
       rc = (out_dtype == LLM_F32) ? launch_tc_pair<float, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream)
                                   : launch_tc_pair<bf16, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream);
-    } else if (bn == 256 && g_persistent && prefer_192(M, N)) {
+    } else if (form == FORM_PERSISTENT_192) {
       LLM_REQUIRE(tensor_map_for(w, N, K, ldw, 192, &mb), "gemm_tc: cuTensorMapEncodeTiled failed");
       rc = (out_dtype == LLM_F32) ? launch_tc_persistent<float, false, 192>(ma, mb, out, M, N, K, ldo, sm_count(), stream)
                                   : launch_tc_persistent<bf16, false, 192>(ma, mb, out, M, N, K, ldo, sm_count(), stream);
-    } else if (bn == 256 && g_persistent && use_persistent(M, N))
+    } else if (form == FORM_PERSISTENT_256)
       rc = (out_dtype == LLM_F32) ? launch_tc_persistent<float, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream)
                                   : launch_tc_persistent<bf16, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream);
     else if (bn == 256) LLM_TC_CASE(256);
@@ -873,14 +888,15 @@ extern "C" int llm_gemm_tc_swiglu(const void* a, const void* w, void* act, int M
   LLM_REQUIRE(error_word() != nullptr, "gemm_tc_swiglu: cannot allocate the error word");
   CUtensorMap ma, mb;
   LLM_REQUIRE(tensor_map_for(a, M, K, lda, BM, &ma) && tensor_map_for(w, 2 * FF, K, ldw, 256, &mb), "gemm_tc_swiglu: cuTensorMapEncodeTiled failed");
-  if (prefer_pairs(g_pair, M, 2 * FF, K)) {
+  const int form = llm_gemm_tc_form(M, 2 * FF, K, 1);
+  if (form == FORM_PAIRS) {
     LLM_REQUIRE(tensor_map_for(w, 2 * FF, K, ldw, 128, &mb), "gemm_tc_swiglu: cuTensorMapEncodeTiled failed");
     const int rc2 = launch_tc_pair<bf16, true>(ma, mb, act, M, 2 * FF, K, ld_act, sm_count(), stream);
     if (rc2 != LLM_OK) return rc2;
     LLM_CHECK_LAUNCH("gemm_tc_swiglu");
     return LLM_OK;
   }
-  const int rc = (g_persistent && use_persistent(M, 2 * FF))
+  const int rc = form == FORM_PERSISTENT_256
                      ? launch_tc_persistent<bf16, true>(ma, mb, act, M, 2 * FF, K, ld_act, sm_count(), stream)
                      : launch_tc<256, false, bf16, true>(ma, mb, act, M, 2 * FF, K, 1, ld_act, 0, 4, stream);
   if (rc != LLM_OK) return rc;

@@ -75,7 +75,8 @@ def run_gemm(args) -> dict:
         splits, out_bytes = parts.shape[0], parts.numel() * 4
     assert ops.tensor_core_error() == 0
     flops, nbytes = 2.0 * M * N * K, N * K * 2 + M * K * 2 + out_bytes
-    return {"kernel": "gemm_tc", "out": out_kind, "M": M, "N": N, "K": K, "k_splits": splits, "us": round(sec * 1e6, 2),
+    form = ops.gemm_form(M, N, K, out_kind == "swiglu") if M > ops.SWAP_MAX_TOKENS else "swapped, weights on the accumulator lanes"
+    return {"kernel": "gemm_tc", "form": form, "out": out_kind, "M": M, "N": N, "K": K, "k_splits": splits, "us": round(sec * 1e6, 2),
             "tflops": round(flops / sec / 1e12, 1), "gbs": round(nbytes / sec / 1e9, 1)}
 
 

@@ -80,6 +80,13 @@ class CudaOps:
         many rounds of tiles, e.g. gate|up and down of a 2,048-token prompt, not q|k|v or o."""
         self.lib("tensorcore").llm_gemm_tc_pair(c_int(-1 if on is None else (1 if on else 0)))
 
+    GEMM_FORMS = ("one tile a CTA", "persistent, tiles of 256", "persistent, tiles of 192", "CTA pairs")
+
+    def gemm_form(self, m: int, n: int, k: int, swiglu: bool = False) -> str:
+        """Which tcgen05 kernel a product of more than SWAP_MAX_TOKENS tokens with n outputs (gate and
+        up rows together when `swiglu`) runs on: one of GEMM_FORMS."""
+        return self.GEMM_FORMS[int(self.lib("tensorcore").llm_gemm_tc_form(c_int(m), c_int(n), c_int(k), c_int(1 if swiglu else 0)))]
+
     def merge_splits_in_cluster(self, on: bool) -> None:
         """Decoding attention split over the keys: the CTAs of one (request, kv head) form a thread-block
         cluster and send their partial results to its first CTA through shared memory (on, the
