@@ -159,6 +159,15 @@ def run_ours(args):
     def prompts(n, length):
         return torch.randint(0, g["vocab_size"], (n, length), generator=gen).tolist()
 
+    def check(phase):
+        """A kernel whose bounded wait gave up leaves a code and returns; every launch after it may do
+        the same, a second at a time. Better to stop at once and say where."""
+        code = eng.ops.tensor_core_error()
+        if code:
+            raise RuntimeError(f"a tensor-core kernel gave up a wait (code {code}) during: {phase}")
+        sys.stderr.write(f"[bench] {phase}: done at {time.time() - t0:.1f}s\n")
+        sys.stderr.flush()
+
     def decode_run(batch, k_steps, w_steps, e2e):
         """-> (seconds per step, kernel launches per step, h2d bytes, d2h bytes)."""
         sch = llmengine.ContinuousBatchScheduler(eng, None, max_concurrent=batch, max_prefill_tokens_per_step=PREFILL_TOKENS)
@@ -169,6 +178,7 @@ def run_ours(args):
                 break
             sch.step()
         assert sch.core.num_running == batch, "the contexts could not be filled"
+        check(f"prompts of batch {batch}")
         launches = 0
 
         def one_step():
@@ -189,6 +199,7 @@ def run_ours(args):
         for _ in range(w_steps):
             one_step()
         torch.cuda.synchronize()
+        check(f"warm-up steps of batch {batch}")
         eng.ops.launches = 0
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t_wall = time.perf_counter()
@@ -200,6 +211,7 @@ def run_ours(args):
         wall = time.perf_counter() - t_wall
         dev = start.elapsed_time(stop) / 1e3
         launches = eng.ops.launches / k_steps
+        check(f"timed steps of batch {batch}" + (" through the scheduler" if e2e else ""))
         if e2e and eng.cuda_graphs and eng.graphs is not None:
             h2d, d2h = eng.graphs.h2d_bytes, eng.graphs.d2h_bytes
         else:
@@ -227,6 +239,8 @@ def run_ours(args):
             eng.cm.release(rid)
             if i >= w_steps:
                 times.append(a.elapsed_time(b) / 1e3)
+            if i == 0:
+                check(f"first prompt step of {PREFILL_TOKENS} tokens")
         return statistics.median(times)
 
     clocks = ClockSampler()
