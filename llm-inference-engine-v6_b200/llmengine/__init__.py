@@ -9,6 +9,7 @@ Names follow the reference's Python package (python/llmengine/__init__.py:6-26).
 from .cache.host import host_module as _host_module
 from .config import ConfigError, LlamaConfig, register_architecture
 from .engine import BlockManager, CapacityError, ContinuousBatchScheduler, Engine
+from .ops import KernelError
 from .weights import WeightError, write_random_model
 
 ModelConfig = LlamaConfig
@@ -20,5 +21,5 @@ def __getattr__(name):
     raise AttributeError(name)
 
 
-__all__ = ["BlockManager", "CapacityError", "ConfigError", "ContinuousBatchScheduler", "Engine", "LlamaConfig",
+__all__ = ["BlockManager", "CapacityError", "ConfigError", "ContinuousBatchScheduler", "Engine", "KernelError", "LlamaConfig",
            "ModelConfig", "SequenceResult", "WeightError", "register_architecture", "write_random_model"]

@@ -138,17 +138,21 @@ PYBIND11_MODULE(_llmengine_host, m) {
       });
 
   py::class_<Scheduler>(m, "SchedulerCore")
-      .def(py::init<CacheManager&, int, int, std::set<int>, int, int, std::int64_t>(), py::arg("cache_manager"),
+      .def(py::init<CacheManager&, int, int, std::set<int>, int, int, std::int64_t, int>(), py::arg("cache_manager"),
            py::arg("vocab_size"), py::arg("max_positions"), py::arg("eos_token_ids"), py::arg("max_concurrent") = 64,
-           py::arg("max_prefill_tokens_per_step") = 256, py::arg("id_base") = 0, py::keep_alive<1, 2>())
+           py::arg("max_prefill_tokens_per_step") = 256, py::arg("id_base") = 0, py::arg("portion_multiple") = 1,
+           py::keep_alive<1, 2>())
       .def_property_readonly("last_admitted", &Scheduler::last_admitted)
       .def("enqueue", &Scheduler::enqueue, py::arg("prompt"), py::arg("max_new_tokens"), py::arg("temperature") = 0.f,
            py::arg("seed") = 0)
       .def("plan", [](Scheduler& s) { StepEntries e; e.v = s.plan(); return e; })
       .def("commit", &Scheduler::commit)
+      .def("fail_step", &Scheduler::fail_step, py::arg("reason") = "error")
+      .def_property_readonly("portion_multiple", &Scheduler::portion_multiple)
       .def("finalize", &Scheduler::finalize)
       .def_property_readonly("idle", &Scheduler::idle)
       .def_property_readonly("has_unfinished", &Scheduler::has_unfinished)
+      .def_property_readonly("plan_open", &Scheduler::plan_open)
       .def_property_readonly("results", &Scheduler::results)
       .def("clear_results", &Scheduler::clear_results)
       .def_property("budget", &Scheduler::budget, &Scheduler::set_budget)

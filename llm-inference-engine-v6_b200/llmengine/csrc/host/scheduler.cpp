@@ -6,17 +6,26 @@
 namespace llmhost {
 
 Scheduler::Scheduler(CacheManager& cm, int vocab_size, int max_positions, std::set<int> eos_token_ids,
-                     int max_concurrent, int max_prefill_tokens_per_step, std::int64_t id_base)
+                     int max_concurrent, int max_prefill_tokens_per_step, std::int64_t id_base, int portion_multiple)
     : cm_(cm), vocab_size_(vocab_size), max_positions_(max_positions), eos_(std::move(eos_token_ids)),
-      max_concurrent_(max_concurrent), budget_(max_prefill_tokens_per_step), id_base_(id_base) {
+      max_concurrent_(max_concurrent), budget_(max_prefill_tokens_per_step), portion_multiple_(portion_multiple),
+      id_base_(id_base) {
   // Same guards as the reference (src/scheduler.cpp:143-150): without them the loop never ends.
   if (max_concurrent_ <= 0) throw std::invalid_argument("ContinuousBatchScheduler: max_concurrent must be >= 1");
   if (budget_ <= 0) throw std::invalid_argument("ContinuousBatchScheduler: max_prefill_tokens_per_step must be >= 1");
   if (vocab_size_ <= 0 || max_positions_ <= 0) throw std::invalid_argument("ContinuousBatchScheduler: bad model sizes");
+  if (portion_multiple_ <= 0) throw std::invalid_argument("ContinuousBatchScheduler: portion_multiple must be >= 1");
+  // a budget below the multiple could never cut a long prompt: the loop would not end
+  if (budget_ < portion_multiple_)
+    throw std::invalid_argument("ContinuousBatchScheduler: max_prefill_tokens_per_step must be at least the model's portion multiple " +
+                                std::to_string(portion_multiple_));
 }
 
 void Scheduler::set_budget(int b) {
   if (b <= 0) throw std::invalid_argument("ContinuousBatchScheduler: max_prefill_tokens_per_step must be >= 1");
+  if (b < portion_multiple_)
+    throw std::invalid_argument("ContinuousBatchScheduler: max_prefill_tokens_per_step must be at least the model's portion multiple " +
+                                std::to_string(portion_multiple_));
   budget_ = b;
 }
 
@@ -105,7 +114,9 @@ const std::vector<StepEntry>& Scheduler::plan() {
     s.step_tokens = 0;
     s.step_samples = false;
     if (s.state == SeqState::FINISHED || budget <= 0) continue;
-    const int n = std::min(s.prompt_len - s.cursor, budget);
+    int n = std::min(s.prompt_len - s.cursor, budget);
+    // a portion that leaves some of the prompt for later ends at a multiple of portion_multiple_
+    if (n < s.prompt_len - s.cursor && portion_multiple_ > 1) n = (s.cursor + n) / portion_multiple_ * portion_multiple_ - s.cursor;
     if (n <= 0) continue;
     if (!cm_.reserve(cache_id(s), n)) {
       finish(s, "capacity");
@@ -192,6 +203,18 @@ void Scheduler::commit(const std::vector<std::int32_t>& sampled) {
     else still.push_back(std::move(s));
   }
   prefilling_.swap(still);
+  plan_.clear();
+  plan_seqs_.clear();
+  plan_open_ = false;
+}
+
+void Scheduler::fail_step(const std::string& reason) {
+  if (!plan_open_) throw std::logic_error("fail_step: no planned step");
+  for (Sequence* s : plan_seqs_) {
+    s->step_tokens = 0;
+    s->step_samples = false;
+    finish(*s, reason.c_str());
+  }
   plan_.clear();
   plan_seqs_.clear();
   plan_open_ = false;

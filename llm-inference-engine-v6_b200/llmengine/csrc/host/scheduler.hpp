@@ -32,7 +32,7 @@ struct SequenceResult {
   std::int64_t seq_id = 0;
   int prompt_len = 0;
   std::vector<std::int32_t> token_ids;  // prompt + generated
-  std::string finish_reason;            // "stop" | "length" | "capacity"
+  std::string finish_reason;            // "stop" | "length" | "capacity" | "error"
 };
 
 struct Sequence {
@@ -52,7 +52,8 @@ struct Sequence {
 class Scheduler {
  public:
   Scheduler(CacheManager& cm, int vocab_size, int max_positions, std::set<int> eos_token_ids,
-            int max_concurrent = 64, int max_prefill_tokens_per_step = 256, std::int64_t id_base = 0);
+            int max_concurrent = 64, int max_prefill_tokens_per_step = 256, std::int64_t id_base = 0,
+            int portion_multiple = 1);
 
   std::int64_t enqueue(std::vector<std::int32_t> prompt, int max_new_tokens, float temperature = 0.f,
                        std::int32_t seed = 0);
@@ -61,16 +62,25 @@ class Scheduler {
   // with one token per wanted row, in the order of the entries, before the next plan().
   const std::vector<StepEntry>& plan();
   void commit(const std::vector<std::int32_t>& sampled);
+  // The planned step could not be run (the device reported a failure): its requests end with
+  // `reason` ("error", as the reference's streaming path names it, include/llmengine/engine.hpp:90),
+  // keep what they had generated, and give their pages back at the next plan(). Requests that were
+  // not part of the step go on.
+  void fail_step(const std::string& reason);
   // Finalizes what is finished without planning (the end of run_until_idle in the reference).
   void finalize();
 
   bool idle() const { return waiting_.empty() && prefilling_.empty() && running_.empty(); }
   bool has_unfinished() const;
+  bool plan_open() const { return plan_open_; }  // a planned step awaits commit() or fail_step()
   std::vector<SequenceResult> results() const;  // sorted by seq_id
   void clear_results() { results_.clear(); }
   int budget() const { return budget_; }
   void set_budget(int b);
   int max_concurrent() const { return max_concurrent_; }
+  // A prompt portion that is not the prompt's last ends at a position that is a multiple of this
+  // (1: anywhere). Mixers whose state can only be carried over at such points ask for it.
+  int portion_multiple() const { return portion_multiple_; }
   int num_waiting() const { return static_cast<int>(waiting_.size()); }
   int num_prefilling() const { return static_cast<int>(prefilling_.size()); }
   int num_running() const { return static_cast<int>(running_.size()); }
@@ -88,7 +98,7 @@ class Scheduler {
   CacheManager& cm_;
   int vocab_size_, max_positions_;
   std::set<int> eos_;
-  int max_concurrent_, budget_;
+  int max_concurrent_, budget_, portion_multiple_;
   std::int64_t id_base_ = 0;
   std::int64_t next_id_ = 0;
   std::vector<std::int64_t> last_admitted_;

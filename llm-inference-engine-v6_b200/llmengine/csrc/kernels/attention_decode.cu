@@ -16,8 +16,12 @@
 // splits' partials in index order: a token's result does not depend on the batch or on page numbers.
 // Up to eight splits of a (request, key/value head) run as ONE thread-block cluster (CLUSTER): each
 // CTA finishes a slice of the output; every CTA stores its partial's shares into the shared memory
-// of the CTAs that finish them (distributed shared memory), and one cluster barrier later each CTA
-// finds all it needs in its own shared memory. More splits run as
+// of the CTAs that finish them (distributed shared memory) and then arrives on an mbarrier in each
+// of them; a CTA that has seen all arrivals finds all it needs in its own shared memory. The
+// hardware cluster barrier is used once, split in two: every thread arrives right after the CTA's
+// own barriers are initialised (nothing conditional comes before that) and waits just before the
+// first access to a peer's shared memory, which CUDA allows only once the peer has started. Every
+// other wait on a peer is a bounded wait on an mbarrier. More splits run as
 // several clusters of eight: every cluster merges its own splits the same way into ONE partial in
 // global memory, and the cluster that arrives last (a fence and a counter) merges those. Without
 // clusters every split's partial goes through global memory (about 2 us slower at six splits, and
@@ -44,7 +48,7 @@ constexpr int DEC_THREADS = 160;  // warps 0-3 compute, warp 4 lane 0 issues the
 constexpr int DEC_CONSUMERS = 128;
 constexpr int TK = 32;            // keys per tile
 constexpr int ROWS = 16;          // query rows (heads of the group; zeros beyond)
-enum : int { ERR_DEC_PRODUCER = 21, ERR_DEC_CONSUMER = 22, ERR_DEC_DRAIN = 23 };
+enum : int { ERR_DEC_PRODUCER = 21, ERR_DEC_CONSUMER = 22, ERR_DEC_DRAIN = 23, ERR_DEC_PEERS = 24 };
 
 struct DecParams {
   const bf16* q; long long ld_q;
@@ -84,6 +88,42 @@ __device__ __forceinline__ void store_to_cta(uint32_t smem_addr, int rank, float
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
+// The two halves of the hardware cluster barrier (all threads of the CTA, converged).
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+// One arrival on the mbarrier that CTA `rank` of this cluster keeps at the address `bar` has here.
+// Release at cluster scope: what this CTA stored into that CTA's shared memory before (ordered
+// before this thread by a CTA barrier) is visible to whoever sees the phase complete.
+__device__ __forceinline__ void mbar_arrive_cta(uint64_t* bar, int rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(rank));
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+
+// Bounded wait for arrivals from the peers of the cluster (acquire at cluster scope). The bound is
+// twice that of the waits inside a CTA: a peer that gives up one of those still arrives here, and
+// must find this CTA running. Unlike mbar_wait it does not leave early when another kernel has
+// already recorded an error: a CTA may not exit while a peer can still reach its shared memory.
+__device__ __forceinline__ bool mbar_wait_peers(uint64_t* bar, uint32_t parity, int* error_out, int code) {
+  const long long t0 = clock64();
+  for (uint32_t i = 0;; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((i & 255u) == 255u && clock64() - t0 > 2 * WAIT_CYCLES) {
+      atomicCAS(error_out, 0, code);
+      return false;
+    }
+  }
+}
+
 template <int HD, bool FUSED, bool DEEP, bool CLUSTER>
 __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                                  const __grid_constant__ CUtensorMap map_v,
@@ -96,7 +136,9 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
   bf16* q_s = reinterpret_cast<bf16*>(ring + (size_t)NS * L::STAGE_BYTES);  // [ROWS][Q_LD]
   uint64_t* full = reinterpret_cast<uint64_t*>(q_s + ROWS * L::Q_LD);       // [NS]
   uint64_t* empty = full + NS;                                              // [NS]
-  int* flags = reinterpret_cast<int*>(empty + NS);                          // [0] abort, [1] tiles issued, [2] is_last
+  uint64_t* peers_in = empty + NS;   // CLUSTER: every CTA of the cluster has stored its shares here (one arrival each)
+  uint64_t* slices_out = peers_in + 1;  // CLUSTER, in the cluster's first CTA: every CTA's slice of the cluster's partial is in global memory
+  int* flags = reinterpret_cast<int*>(slices_out + 1);                      // [0] abort, [1] tiles issued, [2] is_last
   bf16* kv_new = reinterpret_cast<bf16*>(flags + 4);                        // [2][HD]: the token's own key and value (fused form)
   // CLUSTER: where the peers store their shares of the partials. It must be memory that this CTA
   // uses for nothing else: a faster peer writes here while this CTA's ring is still in use.
@@ -126,6 +168,10 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
+    if (CLUSTER) {
+      mbar_init(peers_in, (uint32_t)p.cluster_size);
+      mbar_init(slices_out, (uint32_t)p.cluster_size);
+    }
     flags[0] = 0;
     flags[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -140,6 +186,9 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
     }
   }
   __syncthreads();
+  // This CTA runs and its barriers exist: the peers learn it at their cluster_wait(), which every
+  // thread passes before the CTA's first access to a peer's shared memory.
+  if (CLUSTER) cluster_arrive();
 
   if (warp == 4) {
     // ------------------------------------------------------------------ producer
@@ -412,8 +461,16 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
     }
   }
   __syncthreads();
+  if (CLUSTER) cluster_wait();  // every CTA of the cluster runs and has initialised its barriers
+  const int csize = CLUSTER ? p.cluster_size : 1, rank = CLUSTER ? split % csize : 0;
   if (*abort_flag) {
-    // a wait gave up: let the copies that were issued land (bounded) before the CTA leaves
+    // A wait gave up. The peers wait for this CTA's shares: tell them at once that there are none
+    // (the error word is set; the output of this launch is void), then let the copies that were
+    // issued land (bounded), and leave only when no peer can reach this CTA's shared memory any more.
+    if (CLUSTER && tid == 0) {
+      for (int c = 0; c < csize; ++c) mbar_arrive_cta(peers_in, c);
+      if (p.n_splits > csize) mbar_arrive_cta(slices_out, 0);
+    }
     if (tid == 0) {
       const int issued = flags[1];
       for (int t = max(0, issued - NS); t < issued; ++t) {
@@ -425,13 +482,12 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
           }
         }
       }
+      if (CLUSTER) {
+        mbar_wait_peers(peers_in, 0, p.error, ERR_DEC_PEERS);
+        if (p.n_splits > csize && rank == 0) mbar_wait_peers(slices_out, 0, p.error, ERR_DEC_PEERS);
+      }
     }
-    if (CLUSTER && p.n_splits > 1) {  // the peers wait at the cluster barriers: take part, with nothing to offer
-      __syncthreads();
-      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-      if (p.n_splits > p.cluster_size)
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    }
+    __syncthreads();
     return;
   }
   // ---- merge the four warps (in warp order)
@@ -459,7 +515,7 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
       p.out[(size_t)tok * p.ld_out + (size_t)head * HD + d] = __float2bfloat16_rn(acc * inv);
     } else if (CLUSTER) {
       // element e of the cluster's output is finished by rank e % size: send it this split's share
-      const int csize = p.cluster_size, rank = split % csize, epo = (g * HD + csize - 1) / csize;
+      const int epo = (g * HD + csize - 1) / csize;
       const uint32_t recv_a = smem_u32(recv);
       store_to_cta(recv_a + (uint32_t)(rank * epo + e / csize) * 4u, e % csize, acc * inv);
       if (d == 0) {
@@ -483,9 +539,26 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
     // ---- eight (or fewer) neighbouring splits are the CTAs of this cluster: every CTA has sent each
     // peer its share (remote shared-memory stores above) and, after the barrier, finishes the
     // elements e = rank, rank + size, ... from what it received, in index order
-    const int csize = p.cluster_size, rank = split % csize, group = split / csize;
+    const int group = split / csize;
     n_merge = p.n_splits / csize;
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    __syncthreads();  // the stores of all threads come before the arrivals below
+    if (tid == 0)
+      for (int c = 0; c < csize; ++c) mbar_arrive_cta(peers_in, c);
+    bool peers_ok = true;
+    if (tid == 0) peers_ok = mbar_wait_peers(peers_in, 0, p.error, ERR_DEC_PEERS);
+    peers_ok = __syncthreads_and(peers_ok);
+    // (after this no peer touches this CTA's shared memory again; the first CTA of a cluster also
+    // waits for `slices_out` below)
+    if (!peers_ok) {
+      if (n_merge > 1) {
+        if (tid == 0) {
+          mbar_arrive_cta(slices_out, 0);
+          if (rank == 0) mbar_wait_peers(slices_out, 0, p.error, ERR_DEC_PEERS);
+        }
+        __syncthreads();
+      }
+      return;
+    }
     const int epo = (g * HD + csize - 1) / csize;
     const float* recv_o = recv;
     const float* recv_ml = recv_o + csize * epo;
@@ -529,12 +602,16 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
     }
     if (n_merge == 1) return;  // (a CTA may leave at once: its peers read their own shared memory only)
     __threadfence();  // every CTA's slice of the cluster's partial is out before the leader counts it
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) mbar_arrive_cta(slices_out, 0);
     if (rank != 0) return;
+    bool slices_ok = true;
+    if (tid == 0) slices_ok = mbar_wait_peers(slices_out, 0, p.error, ERR_DEC_PEERS);
+    if (!__syncthreads_and(slices_ok)) return;
   }
   // ---- the CTA (the cluster's leader) that arrives last for this (request, key/value head) merges
   // the partials, in index order whichever one that is
-  if (!CLUSTER) __threadfence();
+  __threadfence();  // (CLUSTER: what the leader has seen of its peers' slices goes on to whoever sees its count)
   __syncthreads();
   if (tid == 0) {
     const int old = atomicAdd(&p.done_count[seq * p.nkv + kvh], 1);
@@ -588,7 +665,7 @@ int g_cluster_merge = 1;  // 0: splits always merge through global memory (for c
 template <int HD, bool DEEP>
 size_t decode_smem_bytes(int keys_per_cta, int page_size, int cluster_group) {  // cluster_group: heads per kv head, 0 without clusters
   using L = DecLayout<HD, DEEP>;
-  return (cluster_group ? (size_t)(cluster_group * (HD + 16) + 8) * sizeof(float) : 0) + 1024 + (size_t)L::STAGES * L::STAGE_BYTES + (size_t)ROWS * L::Q_LD * 2 + 2 * L::STAGES * 8 + 16 + 2 * HD * 2 +
+  return (cluster_group ? (size_t)(cluster_group * (HD + 16) + 8) * sizeof(float) : 0) + 1024 + (size_t)L::STAGES * L::STAGE_BYTES + (size_t)ROWS * L::Q_LD * 2 + (2 * L::STAGES + 2) * 8 + 16 + 2 * HD * 2 +
          (size_t)((keys_per_cta + 2 * TK) / page_size + 4) * sizeof(int);
 }
 

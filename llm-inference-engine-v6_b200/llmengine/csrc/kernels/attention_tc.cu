@@ -46,7 +46,7 @@ struct AttLayout {
 struct AttnTcParams {
   const bf16* q; long long ld_q;
   const int* seq_start; const int* seq_ntok; const int* seq_qoff; const int* block_table;
-  int max_blocks, nq, nkv, page_size, window;
+  int max_blocks, nq, nkv, page_size, window, null_page;
   float scale;
   bf16* out; long long ld_out;
   int* error_out;
@@ -118,7 +118,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
   uint64_t* s_bar = full + 2;           // the scores of a tile are in tensor memory
   uint64_t* p_bar = s_bar + 1;          // all 128 rows of P are in tensor memory (128 arrivals)
   uint64_t* o_bar = p_bar + 1;          // the P V product of a tile is done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_bar + 2);  // (one spare word keeps the ints after it 16-byte aligned)
+  uint64_t* done_bar = o_bar + 1;       // every product that was issued has finished (committed last, also after giving up)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* page_s = reinterpret_cast<int*>(tmem_slot + 4);  // the tile range's slice of the block table
 
@@ -152,6 +153,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
     mbar_init(s_bar, 1);
     mbar_init(p_bar, ROWS);
     mbar_init(o_bar, 1);
+    mbar_init(done_bar, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -159,29 +161,28 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS_ATT) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // The pages of this CTA's key range, read once by all threads: the thread that issues the copies
-  // would otherwise wait for a global read before every single one of them.
+  // The pages of this CTA's key tiles, read once by all threads: the thread that issues the copies
+  // would otherwise wait for a global read before every single one of them. Every tile is fetched
+  // whole: pages that the request does not hold (beyond its newest key, or given back behind a
+  // window) are read from the pool's null page, whose values are finite and meet probabilities of
+  // exactly zero, so no stage has to be cleared and no copy depends on a fill convention.
   const int page_lo = (kt_first * KEYS) / p.page_size;
   {
-    const int n_pages_all = hi / p.page_size - page_lo + 1;
-    for (int i = tid; i < n_pages_all; i += ATT_THREADS) page_s[i] = table[page_lo + i];
+    const int n_pages_all = (kt_last + 1) * pages_per_tile - page_lo;
+    for (int i = tid; i < n_pages_all; i += ATT_THREADS) {
+      const int idx = page_lo + i;
+      const int page = (idx < p.max_blocks && idx * p.page_size <= hi) ? table[idx] : -1;
+      page_s[i] = page >= 0 ? page : p.null_page;
+    }
   }
-  // key/value stages start as zeros: rows that no copy fills (beyond the request's last page) are
-  // multiplied by probabilities of exactly zero and must not hold NaN patterns
-  for (int i = tid; i < 4 * KV_BYTES / 16; i += ATT_THREADS) reinterpret_cast<uint4*>(kv_s)[i] = make_uint4(0, 0, 0, 0);
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the zeros are in place before any copy lands on them
   __syncthreads();
-  auto issue_tile = [&](int i) {  // keys and values of tile i -> stage i % 2; pages beyond the newest key are not fetched
-    const int first_key = (kt_first + i) * KEYS;
+  auto issue_tile = [&](int i) {  // keys and values of tile i -> stage i % 2
+    const int first_page = (kt_first + i) * pages_per_tile - page_lo;
     uint8_t* ks = kv_s + (size_t)(i & 1) * 2 * KV_BYTES;
     uint8_t* vs = ks + KV_BYTES;
-    int n_pages = 0;
-    for (int pg = 0; pg < pages_per_tile; ++pg)
-      if (first_key + pg * p.page_size <= hi) n_pages = pg + 1;
-    mbar_expect_tx(&full[i & 1], (uint32_t)(n_pages * p.page_size * HD * 2 * 2));
-    for (int pg = 0; pg < n_pages; ++pg) {
-      const int page = page_s[(first_key + pg * p.page_size) / p.page_size - page_lo];
-      const int row = (page * p.nkv + kvh) * p.page_size;
+    mbar_expect_tx(&full[i & 1], (uint32_t)(2 * KV_BYTES));
+    for (int pg = 0; pg < pages_per_tile; ++pg) {
+      const int row = (page_s[first_page + pg] * p.nkv + kvh) * p.page_size;
 #pragma unroll
       for (int b = 0; b < DBLK; ++b) {
         tma_load_2d(ks + b * (KEYS * 128) + (size_t)pg * p.page_size * 128, &map_k, b * 64, row, &full[i & 1]);
@@ -232,8 +233,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
         }
         mma_commit(s_bar);
       };
+      int issued = n_tiles > 1 ? 2 : 1, landed = 0;  // tiles whose copies were requested / have arrived
       ok = mbar_wait(&full[0], 0, abort_flag, p.error_out, ERR_ATT_KV);
       if (ok) {
+        landed = 1;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         issue_scores(0);
       }
@@ -255,14 +258,21 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
         if (i + 1 < n_tiles) {  // the next tile's scores go to the tensor pipe right behind this product
           ok = mbar_wait(&full[(i + 1) & 1], (uint32_t)((i + 1) >> 1) & 1u, abort_flag, p.error_out, ERR_ATT_KV);
           if (!ok) break;
+          landed = i + 2;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           issue_scores(i + 1);
         }
         if (i + 2 < n_tiles) {  // stage i % 2 is free once the product of tile i is done
           ok = mbar_wait(o_bar, (uint32_t)i & 1u, abort_flag, p.error_out, ERR_ATT_O);
-          if (ok) issue_tile(i + 2);
+          if (ok) {
+            issue_tile(i + 2);
+            issued = i + 3;
+          }
         }
       }
+      mma_commit(done_bar);
+      // gave up: the copies still on their way land (bounded) before the CTA gives its shared memory back
+      for (int t = landed; !ok && t < issued; ++t) mbar_drain(&full[t & 1], (uint32_t)(t >> 1) & 1u, p.error_out);
     }
   } else {
     // -------------------------------------------------------------- softmax: thread t owns row t
@@ -363,6 +373,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
       }
     }
   }
+  // tensor memory and the stages are the products' until the last one issued is done (at once when
+  // every tile's output was waited for above; what counts when a role gave up)
+  if (tid == 0) mbar_drain(done_bar, 0, p.error_out);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS_ATT) : "memory");
@@ -371,8 +384,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
 template <int HD>
 bool launch_att(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, dim3 grid, int max_blocks, cudaStream_t stream) {
   using L = AttLayout<HD>;
-  // Q, two stages of K and V, six 8-byte words of barriers, four ints, the block-table slice, alignment slack
-  const size_t smem = L::Q_BYTES + 4 * L::KV_BYTES + 6 * sizeof(uint64_t) + 16 + (size_t)max_blocks * sizeof(int) + 1024;
+  // Q, two stages of K and V, six 8-byte words of barriers, four ints, the block-table slice (whole tiles: up to 16
+  // pages beyond the table's width), alignment slack
+  const size_t smem = L::Q_BYTES + 4 * L::KV_BYTES + 6 * sizeof(uint64_t) + 16 + (size_t)(max_blocks + 16) * sizeof(int) + 1024;
   static size_t attr_smem = 0;
   if (smem > attr_smem) {
     if (cudaFuncSetAttribute(paged_attention_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
@@ -394,7 +408,8 @@ extern "C" int llm_attention_tc_supported(int nq, int nkv, int hd, int page_size
          encode_fn() != nullptr;
 }
 
-// q: rows of [nq*hd] bf16; caches [pages, nkv, page_size, hd] bf16 (n_cache_pages pages each);
+// q: rows of [nq*hd] bf16; caches [pages, nkv, page_size, hd] bf16 (n_cache_pages pages each, the LAST of
+// them the null page: finite values, never a request's);
 // seq_* and block_table as in the step's batch; out [n_tokens, nq*hd] bf16.
 extern "C" int llm_paged_attention_tc(const void* q, long long ld_q, const void* kcache, const void* vcache, long long n_cache_pages,
                                       const int* seq_start, const int* seq_ntok, const int* seq_qoff, const int* block_table,
@@ -415,6 +430,7 @@ extern "C" int llm_paged_attention_tc(const void* q, long long ld_q, const void*
   p.q = (const bf16*)q; p.ld_q = ld_q; p.seq_start = seq_start; p.seq_ntok = seq_ntok; p.seq_qoff = seq_qoff; p.block_table = block_table;
   p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.scale = scale;
   p.out = (bf16*)out; p.ld_out = ld_out; p.error_out = error_word();
+  p.null_page = (int)(n_cache_pages - 1);
   LLM_REQUIRE(max_blocks <= 4096, "attention_tc: block tables wider than 4096 pages are not supported");
   const int g = nq / nkv, tq_cap = ROWS / g;
   dim3 grid(nkv, n_seqs, (max_new_tokens + tq_cap - 1) / tq_cap);

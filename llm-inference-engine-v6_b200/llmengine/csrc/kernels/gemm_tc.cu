@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(128)
         mma_f16(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (it > 0 || k > 0) ? 1u : 0u);
       mma_commit(&empty[s]);  // arrives when the MMAs above have read the stage
     }
-    if (ok) mma_commit(acc_ready);
+    mma_commit(acc_ready);  // also when a wait gave up: arrives once every product issued above has finished
   }
   __syncwarp();
   dep_wait();  // every thread: no global write before the previous kernels have finished
@@ -262,6 +262,8 @@ __global__ void __launch_bounds__(128)
       }
     }
   }
+  // a role gave up: products that were issued may still run; the stages and tensor memory are theirs until then
+  if (!ready && n_iter > 0 && threadIdx.x == 0) mbar_drain(acc_ready, 0, error_out);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0) {
@@ -294,7 +296,8 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
   uint64_t* empty = full + stages;
   uint64_t* acc_full = empty + stages;   // [2] the tensor cores have finished a tile in accumulator b
   uint64_t* acc_empty = acc_full + 2;    // [2] the epilogue warps have read accumulator b
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* mma_done = acc_empty + 2;    // every product this CTA issued has finished (committed last, also after giving up)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mma_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* issued_slot = const_cast<int*>(abort_flag) + 1;
 
@@ -311,6 +314,7 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
     }
+    mbar_init(mma_done, 1);
     *abort_flag = 0;
     *issued_slot = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -394,6 +398,7 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
         }
         if (ok) mma_commit(&acc_full[b]);
       }
+      mma_commit(mma_done);
     }
   } else {
     // ------------------------------------------------------------------ epilogue: warps 0-3
@@ -439,6 +444,9 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[b]);
     }
+    // Tensor memory and the stages belong to the products in flight until the last of them is done
+    // (at once when every tile was drained above; what counts when a role gave up).
+    if (threadIdx.x == 0) mbar_drain(mma_done, 0, error_out);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -518,7 +526,8 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
   uint64_t* empty = full + stages;
   uint64_t* acc_full = empty + stages;   // [2]
   uint64_t* acc_empty = acc_full + 2;    // [2] used in the leader only: 8 arrivals
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* mma_done = acc_empty + 2;    // in both CTAs: every product the leader issued has finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mma_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -536,6 +545,7 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 8);  // four epilogue warps in each CTA of the pair
     }
+    mbar_init(mma_done, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -619,6 +629,7 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
         }
         if (ok) mma_commit_pair(&acc_full[b]);
       }
+      mma_commit_pair(mma_done);  // also after giving up: the stages and tensor memory of BOTH CTAs are the products' until then
     }
   } else {
     // ------------------------------------------------------------------ epilogue: warps 0-3 of both CTAs
@@ -664,6 +675,7 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&acc_empty[b]), 0));
     }
+    if (threadIdx.x == 0) mbar_drain(mma_done, 0, error_out);
   }
   __syncwarp();  // lanes of the producer and issue warps went different ways; the cluster barrier wants whole warps
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -679,7 +691,7 @@ int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int 
   constexpr int STAGE_BYTES = A_BYTES + 128 * BK * 2;
   const int k_tiles = (K + BK - 1) / BK;
   const int stages = 6;
-  const size_t smem = (size_t)stages * STAGE_BYTES + (2 * stages + 4) * sizeof(uint64_t) + 16 + 1024;
+  const size_t smem = (size_t)stages * STAGE_BYTES + (2 * stages + 5) * sizeof(uint64_t) + 16 + 1024;
   auto kernel = gemm_tc_pair_kernel<TO, SWIGLU>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -702,7 +714,7 @@ int launch_tc_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out
   constexpr int STAGE_BYTES = A_BYTES + BN * BK * 2;
   const int k_tiles = (K + BK - 1) / BK;
   const int stages = BN == 256 ? 4 : 5;
-  const size_t smem = (size_t)stages * STAGE_BYTES + (2 * stages + 4) * sizeof(uint64_t) + 16 + 1024;
+  const size_t smem = (size_t)stages * STAGE_BYTES + (2 * stages + 5) * sizeof(uint64_t) + 16 + 1024;
   auto kernel = gemm_tc_persistent_kernel<TO, SWIGLU, BN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -902,6 +914,27 @@ extern "C" int llm_gemm_tc_swiglu(const void* a, const void* w, void* act, int M
   if (rc != LLM_OK) return rc;
   LLM_CHECK_LAUNCH("gemm_tc_swiglu");
   return LLM_OK;
+}
+
+// Queues a copy of the error word into `host_word` (pinned host memory) on `stream`, behind the
+// kernels already launched there: after the stream is synchronized the host reads the code of the
+// step without a transfer of its own. May be captured in a CUDA graph.
+extern "C" int llm_tc_error_copy_async(int* host_word, cudaStream_t stream) {
+  int* w = error_word();
+  LLM_REQUIRE(w != nullptr && host_word != nullptr, "tc_error_copy: no error word");
+  if (cudaMemcpyAsync(host_word, w, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess) {
+    llm_set_error("tc_error_copy: cudaMemcpyAsync failed");
+    return LLM_ERR_LAUNCH;
+  }
+  return LLM_OK;
+}
+
+// Writes the error word from the host (0 clears it). For tests of the host's error handling, which
+// must not make a kernel fail in order to see the code. Synchronizes.
+extern "C" int llm_tc_error_set(int code) {
+  int* w = error_word();
+  if (!w) return -1;
+  return cudaMemcpy(w, &code, sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess ? 0 : -2;
 }
 
 // Reads and clears the error code that a tensor-core kernel may have left (0 = none). Synchronizes.

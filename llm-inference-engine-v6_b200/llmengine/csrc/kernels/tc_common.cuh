@@ -49,7 +49,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait. Returns false if the phase did not complete in time or another role aborted.
+// Bounded wait. Returns false if the phase did not complete in time or another role aborted. Once
+// any kernel of the process has recorded an error, later waits that do not complete within a few
+// hundred polls give up at once instead of after a second each: everything computed since that
+// error is void anyway (the host raises when it reads the word), and a fault that repeats in every
+// launch then costs microseconds, not seconds, per launch.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* error_out, int code) {
   if (mbar_try_wait(bar, parity)) return true;  // the usual case costs one instruction
   const long long t0 = clock64();
@@ -57,11 +61,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 255u) == 255u) {
       if (*abort_flag) return false;
+      if (*reinterpret_cast<volatile int*>(error_out) != 0) {
+        *abort_flag = code;
+        return false;
+      }
       if (clock64() - t0 > WAIT_CYCLES) {
         *abort_flag = code;
         atomicCAS(error_out, 0, code);
         return false;
       }
+    }
+  }
+}
+
+// Last wait of a role that is leaving early: for copies or products that it (or its CTA) issued and
+// that still write shared or tensor memory. It looks at no abort flag and at no error word, since
+// the memory may not be given up before they are done; twice the bound of the waits above, so that
+// a role which itself waits out a full bound still gets here in time.
+__device__ __forceinline__ void mbar_drain(uint64_t* bar, uint32_t parity, int* error_out) {
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > 2 * WAIT_CYCLES) {
+      atomicCAS(error_out, 0, (int)ERR_DRAIN);
+      return;
     }
   }
 }

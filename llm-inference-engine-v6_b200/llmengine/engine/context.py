@@ -44,6 +44,12 @@ class Workspace:
             self._buffers[tag].zero_()
         return out
 
+    def zero(self, tag: str) -> None:
+        """Clears a tag's buffer, if there is one (after a failed step left it in an unknown state)."""
+        buf = self._buffers.get(tag)
+        if buf is not None:
+            buf.zero_()
+
     def bytes(self) -> int:
         return sum(b.numel() for b in self._buffers.values())
 

@@ -197,7 +197,33 @@ class Engine:
             self._ensure_cache()
             ctx = self.buffers.prepare(self.cm, entries, self.spec.vocab_size, self.max_pos, pad_to)
             logits = self.model.forward(ctx)
+            self.queue_error_check()
             return ctx, logits
+
+    # ------------------------------------------------------------------ kernels that gave up
+    def queue_error_check(self) -> None:
+        """The tensor-core kernels bound every wait; one that gives up leaves a code in a device word
+        and returns, and what the step computed is void. A copy of that word travels behind every
+        step (4 bytes into pinned memory, also inside the decode graphs) and is looked at wherever
+        the host has waited for the step anyway."""
+        q = getattr(self.ops, "queue_error_check", None)
+        if q is not None:
+            q()
+
+    def raise_if_kernel_error(self) -> None:
+        """Call after the stream has been synchronized. On a code: the counters that the kernels
+        leave at zero between launches are cleared (an aborted launch may not have), the device
+        word is reset, and KernelError is raised; the caller decides what becomes of the requests."""
+        take = getattr(self.ops, "take_step_error", None)
+        code = take() if take is not None else 0
+        if not code:
+            return
+        spaces = [self.ws] + ([c.buffers.ws for c in self.graphs.captured.values()] if self.graphs is not None else [])
+        for ws in spaces:
+            ws.zero("attention.split_counters")
+        from ..ops import KernelError
+        what = getattr(self.ops, "ERROR_CODES", {}).get(code, "unknown code")
+        raise KernelError(f"a tensor-core kernel gave up a bounded wait (code {code}: {what}); the step's results are void")
 
     def step_and_sample(self, entries) -> List[int]:
         """A step followed by the choice of one token for every wanted row (greedy or by the rows'
@@ -212,7 +238,9 @@ class Engine:
                     self.graphs = DecodeGraphs(self)
                 return self.graphs.run(entries)
             ctx, logits = self.step(entries)
-            return self.sampler.sample(logits, ctx, ctx.n_rows)
+            tokens = self.sampler.sample(logits, ctx, ctx.n_rows)  # (waits for the stream)
+            self.raise_if_kernel_error()
+            return tokens
 
     def run_step(self, batch: Sequence[Tuple[int, Sequence[int], Sequence[int]]], end: Iterable[int] = ()) -> torch.Tensor:
         """The whole step function for callers that bring their own schedule (trace replay, tests):
@@ -237,6 +265,10 @@ class Engine:
                         raise CapacityError(f"KV pool exhausted at position {self.cm.length(rid)} of request {rid}")
                     entries.add(rid, [int(t) for t in tokens], [int(w) for w in want])
                 ctx, logits = self.step(entries) if len(entries) else (None, torch.empty(0, self.spec.vocab_size))
+                if len(entries):
+                    if self.device.type == "cuda":
+                        torch.cuda.current_stream().synchronize()
+                    self.raise_if_kernel_error()
             except Exception:
                 for rid in fresh:
                     self.cm.release(rid)
@@ -305,6 +337,11 @@ class Engine:
             sched = ContinuousBatchScheduler(self, None, max_concurrent=1,
                                              max_prefill_tokens_per_step=max(len(prompt), 1))
             sched.enqueue(prompt, int(max_new_tokens), temperature=temperature, seed=seed)
-            sched.run_until_idle()
+            try:
+                sched.run_until_idle()
+            except Exception:
+                if not sched.core.plan_open:
+                    sched.core.finalize()  # the request ended with "error": its pages and slot go back now
+                raise
             r = sched.results[0]
             return list(r.token_ids), r.finish_reason

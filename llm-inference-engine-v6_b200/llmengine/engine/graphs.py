@@ -27,6 +27,7 @@ class _Captured:
         self.host_tokens: Optional[torch.Tensor] = None
         self.pad_to: Tuple[int, int, int, int] = (0, 0, 0, 0)
         self.kernels = 0  # kernel launches inside the graph
+        self.logits: Optional[torch.Tensor] = None
 
 
 class DecodeGraphs:
@@ -37,6 +38,7 @@ class DecodeGraphs:
         self.engine = engine
         self.captured: Dict[Tuple[int, int], _Captured] = {}
         self.h2d_bytes = self.d2h_bytes = 0  # of the last step (for measurements)
+        self.last: Optional[_Captured] = None  # the graph that ran the last step
 
     def clear(self) -> None:
         self.captured.clear()
@@ -60,8 +62,9 @@ class DecodeGraphs:
 
         def prepare(entries):
             ctx = c.buffers.prepare(eng.cm, entries, eng.spec.vocab_size, eng.max_pos, c.pad_to)
-            # the longest context this graph may meet decides the key splits of attention
-            ctx.max_seq_len, ctx.max_new_tokens, ctx.decode_only = blocks * page, 1, True
+            # the longest context this graph may meet decides the key splits of attention (the table
+            # is rounded up to whole buckets of pages; no position lies beyond the model's limit)
+            ctx.max_seq_len, ctx.max_new_tokens, ctx.decode_only = min(blocks * page, eng.max_pos), 1, True
             return ctx
 
         empty = H.StepEntries()  # only padded rows: every kernel runs on the null request
@@ -72,6 +75,7 @@ class DecodeGraphs:
             for _ in range(2):  # sizes every scratch buffer and loads every kernel before the capture
                 logits = eng.model.forward(ctx)
                 sampler.sample_device(logits, ctx, cap)
+                eng.queue_error_check()  # (its pinned word is made here, not inside the capture)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(eng.device)
         ws.frozen = True
@@ -82,6 +86,8 @@ class DecodeGraphs:
         with torch.cuda.graph(graph):
             logits = eng.model.forward(ctx)
             c.tokens = sampler.sample_device(logits, ctx, cap, out=c.host_tokens)
+            c.logits = logits  # of the last replay, padded rows included (read by tests)
+            eng.queue_error_check()
         c.kernels = eng.ops.launches - before
         c.graph = graph
         layout = H.StepLayout.make(cap, cap, cap, blocks, eng.cm.num_groups)
@@ -110,7 +116,9 @@ class DecodeGraphs:
         c.graph.replay()
         eng.ops.launches += c.kernels
         torch.cuda.current_stream().synchronize()
+        eng.raise_if_kernel_error()
         self.h2d_bytes, self.d2h_bytes = c.buffers.h2d_bytes, 4 * cap
+        self.last = c
         return c.host_tokens.tolist()[:seqs]
 
     def run_device(self, entries) -> torch.Tensor:

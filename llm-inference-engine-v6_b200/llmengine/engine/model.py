@@ -7,6 +7,7 @@ for positions whose logits are not asked for, src/engine.cpp:415-433).
 """
 from __future__ import annotations
 
+import math
 from typing import List, Optional, Sequence
 
 import torch
@@ -39,6 +40,14 @@ class Model:
         self.run_needs: List[Sequence[object]] = [
             () if run.cache_from is not None else tuple(self.blocks[run.layer].cache_needs()) for run in spec.order]
         self.windows, self.run_group = plan_groups(self.run_needs)
+        # where the scheduler may cut a prompt: the least common multiple of what the layers ask for
+        self.portion_multiple = 1
+        for needs in self.run_needs:
+            for need in needs:
+                m = int(getattr(need, "portion_multiple", 1))
+                if m < 1:
+                    raise ValueError(f"cache need {need!r}: portion_multiple must be >= 1")
+                self.portion_multiple = math.lcm(self.portion_multiple, m)
         self.caches: List[LayerCache] = [LayerCache() for _ in range(n_runs)]
         self.weight_bytes = 0
 

@@ -12,6 +12,7 @@ from __future__ import annotations
 from typing import List, Sequence
 
 from ..cache.host import host_module
+from ..ops import KernelError
 
 
 class ContinuousBatchScheduler:
@@ -28,7 +29,8 @@ class ContinuousBatchScheduler:
         H = host_module()
         self.core = H.SchedulerCore(engine.cm, engine.spec.vocab_size, engine.max_pos,
                                     set(int(t) for t in engine.spec.eos_token_ids), max_concurrent,
-                                    max_prefill_tokens_per_step, engine._next_id_base())
+                                    max_prefill_tokens_per_step, engine._next_id_base(),
+                                    engine.model.portion_multiple)
         self._cm = engine.cm
         self.steps = 0
 
@@ -48,7 +50,14 @@ class ContinuousBatchScheduler:
             for rid in self.core.last_admitted:
                 eng.model.reset_slot(self._cm.slot(rid))
             if len(entries):
-                self.core.commit(eng.step_and_sample(entries))
+                try:
+                    tokens = eng.step_and_sample(entries)
+                except KernelError:
+                    # what the step computed is void: its requests end with "error" (their pages come
+                    # back at the next plan); requests that were not in the step go on
+                    self.core.fail_step("error")
+                    raise
+                self.core.commit(tokens)
                 self.steps += 1
         return not self.core.idle
 

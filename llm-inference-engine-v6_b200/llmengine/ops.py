@@ -58,6 +58,7 @@ class CudaOps:
         self.tcgen05_attention = True  # prompt portions: attention on tcgen05 where the geometry allows it
         self.tma_decode_attention = True  # single decoded tokens: keys and values by TMA where the geometry allows it
         self.fused_decode_attention = True  # ... with the sum of the q|k|v parts, rotation and cache write in the same kernel
+        self._err_host: Optional[torch.Tensor] = None  # pinned word that queue_error_check copies the kernels' error code into
 
     # ------------------------------------------------------------------ loading
     def lib(self, name: str = "core"):
@@ -278,10 +279,50 @@ class CudaOps:
         return out
 
     def tensor_core_error(self) -> int:
-        """Code left by a tensor-core kernel that gave up a bounded wait (0: none). Synchronizes."""
+        """Code left by a tensor-core kernel that gave up a bounded wait (0: none); reading clears it.
+        Synchronizes."""
         if "tensorcore" not in self._libs:
             return 0
         return int(self._libs["tensorcore"].llm_gemm_tc_error())
+
+    # What the codes mean (csrc/kernels/tc_common.cuh, attention_tc.cu, attention_decode.cu).
+    ERROR_CODES = {1: "product: a stage never became free", 2: "product: operands or an accumulator never arrived",
+                   3: "product: the accumulator was never finished", 4: "product: a copy in flight did not land",
+                   11: "prompt attention: keys or values never arrived", 12: "prompt attention: scores or probabilities never arrived",
+                   13: "prompt attention: the output product never finished",
+                   21: "decoding attention: a stage never became free", 22: "decoding attention: a tile never arrived",
+                   23: "decoding attention: a copy in flight did not land", 24: "decoding attention: a CTA of the cluster never reported"}
+
+    def queue_error_check(self) -> None:
+        """Queues, behind the kernels launched so far on the current stream, a copy of the tensor-core
+        kernels' error word into pinned host memory (4 bytes; may be captured in a CUDA graph).
+        take_step_error() reads it once the stream has been synchronized."""
+        if "tensorcore" not in self._libs:
+            return
+        if self._err_host is None:
+            self._err_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        lib = self._libs["tensorcore"]
+        rc = lib.llm_tc_error_copy_async(c_void_p(self._err_host.data_ptr()), _stream())
+        if rc != 0:
+            raise KernelError(lib.llm_last_error().decode())
+
+    def take_step_error(self) -> int:
+        """The code that the last queued check brought back (0: none), without touching the device
+        unless there is one: then the device's word is cleared, so that later kernels wait normally."""
+        if self._err_host is None:
+            return 0
+        code = int(self._err_host[0])
+        if code:
+            self._err_host[0] = 0
+            self.tensor_core_error()
+        return code
+
+    def set_tensor_core_error(self, code: int) -> None:
+        """Writes the error word from the host, for tests of the error handling (no kernel has to
+        fail for the host to see a code)."""
+        rc = int(self.lib("tensorcore").llm_tc_error_set(c_int(code)))
+        if rc != 0:
+            raise KernelError(f"cannot write the error word ({rc})")
 
     # ------------------------------------------------------------------ attention
     def rope_kv_write(self, qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,

@@ -25,18 +25,26 @@ class BuildEnv:
 # ---------------------------------------------------------------------------- cache needs
 @dataclass(frozen=True)
 class KVNeed:
-    """Keys and values per token, kept in pages. window 0: all of them; W: the last W."""
+    """Keys and values per token, kept in pages. window 0: all of them; W: the last W.
+    portion_multiple: see StateNeed."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    portion_multiple: int = 1
 
 
 @dataclass(frozen=True)
 class StateNeed:
-    """Per-request state of fixed size, kept in the request's slot; zeroed when a request starts."""
+    """Per-request state of fixed size, kept in the request's slot; zeroed when a request starts.
+    portion_multiple: where a prompt may be cut. 1: anywhere (attention, and any state that is
+    updated token by token). M > 1: a portion that leaves part of the prompt for a later step must
+    end at a position that is a multiple of M (a mixer that carries its state over only at the
+    edges of chunks of M tokens); the scheduler cuts prompts accordingly, and the multiple of a
+    model is the least common multiple over its layers. Single decoded tokens are not portions."""
     name: str
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+    portion_multiple: int = 1
 
 
 @dataclass

@@ -243,6 +243,18 @@ def forward_logits(cfg, w, ids) -> np.ndarray:
     """Logits [T,V] at every position of one sequence (src/engine.cpp:694-716 with the layer loop
     of src/engine.cpp:105-261): h=E[id]; per layer h+=Attn(RMSNorm(h)); h+=MLP(RMSNorm(h));
     logits = lm_head(RMSNorm(h))."""
+    return logits_at(cfg, w, final_hidden(cfg, w, ids), None)
+
+
+def logits_at(cfg, w, h: np.ndarray, rows) -> np.ndarray:
+    """Final norm and head for the given rows of the residual stream (all rows if None): the
+    reference skips both for positions whose logits are not asked for (src/engine.cpp:415-433)."""
+    x = rmsnorm(h if rows is None else h[np.asarray(rows, dtype=np.int64)], w["model.norm.weight"], cfg["rms_norm_eps"])
+    return linear(x, w["lm_head.weight"])
+
+
+def final_hidden(cfg, w, ids) -> np.ndarray:
+    """The residual stream [T,H] after the last layer (the layer loop of src/engine.cpp:105-261)."""
     T = len(ids)
     hd = cfg["head_dim"]
     inv = llama3_inv_freq(hd, cfg["rope_theta"], cfg["rope_has_scaling"], cfg["rope_factor"],
@@ -258,8 +270,7 @@ def forward_logits(cfg, w, ids) -> np.ndarray:
         x = rmsnorm(h, w[p + "post_attention_layernorm.weight"], eps)
         h = h + swiglu_mlp(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
                            w[p + "mlp.down_proj.weight"])
-    x = rmsnorm(h, w["model.norm.weight"], eps)
-    return linear(x, w["lm_head.weight"])
+    return h
 
 
 # ----------------------------------------------------------------------------- sampling, generation

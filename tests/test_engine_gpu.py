@@ -11,21 +11,27 @@ import torch
 
 import llmengine
 import plain_llama as P
-from tiny import TINY_A, TINY_B, TINY_D, make_model_dir, random_ids
+from tiny import TINY_A, TINY_B, TINY_D, TINY_E, make_model_dir, random_ids
 
 pytestmark = pytest.mark.gpu
 TOL = {"fp32": 2e-4, "bf16": 6e-2}
 
 
-@pytest.fixture(scope="module", params=[("a", "fp32"), ("a", "bf16"), ("b", "fp32"), ("b", "bf16"), ("d", "fp32"), ("d", "bf16")],
+# f: configuration d with a position limit (500) that is no multiple of 16 pages of 16 positions
+TINY_F = dict(TINY_D, max_position_embeddings=500)
+
+
+@pytest.fixture(scope="module", params=[("a", "fp32"), ("a", "bf16"), ("b", "fp32"), ("b", "bf16"), ("d", "fp32"), ("d", "bf16"),
+                                        ("e", "fp32"), ("e", "bf16"), ("f", "bf16")],
                 ids=lambda p: f"{p[0]}-{p[1]}")
 def setup(request, tmp_path_factory):
     name, dtype = request.param
-    cfg = {"a": TINY_A, "b": TINY_B, "d": TINY_D}[name]  # d: head size 64, pages of 16: the tensor-core attention kernels
+    # d: head size 64, pages of 16: the tensor-core attention kernels; e: head size 128, a group of three, pages of 32
+    cfg = {"a": TINY_A, "b": TINY_B, "d": TINY_D, "e": TINY_E, "f": TINY_F}[name]
     d = str(tmp_path_factory.mktemp(f"eng_{name}_{dtype}"))
     make_model_dir(d, cfg, torch.float32 if dtype == "fp32" else torch.bfloat16)
     pc, pw = P.read_model(d)
-    eng = llmengine.Engine(d, dtype, block_size=4 if name == "a" else 16, num_blocks=96, max_concurrent=8)
+    eng = llmengine.Engine(d, dtype, block_size={"a": 4, "e": 32}.get(name, 16), num_blocks=96, max_concurrent=8)
     return cfg, eng, pc, pw, dtype
 
 
@@ -502,7 +508,8 @@ def _window_row(q, k, v, nq, nkv, hd):
     return out.reshape(-1)
 
 
-@pytest.mark.parametrize("name,dtype,seed", [("d", "fp32", 1), ("a", "fp32", 2), ("e", "fp32", 3), ("d", "bf16", 4)])
+@pytest.mark.parametrize("name,dtype,seed", [("d", "fp32", 1), ("a", "fp32", 2), ("e", "fp32", 3), ("d", "bf16", 4), ("e", "bf16", 5),
+                                             ("f", "bf16", 6)])
 def test_scheduler_under_random_load_and_page_pressure(tmp_path, name, dtype, seed):
     """Forty requests of random lengths, budgets and temperatures arrive while others run, through a
     pool that holds about three of them: many end with "capacity". Every request's tokens are the
@@ -510,7 +517,7 @@ def test_scheduler_under_random_load_and_page_pressure(tmp_path, name, dtype, se
     tie), "length" means exactly max_new_tokens, and no page is lost."""
     from tiny import TINY
     rng = np.random.default_rng(seed)
-    cfg, page = TINY[name]
+    cfg, page = dict(TINY, f=(TINY_F, 16))[name]
     d = str(tmp_path / "m")
     make_model_dir(d, cfg, torch.float32 if dtype == "fp32" else torch.bfloat16)
     pc, pw = P.read_model(d)

@@ -7,8 +7,8 @@ import pytest
 import torch
 
 import plain_llama as P
-from tiny import (TINY, make_model_dir, random_ids, round64, run_trace, trace_mixed, trace_portions, trace_tail,
-                  trace_whole, Trace)
+from tiny import (MIXED_SIZES, MIXED_SIZES_LONG, TINY, make_model_dir, random_ids, round64, run_trace, trace_mixed,
+                  trace_portions, trace_tail, trace_whole, Trace)
 
 pytestmark = pytest.mark.gpu
 
@@ -39,17 +39,19 @@ def replayed(request, tmp_path_factory):
         full.extend(t)
     longest = max(round64(len(v)) for v in reqs.values())
     max_tokens = longest + 3 * 64  # room for the longest request and three short ones: pages are reused
-    t = trace_mixed({f"mixed.{k}": v for k, v in reqs.items()}, max_tokens, seed=5)
+    # (configuration a holds 128 positions: its prompts are too short for the long portions)
+    t = trace_mixed({f"mixed.{k}": v for k, v in reqs.items()}, max_tokens, seed=5,
+                    sizes=MIXED_SIZES if name == "a" else MIXED_SIZES_LONG)
     spans["mixed"] = (len(full.steps), len(full.steps) + len(t.steps))
     full.extend(t)
     out = str(tmp_path_factory.mktemp(f"out_{name}_{dtype}"))
     rows = run_trace(d, dtype, full, out, max_tokens, page, cfg["vocab_size"])
-    return dtype, reqs, plain, rows, t
+    return dtype, reqs, plain, rows, t, name
 
 
 @pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
 def test_cut_matches_plain(replayed, cut):
-    dtype, reqs, plain, rows, _ = replayed
+    dtype, reqs, plain, rows, *_ = replayed
     worst = (0.0, None)
     for k, ids in reqs.items():
         for p in range(len(ids)):
@@ -63,7 +65,7 @@ def test_cut_matches_plain(replayed, cut):
 def test_cuts_agree_with_one_another(replayed):
     """The logits at a position do not depend on how the tokens were cut into steps, on what else
     was in the batch, or on which pages were used, beyond rounding."""
-    dtype, reqs, plain, rows, _ = replayed
+    dtype, reqs, plain, rows, *_ = replayed
     tol = 2e-5 if dtype == "float32" else 3e-2
     for k, ids in reqs.items():
         for p in range(len(ids)):
@@ -75,10 +77,13 @@ def test_cuts_agree_with_one_another(replayed):
 
 def test_mixed_trace_is_really_mixed(replayed):
     """The trace used above has steps with four live requests, prompt portions beside single tokens."""
-    *_, t = replayed
+    *_, t, name = replayed
     assert max(len(s["entries"]) for s in t.steps) == 4
     assert any(len({len(e["tokens"]) == 1 for e in s["entries"]}) == 2 for s in t.steps)
     assert any(len(e["tokens"]) == 2 for s in t.steps for e in s["entries"])
+    if name != "a":  # a portion of 32 tokens or more beside single tokens: what a scheduler's mixed steps look like
+        assert any(max(len(e["tokens"]) for e in s["entries"]) >= 32 and min(len(e["tokens"]) for e in s["entries"]) == 1
+                   for s in t.steps)
 
 
 def test_requests_that_start_after_others_ended_are_new_requests(tmp_path):

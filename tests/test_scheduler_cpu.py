@@ -198,3 +198,95 @@ def test_capacity_through_the_engine(engines):
         eng.forward_logits_paged(random_ids(5 * bs, cfg["vocab_size"], 1), bm)
     assert bm.free_blocks == 4
     eng.cm.check()
+
+
+def test_a_failed_step_ends_its_requests_with_error_and_the_others_go_on():
+    cm, s = core(pages=16, page=4, max_concurrent=2, max_prefill_tokens_per_step=8)
+    a = s.enqueue([1, 2, 3], 4)
+    b = s.enqueue([4, 5], 4)
+    c = s.enqueue([6], 2)  # waits: two may run at a time
+    e = s.plan()
+    assert e.ids() == [a, b]
+    with pytest.raises(RuntimeError, match="no planned step"):
+        core()[1].fail_step("error")
+    s.fail_step("error")  # the device said that the step's results are void
+    drain(s)
+    r = {x.seq_id: x for x in s.results}
+    assert r[a].finish_reason == "error" and list(r[a].token_ids) == [1, 2, 3]
+    assert r[b].finish_reason == "error" and r[c].finish_reason == "length" and len(r[c].token_ids) == 3
+    assert cm.free_pages() == 16 and cm.free_slots == 8
+    cm.check()
+
+
+def test_prompts_are_cut_at_multiples_of_what_the_model_asks_for():
+    """A mixer that carries its state over only at the edges of chunks of M tokens asks for portions
+    that end at multiples of M (parts.base.StateNeed.portion_multiple); the budget is then used up
+    to the last such position, the end of a prompt is always a legal cut, and decoding is untouched."""
+    cm, s = core(pages=64, page=4, max_concurrent=4, max_prefill_tokens_per_step=11, portion_multiple=4)
+    assert s.portion_multiple == 4
+    a = s.enqueue(list(range(23)), 2)
+    b = s.enqueue(list(range(6)), 2)
+    batches = drain(s)
+    cuts = {a: [], b: []}
+    for batch in batches:
+        for rid, toks, _ in batch:
+            if len(toks) > 1 or len(cuts[rid]) == 0 or sum(cuts[rid]) < (23 if rid == a else 6):
+                cuts[rid].append(len(toks))
+    # a: 8 (11 rounded down to a multiple of 4), 8, then its last 7; b gets what is left of each budget
+    assert cuts[a][:3] == [8, 8, 7] and sum(cuts[a][:3]) == 23
+    ends, pos = [], 0
+    for n in cuts[b]:
+        pos += n
+        ends.append(pos)
+        if pos == 6:
+            break
+    assert all(p % 4 == 0 or p == 6 for p in ends)
+    assert all(x.finish_reason == "length" for x in s.results)
+    with pytest.raises(ValueError, match="portion multiple"):
+        core(max_prefill_tokens_per_step=3, portion_multiple=4)
+    with pytest.raises(ValueError, match="portion multiple"):
+        s.budget = 2
+
+
+class _FailingOps(CpuOps):
+    """The test double, reporting a kernel that gave up a wait at a chosen step (no kernel has to)."""
+
+    ERROR_CODES = {22: "decoding attention: a tile never arrived"}
+
+    def __init__(self):
+        self.fail_at, self.checks = -1, 0
+
+    def queue_error_check(self):
+        self.checks += 1
+
+    def take_step_error(self):
+        return 22 if self.checks == self.fail_at else 0
+
+
+def test_a_kernel_that_gave_up_raises_and_the_engine_stays_usable(tmp_path):
+    d = str(tmp_path / "m")
+    make_model_dir(d, TINY_A, torch.float32)
+    pc, pw = P.read_model(d)
+    ops = _FailingOps()
+    eng = llmengine.Engine(d, "fp32", device="cpu", ops=ops, block_size=4, num_blocks=32)
+    sch = llmengine.ContinuousBatchScheduler(eng, None, max_concurrent=2, max_prefill_tokens_per_step=64)
+    p1, p2, p3 = (random_ids(n, 256, 70 + n) for n in (5, 7, 6))
+    sch.enqueue(p1, 3)
+    sch.enqueue(p2, 3)
+    sch.enqueue(p3, 3)
+    sch.step()
+    ops.fail_at = ops.checks + 1  # the next step's kernels "give up"
+    with pytest.raises(llmengine.KernelError, match="code 22.*a tile never arrived"):
+        sch.step()
+    sch.run_until_idle()
+    r = sch.results
+    assert [x.finish_reason for x in r] == ["error", "error", "length"]
+    assert list(r[2].token_ids) == P.generate(pc, pw, p3, 3)[0]  # the request that was not in the failed step
+    assert len(r[0].token_ids) == len(p1) + 1  # what was generated before the failure is kept
+    eng.cm.check()
+    assert eng.cm.free_pages(0) == 32 and eng.cm.free_slots == eng.cm.num_slots
+    # the same through run_step: the error surfaces, fresh requests give their pages back
+    ops.fail_at = ops.checks + 1
+    with pytest.raises(llmengine.KernelError):
+        eng.run_step([(5, p1, [0])])
+    assert eng.cm.free_pages(0) == 32

@@ -80,6 +80,25 @@ class Trace:
         if rows:
             self.rows[k] = rows
 
+    def keep_only(self, wanted) -> "Trace":
+        """Asks only for the logits at the positions wanted(request name) -> set of positions (for
+        models whose head is too large to compare at every position)."""
+        self.rows = {}
+        pos: Dict[str, int] = {}
+        for k, s in enumerate(self.steps):
+            rows = []
+            for e in s["entries"]:
+                start = pos.get(e["id"], 0)
+                keep = wanted(e["id"])
+                e["want"] = [w for w in range(len(e["tokens"])) if start + w in keep]
+                rows += [(e["id"], start + w) for w in e["want"]]
+                pos[e["id"]] = start + len(e["tokens"])
+            for name in s["end"]:
+                pos.pop(name, None)
+            if rows:
+                self.rows[k] = rows
+        return self
+
     def extend(self, other: "Trace") -> None:
         off = len(self.steps)
         for s in other.steps:
@@ -126,10 +145,17 @@ def trace_portions(reqs: Dict[str, List[int]], sizes=(7, 2, 13, 2, 5, 3, 16, 2, 
     return t
 
 
-def trace_mixed(reqs: Dict[str, List[int]], max_tokens: int, seed: int = 0, max_live: int = 4) -> Trace:
-    """Up to `max_live` live requests; portions of some beside single (decoded) tokens of others;
-    a request starts only when the pool (max_tokens, each request rounded up to 64) has room, so
-    later requests reuse the pages of finished ones."""
+MIXED_SIZES = (2, 3, 5, 8, 13, 21)
+# ... and portions long enough for the kernels that serve a scheduler's real mixed steps (a long
+# prompt portion beside single decoded tokens): tensor-core attention of portions, token-tile products
+MIXED_SIZES_LONG = MIXED_SIZES + (40, 70, 130)
+
+
+def trace_mixed(reqs: Dict[str, List[int]], max_tokens: int, seed: int = 0, max_live: int = 4,
+                sizes: Sequence[int] = MIXED_SIZES) -> Trace:
+    """Up to `max_live` live requests; portions of some (of the given sizes) beside single (decoded)
+    tokens of others; a request starts only when the pool (max_tokens, each request rounded up to
+    64) has room, so later requests reuse the pages of finished ones."""
     rng = np.random.default_rng(seed)
     t = Trace()
     waiting = list(reqs.items())
@@ -150,7 +176,7 @@ def trace_mixed(reqs: Dict[str, List[int]], max_tokens: int, seed: int = 0, max_
                 continue  # a request may sit out a step
             ids, p = st["ids"], st["pos"]
             if p < st["prompt"]:
-                n = int(min(rng.choice([2, 3, 5, 8, 13, 21]), st["prompt"] - p))
+                n = int(min(rng.choice(list(sizes)), st["prompt"] - p))
                 if st["prompt"] - p - n == 1:
                     n += 1
             else:
