@@ -12,16 +12,12 @@ Keys and defaults follow the reference's load_config (src/weights.cpp:55-121) an
 """
 from __future__ import annotations
 
-import json
-import os
 from dataclasses import dataclass, field
 from typing import Any, Dict, FrozenSet, Optional
 
 import numpy as np
 
-
-class ConfigError(ValueError):
-    """config.json is missing a key, or its values do not fit together."""
+from .files import ConfigError
 
 
 def _f32(x) -> float:
@@ -209,19 +205,3 @@ class LlamaConfig:
         if self.eos_token_ids:
             d["eos_token_id"] = sorted(self.eos_token_ids)
         return d
-
-
-def read_config_json(model_dir: str) -> Dict[str, Any]:
-    path = os.path.join(model_dir, "config.json")
-    if not os.path.isfile(path):
-        raise ConfigError(f"no config.json in {model_dir}")
-    with open(path) as f:
-        return json.load(f)
-
-
-def read_generation_config_json(model_dir: str) -> Optional[Dict[str, Any]]:
-    path = os.path.join(model_dir, "generation_config.json")
-    if not os.path.isfile(path):
-        return None
-    with open(path) as f:
-        return json.load(f)

@@ -9,7 +9,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any, Callable, Dict, List, Optional
 
-from .llama import ConfigError, read_config_json, read_generation_config_json
+from .files import ConfigError, read_config_json, read_generation_config_json
 
 
 @dataclass(frozen=True)

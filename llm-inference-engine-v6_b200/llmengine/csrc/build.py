@@ -37,7 +37,7 @@ CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wex
 # tcgen05/TMA kernels that only the bfloat16 path uses.
 KERNEL_LIBRARIES: Dict[str, List[str]] = {
     "core": ["status.cu", "elementwise.cu", "gemm_simt.cu", "rope_kv.cu", "attention_simt.cu", "sampling.cu"],
-    "tensorcore": ["status.cu", "gemm_tc.cu", "attention_mma.cu", "attention_tc.cu", "attention_decode.cu"],
+    "tensorcore": ["status.cu", "gemm_tc.cu", "gemm_decode.cu", "attention_mma.cu", "attention_tc.cu", "attention_decode.cu"],
 }
 HOST_SOURCES = ["cache_manager.cpp", "scheduler.cpp", "bindings.cpp"]
 

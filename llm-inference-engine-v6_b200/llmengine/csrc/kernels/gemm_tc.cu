@@ -60,20 +60,6 @@ struct TileWalk {
   }
 };
 
-// Stage and phase of a ring, stepped without a division.
-struct RingPos {
-  int s;
-  uint32_t ph;
-  int stages;
-  __device__ __forceinline__ RingPos(int stages_, int s_ = 0, uint32_t ph_ = 0) : s(s_), ph(ph_), stages(stages_) {}
-  __device__ __forceinline__ void next() {
-    if (++s == stages) {
-      s = 0;
-      ph ^= 1u;
-    }
-  }
-};
-
 template <typename TO>
 __device__ __forceinline__ void store_row16(TO* dst, const float* v, int valid, bool aligned);
 

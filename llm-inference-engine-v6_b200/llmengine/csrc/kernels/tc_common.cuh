@@ -50,25 +50,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait. Returns false if the phase did not complete in time or another role aborted. Once
-// any kernel of the process has recorded an error, later waits that do not complete within a few
-// hundred polls give up at once instead of after a second each: everything computed since that
-// error is void anyway (the host raises when it reads the word), and a fault that repeats in every
-// launch then costs microseconds, not seconds, per launch.
+// any kernel of the process has recorded an error, a wait that has lasted longer than any wait of
+// a healthy kernel (RECHECK_CYCLES) gives up instead of waiting out its full second: everything
+// computed since that error is void anyway (the host raises when it reads the word), and a fault
+// that repeats in every launch then costs tens of microseconds, not seconds, per launch. The word
+// lives in global memory, so it is looked at only that rarely: a load of it stalls the polling
+// thread for a microsecond, which the roles of a pipeline cannot spare in every wait.
+constexpr long long RECHECK_CYCLES = 100000;  // about 50 us
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* error_out, int code) {
   if (mbar_try_wait(bar, parity)) return true;  // the usual case costs one instruction
   const long long t0 = clock64();
+  long long next_check = t0 + RECHECK_CYCLES;
   for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 255u) == 255u) {
       if (*abort_flag) return false;
-      if (*reinterpret_cast<volatile int*>(error_out) != 0) {
-        *abort_flag = code;
-        return false;
-      }
-      if (clock64() - t0 > WAIT_CYCLES) {
-        *abort_flag = code;
-        atomicCAS(error_out, 0, code);
-        return false;
+      const long long now = clock64();
+      if (now > next_check) {
+        next_check = now + RECHECK_CYCLES;
+        if (*reinterpret_cast<volatile int*>(error_out) != 0) {
+          *abort_flag = code;
+          return false;
+        }
+        if (now - t0 > WAIT_CYCLES) {
+          *abort_flag = code;
+          atomicCAS(error_out, 0, code);
+          return false;
+        }
       }
     }
   }
@@ -138,6 +146,20 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, float* v) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
+
+// Stage and phase of a ring, stepped without a division.
+struct RingPos {
+  int s;
+  uint32_t ph;
+  int stages;
+  __device__ __forceinline__ RingPos(int stages_, int s_ = 0, uint32_t ph_ = 0) : s(s_), ph(ph_), stages(stages_) {}
+  __device__ __forceinline__ void next() {
+    if (++s == stages) {
+      s = 0;
+      ph ^= 1u;
+    }
+  }
+};
 
 // ------------------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,

@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import tempfile
 import threading
+import warnings
 from typing import Iterable, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -140,6 +141,10 @@ class Engine:
             model = Model(self.spec, env)
             model.load(self.model_dir)
             self.model = model
+            if self.cuda_graphs and not model.capturable:
+                self.cuda_graphs = False  # a part waits for the device inside its forward: steps stay eager
+            for line in model.kernel_notes():
+                warnings.warn(line, stacklevel=2)
         return self.model
 
     def _default_blocks(self, model: Model, block_size: int) -> int:

@@ -23,10 +23,10 @@ from ..weights.random_init import model_tensor_needs
 class Model:
     def __init__(self, spec: ModelSpec, env: BuildEnv):
         self.spec, self.env = spec, env
+        self.embedding = build_part("embedding", spec.embedding, env)
         self.blocks = [build_part("block", b, env) for b in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, env)
-        self.embedding: Optional[torch.Tensor] = None
-        self.head: Optional[torch.Tensor] = None
+        self.head = build_part("head", spec.head, env)
         n_runs = len(spec.order)
         for r, run in enumerate(spec.order):
             if not (0 <= run.layer < len(self.blocks)):
@@ -54,12 +54,10 @@ class Model:
     # ------------------------------------------------------------------ weights
     def load(self, model_dir: str) -> None:
         needs = model_tensor_needs(self.spec)
-        tensors = load_tensors(Checkpoint(model_dir), needs, self.spec.duplicates, self.env.device, self.env.dtype)
-        self.embedding = tensors[self.spec.embedding.weight]
-        self.head = tensors[self.spec.head.weight]
-        for b in self.blocks:
-            b.load(tensors)
-        self.final_norm.load(tensors)
+        tensors = load_tensors(Checkpoint(model_dir), needs, self.spec.duplicates, self.env.device, self.env.dtype,
+                               ignore=self.spec.ignore)
+        for part in (self.embedding, *self.blocks, self.final_norm, self.head):
+            part.load(tensors)
         self.weight_bytes = sum(t.numel() * t.element_size() for t in tensors.values())
         self.tensor_names = sorted(tensors)
 
@@ -86,16 +84,37 @@ class Model:
                     t[slot].zero_()
 
     # ------------------------------------------------------------------ forward
+    def parts(self):
+        """Every part of the model, the parts of parts included."""
+        todo = [self.embedding, *self.blocks, self.final_norm, self.head]
+        while todo:
+            part = todo.pop()
+            yield part
+            todo.extend(part.subparts())
+
+    @property
+    def capturable(self) -> bool:
+        """Whether a decode step of this model may be recorded as a CUDA graph: every part says so."""
+        return all(p.capturable for p in self.parts())
+
+    def kernel_notes(self) -> List[str]:
+        seen, out = set(), []
+        for p in self.parts():
+            for line in p.kernel_notes():
+                if line not in seen:
+                    seen.add(line)
+                    out.append(line)
+        return sorted(out)
+
     def forward(self, ctx) -> torch.Tensor:
-        ops, n = self.env.ops, ctx.n_tokens
-        H, V = self.spec.hidden_size, self.spec.vocab_size
-        h = ctx.ws.get("model.residual", (n, H), torch.float32)
-        ops.embed(self.embedding, ctx.token_ids, h)
-        res = Residual(h)
+        res = Residual(self.embedding.forward(ctx))
         for r, run in enumerate(self.spec.order):
             res = self.blocks[run.layer].forward(res, ctx, self.caches[r])
-        logits = ctx.ws.get("model.logits", (max(ctx.n_rows, 1), V), torch.float32)[:ctx.n_rows]
         if ctx.n_rows > 0:
-            x = self.final_norm.forward(res, ctx, rows=ctx.logit_rows, n_rows=ctx.n_rows)
-            ops.gemm(x, self.head, logits)
-        return logits
+            if self.final_norm.can_defer and self.head.wants_lazy_norm(ctx):
+                x = self.final_norm.forward(res, ctx, rows=ctx.logit_rows, n_rows=ctx.n_rows, lazy=True)
+            else:
+                x = self.final_norm.forward(res, ctx, rows=ctx.logit_rows, n_rows=ctx.n_rows)
+        else:
+            x = ctx.ws.get("norm.rows_out", (1, self.spec.hidden_size), self.env.dtype)[:0]
+        return self.head.forward(x, ctx)

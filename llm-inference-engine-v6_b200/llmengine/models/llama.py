@@ -49,6 +49,8 @@ def describe_llama(cfg: LlamaConfig) -> ModelSpec:
         max_positions=cfg.max_position_embeddings,
         eos_token_ids=cfg.eos_token_ids,
         duplicates={"lm_head.weight": embed_name} if tied else {},
+        # buffers that exporters of this architecture save beside the weights and nobody reads
+        ignore=("*.rotary_emb.inv_freq",),
     )
 
 

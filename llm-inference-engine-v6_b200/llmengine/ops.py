@@ -58,6 +58,8 @@ class CudaOps:
         self.tcgen05_attention = True  # prompt portions: attention on tcgen05 where the geometry allows it
         self.tma_decode_attention = True  # single decoded tokens: keys and values by TMA where the geometry allows it
         self.fused_decode_attention = True  # ... with the sum of the q|k|v parts, rotation and cache write in the same kernel
+        self.few_token_products = True  # steps of few tokens: products that add their K pieces inside a cluster, norms and activation folded in
+        self._few_cache = {}
         self._err_host: Optional[torch.Tensor] = None  # pinned word that queue_error_check copies the kernels' error code into
 
     # ------------------------------------------------------------------ loading
@@ -257,6 +259,77 @@ class CudaOps:
         parts = ws.get(tag, (1, M, N), torch.float32)
         self.gemm(a, w, parts[0])
         return parts
+
+    # ------------------------------------------------------------------ products of a step with few tokens
+    FEW_TOKENS = 64  # up to here the weights fill the accumulator lanes and the kernel below applies
+    FEW_TOKENS_TARGET_CTAS = 296  # K pieces are chosen so that about this many CTAs stream the weights
+
+    def few_token_splits(self, n: int, k: int, t: int, mode: str) -> int:
+        """K pieces (CTAs of the cluster that adds them up) that gemm_few_tokens will use: 0 if the
+        kernel does not take these sizes. mode: "plain", "residual" or "swiglu" (n counts gate and up rows)."""
+        if not self.tensor_cores or not self.few_token_products or not (1 <= t <= self.FEW_TOKENS) or k % 8:
+            return 0
+        key = (n, k, t, mode)
+        hit = self._few_cache.get(key)
+        if hit is None:
+            hit = self._few_cache[key] = self._few_token_splits(n, k, t, mode)
+        return hit
+
+    def _few_token_splits(self, n: int, k: int, t: int, mode: str) -> int:
+        tiles = -(-n // (256 if mode == "swiglu" else 128))
+        target = self.FEW_TOKENS_TARGET_CTAS if t <= 32 else self.FEW_TOKENS_TARGET_CTAS // 2
+        want = max(1, min(16, -(-target // tiles), max(1, -(-k // 64) // 2)))
+        if mode == "residual":
+            want = max(want, 2)
+        return int(self.lib("tensorcore").llm_gemm_decode_splits(c_int(n), c_int(k), c_int(t), c_int(self._FEW_MODES[mode]), c_int(want)))
+
+    _FEW_MODES = {"plain": 0, "residual": 1, "swiglu": 2}
+
+    def gemm_few_tokens(self, w: torch.Tensor, out: torch.Tensor, mode: str = "plain", x: Optional[torch.Tensor] = None,
+                        norm=None, sumsq_out: Optional[torch.Tensor] = None, n_tokens: Optional[int] = None) -> torch.Tensor:
+        """out <- x . w^T for at most FEW_TOKENS tokens, with the K pieces added inside a thread-block
+        cluster (no partial sums in memory) and the work around the product folded in.
+        Activations: `x` bf16 [t, k]; or `norm` = (h float32 [rows, k], sumsq float32 [rows, parts], weight
+        float32 [k], eps, row list int32 [t] or None): the RMSNorm of those rows, which then is no
+        kernel of its own.
+        mode "plain": out [t, n] float32 or bf16. "residual": out is the float32 residual stream
+        [t, n], the product is added to it in place, and sumsq_out [t, parts] receives the parts of
+        the new rows' sums of squares (parts = sumsq_out.shape[1], as residual_sumsq_parts says).
+        "swiglu": w holds blocks of 128 gate rows and the 128 matching up rows, out bf16 [t, n / 2]."""
+        _need(w, "gemm_few.w", torch.bfloat16); _need(out, "gemm_few.out")
+        n, k = w.shape
+        lib = self.lib("tensorcore")
+        if x is not None:
+            _need(x, "gemm_few.x", torch.bfloat16)
+            t = x.shape[0] if n_tokens is None else n_tokens
+            assert x.shape[1] == k
+            xb, xf, ldx, ss, nss, nw, eps, rows = _ptr(x), c_void_p(0), x.stride(0), c_void_p(0), 0, c_void_p(0), 0.0, c_void_p(0)
+        else:
+            h, sumsq, weight, eps, row_list = norm
+            _need(h, "gemm_few.h", torch.float32); _need(sumsq, "gemm_few.sumsq", torch.float32); _need(weight, "gemm_few.norm_weight", torch.float32)
+            assert h.shape[1] == k and weight.numel() == k and sumsq.dim() == 2 and sumsq.is_contiguous() and sumsq.shape[0] >= h.shape[0]
+            t = (row_list.numel() if row_list is not None else h.shape[0]) if n_tokens is None else n_tokens
+            if row_list is not None:
+                _need(row_list, "gemm_few.rows", torch.int32)
+            xb, xf, ldx, ss, nss, nw, rows = c_void_p(0), _ptr(h), h.stride(0), _ptr(sumsq), sumsq.shape[1], _ptr(weight), _ptr(row_list)
+        assert out.shape[0] >= t and out.shape[1] == (n // 2 if mode == "swiglu" else n)
+        splits = self.few_token_splits(n, k, t, mode)
+        if splits == 0:
+            raise KernelError(f"gemm_few_tokens: sizes not taken (tokens={t} n={n} k={k} mode={mode})")
+        nso = 0
+        if mode == "residual":
+            _need(sumsq_out, "gemm_few.sumsq_out", torch.float32)
+            assert sumsq_out.is_contiguous() and sumsq_out.shape[0] >= t
+            nso = sumsq_out.shape[1]
+        self._check(lib.llm_gemm_decode(_ptr(w), c_longlong(w.stride(0)), c_int(n), c_int(k), c_int(t), xb, xf, c_longlong(ldx), ss,
+                                        c_int(nss), nw, c_float(eps), rows, c_int(self._FEW_MODES[mode]), _ptr(out),
+                                        c_longlong(out.stride(0)), c_int(dtype_code(out.dtype)), _ptr(sumsq_out), c_int(nso),
+                                        c_int(splits), _stream()), lib)
+        return out
+
+    def residual_sumsq_parts(self, n: int, k: int, t: int) -> int:
+        """Parts of a row's sum of squares that gemm_few_tokens(mode="residual") writes for these sizes."""
+        return -(-n // 128) * self.few_token_splits(n, k, t, "residual")
 
     def reduce_partials(self, parts: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """out = sum over parts[p] (index order); out float32 or bfloat16, contiguous."""
@@ -492,6 +565,22 @@ class CudaOps:
                                                  c_longlong(out.stride(0)), c_int(n_tokens), c_int(nq), c_int(nkv),
                                                  c_int(hd), c_int(page), c_float(scale), c_int(window), _stream()), lib)
         return out
+
+    def attention_kernels(self, nq: int, nkv: int, hd: int, page: int):
+        """-> (what prompt portions of 32 tokens or more run on, what single decoded tokens run on) for
+        a bfloat16 model of this geometry: "tensor cores" (tcgen05 for portions; TMA-fed mma.sync for
+        decoding), "tensor cores (mma.sync, the general kernel)" or "CUDA cores"."""
+        lib = self.lib("tensorcore")
+        ld = nq * hd
+        general = bool(lib.llm_attention_mma_supported(c_int(nq), c_int(nkv), c_int(hd), c_longlong(ld), c_longlong(ld)))
+        fallback = "tensor cores (mma.sync, the general kernel)" if general else "CUDA cores"
+        prompt = "tensor cores" if self.tcgen05_attention and lib.llm_attention_tc_supported(
+            c_int(nq), c_int(nkv), c_int(hd), c_int(page), c_longlong(ld), c_longlong(ld)) else fallback
+        decode = "tensor cores" if self.tma_decode_attention and lib.llm_attention_decode_supported(
+            c_int(nq), c_int(nkv), c_int(hd), c_int(page), c_longlong(ld), c_longlong(ld)) else fallback
+        if not self.tensor_cores:
+            prompt = decode = "CUDA cores"
+        return prompt, decode
 
     # ------------------------------------------------------------------ sampling
     def sample_scratch_words(self, n_rows: int, vocab: int) -> int:

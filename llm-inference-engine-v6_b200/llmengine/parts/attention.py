@@ -9,11 +9,11 @@ projection (src/engine.cpp:364-379). The residual sum is left to the caller.
 from __future__ import annotations
 
 import math
-from typing import List
+from typing import List, Optional
 
 import torch
 
-from .base import KVNeed, LayerCache, Mixer
+from .base import KVNeed, LayerCache, Mixer, NormalizedRows
 from .registry import build_part, part_class, register_part
 from .spec import AttentionSpec, TensorNeed
 
@@ -37,8 +37,24 @@ class PagedAttention(Mixer):
                 TensorNeed(spec.v_weight, (dkv, spec.hidden)), TensorNeed(spec.o_weight, (spec.hidden, dq))] + \
             list(part_class("position", spec.position.kind).tensor_needs(spec.position))
 
+    def subparts(self):
+        return (self.position,)
+
     def cache_needs(self):
         return (KVNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window),)
+
+    def kernel_notes(self):
+        s, notes = self.spec, []
+        if self.env.dtype == torch.bfloat16 and hasattr(self.env.ops, "attention_kernels"):
+            prompt, decode = self.env.ops.attention_kernels(s.num_heads, s.num_kv_heads, s.head_dim, self.env.page_size)
+            for what, kernel in (("prompt portions", prompt), ("single decoded tokens", decode)):
+                if kernel != "tensor cores":
+                    notes.append(f"attention with head size {s.head_dim}, {s.num_heads // s.num_kv_heads} query heads a key/value "
+                                 f"head and pages of {self.env.page_size}: {what} run on {kernel}")
+            for name, k in (("q|k|v", s.hidden), ("o", s.num_heads * s.head_dim)):
+                if k % 8:
+                    notes.append(f"attention: the {name} product sums over {k} inputs, no multiple of 8: it runs on CUDA cores")
+        return notes
 
     def load(self, tensors) -> None:
         s = self.spec
@@ -46,28 +62,75 @@ class PagedAttention(Mixer):
         self.w_o = tensors[s.o_weight]
         self.position.load(tensors)
 
-    def forward(self, x: torch.Tensor, ctx, cache: LayerCache) -> torch.Tensor:
+    def _few_tokens(self, ctx) -> bool:
+        """The step has few enough tokens for the products that add their K pieces inside a cluster and
+        take the work around them in (ops.gemm_few_tokens)."""
+        s, ops, n = self.spec, self.env.ops, ctx.n_tokens
+        return (self.env.dtype == torch.bfloat16 and hasattr(ops, "gemm_few_tokens") and
+                ops.few_token_splits(self.w_qkv.shape[0], s.hidden, n, "plain") > 0 and
+                ops.few_token_splits(s.hidden, s.num_heads * s.head_dim, n, "residual") > 0)
+
+    def wants_lazy_norm(self, ctx) -> bool:
+        return self._few_tokens(ctx) and self.position.takes_partial_sums
+
+    def forward(self, x, ctx, cache: LayerCache) -> Optional[torch.Tensor]:
         s, ops, n = self.spec, self.env.ops, ctx.n_tokens
         dq, dkv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
         qkv = ctx.ws.get("attention.qkv", (n, dq + 2 * dkv), self.env.dtype)
         att = ctx.ws.get("attention.out", (n, dq), self.env.dtype)
+        few = self._few_tokens(ctx)
+        if isinstance(x, NormalizedRows) and not (few and cache.writes and self.position.takes_partial_sums):
+            x = x.dense(ctx)
         if n <= 64 and cache.writes and self.position.takes_partial_sums:
-            # few tokens: the product comes as K-split partial sums, added by the position kernel
-            parts = ops.gemm_partials(x[:n], self.w_qkv, ctx.ws, "attention.qkv_parts")
+            # few tokens: the product comes as float32 sums (in parts, unless the K pieces were added
+            # inside the product), finished by the position kernel or by the attention kernel
+            if few:
+                parts = ctx.ws.get("attention.qkv_parts", (1, n, dq + 2 * dkv), torch.float32)
+                if isinstance(x, NormalizedRows):
+                    ops.gemm_few_tokens(self.w_qkv, parts[0], "plain", norm=(x.h, x.sumsq, x.weight, x.eps, x.rows), n_tokens=n)
+                else:
+                    ops.gemm_few_tokens(self.w_qkv, parts[0], "plain", x=x[:n])
+            else:
+                parts = ops.gemm_partials(x[:n], self.w_qkv, ctx.ws, "attention.qkv_parts")
             tables = self.position.rotation_tables() if cache.k is not None else None
             if tables is not None and ops.decode_attention_fusable(ctx, cache.k, s.num_heads, s.num_kv_heads, s.head_dim, att):
                 # single decoded tokens: summing the parts, rotation and the cache write happen inside the attention kernel
                 ops.paged_attention_decode_fused(parts, tables[0], tables[1], cache.k, cache.v, ctx,
                                                  ctx.block_tables[cache.group], att, s.num_heads, s.num_kv_heads,
                                                  s.head_dim, self.scale, s.window)
-                return ops.gemm_partials(att, self.w_o, ctx.ws, "attention.delta")
+                return self._output(att, ctx, few)
             self.position.rotate_and_store(qkv, ctx, cache, s.num_heads, s.num_kv_heads, s.head_dim, parts=parts)
         else:
             ops.gemm(x[:n], self.w_qkv, qkv, ctx.ws)
             self.position.rotate_and_store(qkv, ctx, cache, s.num_heads, s.num_kv_heads, s.head_dim)
         ops.paged_attention(qkv[:, :dq], cache.k, cache.v, ctx, ctx.block_tables[cache.group], att, s.num_heads,
                             s.num_kv_heads, s.head_dim, self.scale, s.window)
-        return ops.gemm_partials(att, self.w_o, ctx.ws, "attention.delta")
+        return self._output(att, ctx, few)
+
+    def _output(self, att: torch.Tensor, ctx, few: bool) -> Optional[torch.Tensor]:
+        """The output projection: added into the residual stream by the product itself where that
+        applies (returns None), else float32 partial sums for the next norm to add."""
+        return add_into_stream_or_partials(self.env.ops, att, self.w_o, ctx, few, "attention.delta")
+
+
+def add_into_stream_or_partials(ops, x: torch.Tensor, w: torch.Tensor, ctx, few: bool, tag: str) -> Optional[torch.Tensor]:
+    """A sub-layer's last product x . w^T. With few tokens, and a residual stream to work for, the
+    product adds itself into the stream and leaves the parts of the rows' sums of squares there
+    (so that the next norm need not run); otherwise it returns float32 partial sums."""
+    res, n = ctx.residual, ctx.n_tokens
+    if few and res is not None and res.pending is None and res.h.shape[1] == w.shape[0]:
+        parts = ops.residual_sumsq_parts(w.shape[0], w.shape[1], n)
+        ss = ctx.ws.get(tag + ".sumsq", (res.h.shape[0], parts), torch.float32)
+        ops.gemm_few_tokens(w, res.h, "residual", x=x[:n], sumsq_out=ss, n_tokens=n)
+        res.sumsq = ss
+        return None
+    res_sumsq_off(res)
+    return ops.gemm_partials(x, w, ctx.ws, tag)
+
+
+def res_sumsq_off(res) -> None:
+    if res is not None:
+        res.sumsq = None  # a delta is on its way: the sums of squares no longer describe the stream
 
 
 register_part("mixer", "attention", PagedAttention)

@@ -64,19 +64,61 @@ class LayerCache:
 class Residual:
     """The float32 residual stream h [tokens, hidden] and a float32 delta that has not been added
     yet ([tokens, hidden], or [parts, tokens, hidden] to be summed in index order). The next norm
-    adds it while it reads h, which saves one pass over the stream."""
+    adds it while it reads h, which saves one pass over the stream.
+
+    A part whose last product can add into the stream itself (ctx.residual is the stream it works
+    for) returns None instead of a delta and may leave `sumsq`: float32 [tokens, parts], the parts
+    of every row's sum of squares as the stream stands now. With them a norm need not run as a
+    kernel of its own: it hands NormalizedRows to a consumer that folds it into its first product."""
 
     def __init__(self, h: torch.Tensor):
         self.h = h
         self.pending: Optional[torch.Tensor] = None
+        self.sumsq: Optional[torch.Tensor] = None  # valid only while pending is None and h is untouched since
+
+
+@dataclass
+class NormalizedRows:
+    """What a norm hands on without having run: rows of the float32 stream, the parts of their sums
+    of squares, its weight and eps; `rows` (int32) picks rows, `n` is how many. A consumer that
+    takes it (wants_lazy_norm) computes (weight * x) / rms(x) itself; dense() runs the norm's kernel."""
+    h: torch.Tensor
+    sumsq: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+    rows: Optional[torch.Tensor]
+    n: int
+    norm: "Norm"
+
+    def dense(self, ctx) -> torch.Tensor:
+        return self.norm.run(self.h, ctx, self.rows, self.n)
 
 
 class Part:
     category = ""
+    # False for a part whose forward waits for the device or sizes its work from device data (a
+    # .tolist(), a .nonzero()): such a step cannot be recorded as a CUDA graph, and the engine then
+    # runs the model's decode steps kernel by kernel. Parts made of kernels on fixed shapes leave it True.
+    capturable = True
 
     def __init__(self, spec, env: BuildEnv):
         self.spec = spec
         self.env = env
+
+    def subparts(self) -> Sequence["Part"]:
+        """The parts this one is made of (a block's norms, mixer and feed-forward; a mixer's position
+        encoding), so that questions asked of a model reach every part."""
+        return ()
+
+    def wants_lazy_norm(self, ctx) -> bool:
+        """True if, in this step, the part takes NormalizedRows in place of normalised activations."""
+        return False
+
+    def kernel_notes(self) -> List[str]:
+        """One line for each thing a user should know about how this part will run at the engine's
+        precision, e.g. that its sizes leave the tensor-core kernels out; shown once when the
+        model is loaded."""
+        return []
 
     @staticmethod
     def tensor_needs(spec) -> List[TensorNeed]:
@@ -86,12 +128,31 @@ class Part:
         """Receives every tensor it asked for, on the device, in the asked precision."""
 
 
+class Embedding(Part):
+    category = "embedding"
+
+    def forward(self, ctx) -> torch.Tensor:
+        """The float32 residual stream [tokens, hidden] of the step's tokens (ctx.token_ids)."""
+        raise NotImplementedError
+
+
+class Head(Part):
+    category = "head"
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        """x: the wanted rows after the final norm [rows, hidden] (engine dtype). Returns float32
+        logits [rows, vocab]."""
+        raise NotImplementedError
+
+
 class Norm(Part):
     category = "norm"
+    can_defer = False  # True: forward(..., lazy=True) may return NormalizedRows
 
     def forward(self, res: Residual, ctx, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> torch.Tensor:
         """Adds res.pending into res.h (when `rows` is None) and returns the normalised rows in the
-        engine dtype. With `rows`, only those source rows are normalised and res is left alone."""
+        engine dtype. With `rows`, only those source rows are normalised and res is left alone.
+        Norms with can_defer take `lazy=True` as well (asked for only when the consumer wants it)."""
         raise NotImplementedError
 
 

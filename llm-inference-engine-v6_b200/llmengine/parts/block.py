@@ -25,6 +25,9 @@ class PreNormBlock(Block):
             out += part_class(cat, sub.kind).tensor_needs(sub)
         return out
 
+    def subparts(self):
+        return (self.norm1, self.mixer, self.norm2, self.feed_forward)
+
     def cache_needs(self):
         return self.mixer.cache_needs()
 
@@ -33,11 +36,19 @@ class PreNormBlock(Block):
             p.load(tensors)
 
     def forward(self, res: Residual, ctx, cache: LayerCache) -> Residual:
-        x = self.norm1.forward(res, ctx)
+        ctx.residual = res  # a part whose last product can add into the stream itself returns None
+        x = self._norm(self.norm1, self.mixer, res, ctx)
         res.pending = self.mixer.forward(x, ctx, cache)
-        x = self.norm2.forward(res, ctx)
+        x = self._norm(self.norm2, self.feed_forward, res, ctx)
         res.pending = self.feed_forward.forward(x, ctx)
+        ctx.residual = None
         return res
+
+    @staticmethod
+    def _norm(norm, consumer, res: Residual, ctx):
+        if norm.can_defer and consumer.wants_lazy_norm(ctx):
+            return norm.forward(res, ctx, lazy=True)
+        return norm.forward(res, ctx)
 
 
 register_part("block", "pre_norm", PreNormBlock)

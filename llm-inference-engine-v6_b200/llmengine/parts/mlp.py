@@ -5,11 +5,12 @@ put together: [Wg; Wu], or, in bfloat16 when the intermediate size is a multiple
 tensor-core product holds both and the activation is applied in its epilogue."""
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import torch
 
-from .base import FeedForward
+from .attention import add_into_stream_or_partials, res_sumsq_off
+from .base import FeedForward, NormalizedRows
 from .registry import register_part
 from .spec import GatedMLPSpec, TensorNeed
 
@@ -28,6 +29,17 @@ class GatedMLP(FeedForward):
                 TensorNeed(spec.up_weight, (spec.intermediate, spec.hidden)),
                 TensorNeed(spec.down_weight, (spec.hidden, spec.intermediate))]
 
+    def kernel_notes(self):
+        s, notes = self.spec, []
+        if self.env.dtype == torch.bfloat16:
+            for name, k in (("gate|up", s.hidden), ("down", s.intermediate)):
+                if k % 8:
+                    notes.append(f"feed-forward: the {name} product sums over {k} inputs, no multiple of 8: it runs on CUDA cores")
+            if s.intermediate % 128:
+                notes.append(f"feed-forward: an intermediate size of {s.intermediate} is no multiple of 128: the activation is a "
+                             "kernel of its own instead of the gate|up product's epilogue")
+        return notes
+
     def load(self, tensors) -> None:
         s = self.spec
         g, u = tensors[s.gate_weight], tensors[s.up_weight]
@@ -38,9 +50,29 @@ class GatedMLP(FeedForward):
             self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         self.w_down = tensors[s.down_weight]
 
-    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    def _few_tokens(self, ctx) -> bool:
+        s, ops, n = self.spec, self.env.ops, ctx.n_tokens
+        return (self.blocked and hasattr(ops, "gemm_few_tokens") and
+                ops.few_token_splits(2 * s.intermediate, s.hidden, n, "swiglu") > 0 and
+                ops.few_token_splits(s.hidden, s.intermediate, n, "residual") > 0)
+
+    def wants_lazy_norm(self, ctx) -> bool:
+        return self._few_tokens(ctx)
+
+    def forward(self, x, ctx) -> Optional[torch.Tensor]:
         s, ops, n = self.spec, self.env.ops, ctx.n_tokens
         act = ctx.ws.get("mlp.act", (n, s.intermediate), self.env.dtype)
+        if self._few_tokens(ctx):
+            # few tokens: the norm before (if it was handed on), the sum of the K pieces and SiLU * up all
+            # happen inside the gate|up product; the down product adds itself into the residual stream
+            if isinstance(x, NormalizedRows):
+                ops.gemm_few_tokens(self.w_gate_up, act, "swiglu", norm=(x.h, x.sumsq, x.weight, x.eps, x.rows), n_tokens=n)
+            else:
+                ops.gemm_few_tokens(self.w_gate_up, act, "swiglu", x=x[:n])
+            return add_into_stream_or_partials(ops, act, self.w_down, ctx, True, "mlp.delta")
+        if isinstance(x, NormalizedRows):
+            x = x.dense(ctx)
+        res_sumsq_off(ctx.residual)
         if self.blocked:
             ops.gemm_swiglu(x[:n], self.w_gate_up, act, ctx.ws)
         elif n <= 64:  # few tokens: the products may come as partial sums, added by their consumers

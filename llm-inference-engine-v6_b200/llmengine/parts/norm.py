@@ -6,7 +6,7 @@ from typing import List, Optional
 
 import torch
 
-from .base import Norm, Residual
+from .base import Norm, NormalizedRows, Residual
 from .registry import register_part
 from .spec import NormSpec, TensorNeed
 
@@ -18,17 +18,31 @@ class RMSNorm(Norm):
 
     @staticmethod
     def tensor_needs(spec: NormSpec) -> List[TensorNeed]:
-        return [TensorNeed(spec.weight, (spec.dim,), "float32")]
+        return [TensorNeed(spec.weight, (spec.dim,), "float32", init="around_one")]
 
     def load(self, tensors) -> None:
         self.weight = tensors[self.spec.weight]
 
-    def forward(self, res: Residual, ctx, rows=None, n_rows=None) -> torch.Tensor:
+    can_defer = True
+
+    def forward(self, res: Residual, ctx, rows=None, n_rows=None, lazy: bool = False):
         n = ctx.n_tokens if rows is None else (rows.numel() if n_rows is None else n_rows)
+        if lazy and res.pending is None and res.sumsq is not None:
+            # the stream is up to date and the sums of squares of its rows are known: whoever
+            # consumes the rows computes (w * x) / rms(x) while it loads them
+            return NormalizedRows(res.h, res.sumsq, self.weight, self.spec.eps, rows, n, self)
         out = ctx.ws.get("norm.out" if rows is None else "norm.rows_out", (n, self.spec.dim), self.env.dtype)
         self.env.ops.rmsnorm(res.h, self.weight, self.spec.eps, out, delta=res.pending, rows=rows, n_rows=n)
         if rows is None:
+            if res.pending is not None:
+                res.sumsq = None  # the stream has moved on
             res.pending = None
+        return out
+
+    def run(self, h: torch.Tensor, ctx, rows, n: int) -> torch.Tensor:
+        """The norm's kernel on rows of a stream that has nothing pending (NormalizedRows.dense)."""
+        out = ctx.ws.get("norm.out" if rows is None else "norm.rows_out", (n, self.spec.dim), self.env.dtype)
+        self.env.ops.rmsnorm(h, self.weight, self.spec.eps, out, rows=rows, n_rows=n)
         return out
 
 

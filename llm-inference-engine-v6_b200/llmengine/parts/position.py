@@ -47,6 +47,23 @@ def rope_tables(spec: PositionSpec):
     return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
 
 
+# One pair of tables per (spec, device), whichever and however many layers use it: the layers of a
+# model share one position spec, and a table of 131,072 positions with head size 128 is 67 MB.
+_TABLES = {}
+
+
+def shared_rope_tables(spec: PositionSpec, device: torch.device):
+    key = (spec, str(device))
+    hit = _TABLES.get(key)
+    if hit is None:
+        cos, sin = rope_tables(spec)
+        hit = (torch.from_numpy(cos).to(device), torch.from_numpy(sin).to(device))
+        while len(_TABLES) >= 8:  # engines come and go in one process (tests): the oldest entries go
+            _TABLES.pop(next(iter(_TABLES)))
+        _TABLES[key] = hit
+    return hit
+
+
 class RotaryPosition(PositionEncoding):
     takes_partial_sums = True
 
@@ -56,9 +73,7 @@ class RotaryPosition(PositionEncoding):
             raise ValueError(f"rotary position encoding needs an even head_dim, got {spec.head_dim}")
         if spec.max_positions <= 0:
             raise ValueError("rotary position encoding needs max_positions >= 1")
-        cos, sin = rope_tables(spec)
-        self.cos = torch.from_numpy(cos).to(env.device)
-        self.sin = torch.from_numpy(sin).to(env.device)
+        self.cos, self.sin = shared_rope_tables(spec, env.device)
 
     def rotation_tables(self):
         return self.cos, self.sin

@@ -1,6 +1,6 @@
 """Registry of part classes: (category, kind) -> class.
 
-Categories: "norm", "position", "mixer", "feed_forward", "block". A part class is built as
+Categories: "embedding", "norm", "position", "mixer", "feed_forward", "block", "head". A part class is built as
 `cls(spec, env)` and must provide the interface of its category (parts/base.py). Registering a
 class is all it takes to make a new kind usable from a model description; nothing in the engine
 names a concrete part.
@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from typing import Dict, Tuple, Type
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block")
+CATEGORIES = ("embedding", "norm", "position", "mixer", "feed_forward", "block", "head")
 _PARTS: Dict[Tuple[str, str], Type] = {}
 
 

@@ -19,10 +19,13 @@ class TensorNeed:
     precision: "compute" = a matrix that feeds matrix products, kept in the engine's dtype
                (bfloat16, or float32 on the 32-bit path);
                "float32" = always widened to float32 (norm weights and other vectors);
-               "stored"  = kept as the file stores it (32-bit stays 32-bit, integer tables int32)."""
+               "stored"  = kept as the file stores it (32-bit stays 32-bit, integer tables int32).
+    init: what the random-weights mode draws for it: "normal" = N(0, std); "around_one" = N(1, std)
+          (weights that multiply, such as a norm's); "zeros" (biases and other additive terms)."""
     name: str
     shape: Tuple[int, ...]
     precision: str = "compute"
+    init: str = "normal"
 
 
 @dataclass(frozen=True)
@@ -96,31 +99,39 @@ class LayerRun:
 
 @dataclass(frozen=True)
 class EmbeddingSpec:
+    """kind "lookup": residual stream row = table row of the token id, widened to float32."""
     weight: str
     vocab_size: int
     dim: int
+    kind: str = "lookup"
 
 
 @dataclass(frozen=True)
 class HeadSpec:
+    """kind "linear": logits = x . W^T in float32, no bias, for the wanted rows only."""
     weight: str  # the embedding's name when input and output embeddings are tied
     vocab_size: int
     dim: int
+    kind: str = "linear"
 
 
 @dataclass(frozen=True)
 class ModelSpec:
     architecture: str
-    embedding: EmbeddingSpec
+    embedding: object  # any registered "embedding" spec with `kind`, `weight`, `vocab_size`, `dim`
     layers: Tuple[BlockSpec, ...]
     order: Tuple[LayerRun, ...]
     final_norm: object
-    head: HeadSpec
+    head: object       # any registered "head" spec with `kind`, `weight`, `vocab_size`, `dim`
     max_positions: int
     eos_token_ids: FrozenSet[int] = field(default_factory=frozenset)
     # names that may be present in the checkpoint without being read, each with the needed tensor
     # it must agree with in shape (a tied lm_head saved beside the embedding)
     duplicates: Dict[str, str] = field(default_factory=dict)
+    # shell-style patterns of names that a checkpoint may carry and nobody reads (buffers that some
+    # exporters save, such as "*.rotary_emb.inv_freq"); the reference maps whatever a file holds and
+    # reads what it needs (src/weights.cpp:269-301), so it ignores them too
+    ignore: Tuple[str, ...] = ()
 
     @property
     def vocab_size(self) -> int:

@@ -13,7 +13,8 @@ as norm weights are always float32; tensors asked for as "stored" keep the file'
 """
 from __future__ import annotations
 
-from typing import Dict, Iterable, List, Mapping
+from fnmatch import fnmatchcase
+from typing import Dict, Iterable, List, Mapping, Sequence
 
 import torch
 
@@ -76,7 +77,8 @@ class Checkpoint:
 
 
 def load_tensors(ckpt: Checkpoint, needs: Mapping[str, TensorNeed], duplicates: Mapping[str, str],
-                 device: torch.device, compute_dtype: torch.dtype) -> Dict[str, torch.Tensor]:
+                 device: torch.device, compute_dtype: torch.dtype, ignore: Sequence[str] = ()) -> Dict[str, torch.Tensor]:
+    """ignore: shell-style patterns of names the checkpoint may carry unread (ModelSpec.ignore)."""
     missing, unexpected, wrong = [], [], []
     for name, need in sorted(needs.items()):
         if name not in ckpt:
@@ -91,7 +93,8 @@ def load_tensors(ckpt: Checkpoint, needs: Mapping[str, TensorNeed], duplicates: 
             continue
         twin = duplicates.get(name)
         if twin is None:
-            unexpected.append(name)
+            if not any(fnmatchcase(name, pat) for pat in ignore):
+                unexpected.append(name)
         elif twin in ckpt and (tuple(ckpt.shape(name)) != tuple(ckpt.shape(twin)) or ckpt.dtype(name) != ckpt.dtype(twin)):
             # a tied output embedding saved beside the input embedding must agree with it
             # (src/weights.cpp:259-264)

@@ -4,8 +4,9 @@ configuration and a seed.
 The reference has no such mode in C++ (its tests save a seeded model from another library,
 tests/fixtures.py:16-55). Here every tensor the model description names is drawn on the CPU from a
 generator keyed by (seed, tensor name), so a tensor's values depend on nothing else: not on the
-order of tensors, not on the device. Matrices and embeddings ~ N(0, std), vectors (norm weights)
-~ N(1, std); std defaults to 0.02.
+order of tensors, not on the device. What is drawn is a field of the part's own `TensorNeed`
+(`init`): N(0, std) by default, N(1, std) for weights that multiply (norm weights), zeros for
+additive terms; std defaults to 0.02.
 """
 from __future__ import annotations
 
@@ -25,8 +26,8 @@ from .safetensors_io import write_safetensors
 
 def model_tensor_needs(spec: ModelSpec) -> Dict[str, TensorNeed]:
     """Every tensor the described model reads."""
-    needs = [TensorNeed(spec.embedding.weight, (spec.embedding.vocab_size, spec.embedding.dim), "compute"),
-             TensorNeed(spec.head.weight, (spec.head.vocab_size, spec.head.dim), "compute")]
+    needs = list(part_class("embedding", spec.embedding.kind).tensor_needs(spec.embedding))
+    needs += part_class("head", spec.head.kind).tensor_needs(spec.head)
     for block in spec.layers:
         needs += part_class("block", block.kind).tensor_needs(block)
     needs += part_class("norm", spec.final_norm.kind).tensor_needs(spec.final_norm)
@@ -42,9 +43,14 @@ def random_tensors(spec: ModelSpec, seed: int, dtype: torch.dtype = torch.bfloat
     for name, need in sorted(model_tensor_needs(spec).items()):
         g = torch.Generator(device="cpu")
         g.manual_seed(_tensor_seed(seed, name))
-        t = torch.randn(need.shape, generator=g, dtype=torch.float32) * std
-        if need.precision == "float32" and len(need.shape) == 1:
-            t += 1.0
+        if need.init == "zeros":
+            t = torch.zeros(need.shape, dtype=torch.float32)
+        elif need.init in ("normal", "around_one"):
+            t = torch.randn(need.shape, generator=g, dtype=torch.float32) * std
+            if need.init == "around_one":
+                t += 1.0
+        else:
+            raise ValueError(f"tensor need '{name}': unknown init '{need.init}' (normal, around_one, zeros)")
         out[name] = t.to(dtype)
     return out
 

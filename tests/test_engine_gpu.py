@@ -144,6 +144,8 @@ def _register_toy():
     from dataclasses import replace
 
     class RunningMean(Mixer):
+        capturable = False  # its forward reads the batch on the host: no CUDA graph may record it
+
         @staticmethod
         def tensor_needs(spec):
             return [TensorNeed(spec.weight, (spec.hidden, spec.hidden))]
@@ -219,6 +221,17 @@ def test_toy_mixer_with_state_can_be_registered_built_and_stepped(tmp_path):
     np.testing.assert_allclose(eng.run_step([(3, ids_b, range(14))], end=[3]).cpu().numpy(), ref_b, atol=2e-4, rtol=0)
     out, reason = eng.generate(ids_b[:4], 5)
     assert len(out) == 9 and reason == "length" and eng.cm.free_slots == 2
+    # bfloat16 serving replays CUDA graphs for decode steps, unless a part says that it cannot be
+    # recorded: then generation and the scheduler run the same steps kernel by kernel
+    engb = llmengine.Engine(d, "bf16", block_size=4, num_blocks=24, max_concurrent=2)
+    np.testing.assert_allclose(engb.forward_logits(ids_a), ref_a, atol=6e-2, rtol=0)
+    assert engb.cuda_graphs is False and engb.graphs is None
+    outb, reason = engb.generate(ids_b[:4], 8)
+    assert len(outb) == 12 and reason == "length" and engb.graphs is None
+    lg = _toy_plain(pc, pw, outb)
+    for k in range(4, 12):  # each token is the plain model's choice, or a near tie
+        best = int(lg[k - 1].argmax())
+        assert outb[k] == best or lg[k - 1][best] - lg[k - 1][outb[k]] < 0.12
 
 
 # ------------------------------------------------- a toy routed feed-forward, a toy position encoding

@@ -85,3 +85,30 @@ def test_no_alloc_sampling_refuses_more_rows_than_its_scratch_holds():
                                  c_int(64), c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc != 0 and b"exceed the built-in scratch" in lib.llm_last_error()
     torch.cuda.synchronize()
+
+
+def test_no_alloc_sampling_at_the_full_extent_of_its_scratch():
+    """The largest request the built-in array takes: 256 rows, the vocabulary scanned in 64 chunks
+    (any vocabulary above 258,048 entries), so that the last (value, index) words of the array are
+    written and read. Greedy rows are checked against an argmax taken by another library on the
+    host, not only against the regular entry point, which shares the kernels."""
+    lib = _lib()
+    dev = torch.device("cuda:0")
+    n, vocab = MAX_ROWS, 258048 + 1001
+    assert lib.llm_sample_chunks(c_int(vocab)) == 64
+    g = torch.Generator(device=dev).manual_seed(7)
+    logits = torch.randn(n, vocab, generator=g, device=dev)
+    logits[2, vocab - 1] = 50.0      # the winner sits in the last chunk's last place
+    logits[4, 0] = logits[4, vocab - 2] = 50.0  # a tie across the first and the last chunk: the lower index wins
+    temps = torch.zeros(n, device=dev)
+    temps[1::2] = 0.8                # every other row is sampled
+    seeds = torch.arange(n, dtype=torch.int32, device=dev)
+    draws = torch.full((n,), 5, dtype=torch.int32, device=dev)
+    want = _regular(lib, logits, temps, seeds, draws, n, vocab)
+    first = _no_alloc(lib, logits, temps, seeds, draws, n, vocab)
+    second = _no_alloc(lib, logits, temps, seeds, draws, n, vocab)
+    torch.cuda.synchronize()
+    assert torch.equal(first, want) and torch.equal(second, want)
+    host = logits[0::2].cpu().numpy().argmax(axis=1)  # numpy: the first index of the maximum
+    assert first[0::2].cpu().tolist() == host.tolist()
+    assert int(first[4]) == 0 and int(first[2]) == vocab - 1
