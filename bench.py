@@ -9,13 +9,16 @@ geometry with random bfloat16 weights (written as a model folder by the engine's
 mode and read back through its loader), a batch of 8 and contexts of 2,048 tokens.
 
 One JSON line is printed:
-  value        decoded tokens a second, device time (CUDA events around K steps, host running ahead)
+  value        decoded tokens a second, device time (CUDA events around K steps, host running ahead); the
+               K-step region is timed --reps times (default 5) and the median is reported, with the
+               fastest and slowest region in `spread`
   e2e          the same through the Python entry point (ContinuousBatchScheduler.step): every step
                copies that step's batch from pinned host memory and reads the sampled tokens back
   prefill      one 2,048-token prompt as one step: tokens a second, ms, fraction of the tensor peak
   roofline     decode step: bytes it must read (every weight once + the cache of the live requests)
                / step time, against the measured copy bandwidth
-  points       decode tokens a second at batch 1 and 64
+  points       decode tokens a second at batch 1 and 64 (with ms a step and the fraction of the copy
+               bandwidth), and at batch 8 through the true 32-bit path (CUDA-core kernels)
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from the fallback figures
 measured earlier on this pool (6.65 TB/s, 1.59 PFLOP/s). For --gpus > 1 one line says that this
 engine is single-GPU and the exit code is 2.
@@ -151,13 +154,14 @@ def run_ours(args):
     t0 = time.time()
     llmengine.write_random_model(tmp.name, g, seed=0, dtype=torch.bfloat16)
     max_batch = max(args.batch, 64 if args.points else args.batch, 1)
-    room = CONTEXT + 2 * (K + W) + max_batch + 64
+    R = max(1, args.reps)
+    room = CONTEXT + 2 * (K * R + W) + max_batch + 64
     num_blocks = max_batch * (room + BLOCK_SIZE - 1) // BLOCK_SIZE + PREFILL_TOKENS // BLOCK_SIZE + 8
     skip = set(x for x in args.skip.split(",") if x)
     if "points" in skip:
         args.points = False
-    eng = llmengine.Engine(tmp.name, "bf16", block_size=BLOCK_SIZE, num_blocks=num_blocks, max_concurrent=max_batch,
-                           cuda_graphs=args.graphs)
+    eng = main_eng = llmengine.Engine(tmp.name, "bf16", block_size=BLOCK_SIZE, num_blocks=num_blocks, max_concurrent=max_batch,
+                                      cuda_graphs=args.graphs)
     eng.configure_cache()
     sys.stderr.write(f"[bench] model written and loaded in {time.time() - t0:.1f}s; {num_blocks} pages\n")
     gen = torch.Generator().manual_seed(1)
@@ -169,17 +173,19 @@ def run_ours(args):
     def check(phase):
         """A kernel whose bounded wait gave up leaves a code and returns; every launch after it may do
         the same, a second at a time. Better to stop at once and say where."""
-        code = eng.ops.tensor_core_error()
+        code = main_eng.ops.tensor_core_error()
         if code:
             raise RuntimeError(f"a tensor-core kernel gave up a wait (code {code}) during: {phase}")
         sys.stderr.write(f"[bench] {phase}: done at {time.time() - t0:.1f}s\n")
         sys.stderr.flush()
 
-    def decode_run(batch, k_steps, w_steps, e2e):
-        """-> (seconds per step, kernel launches per step, h2d bytes, d2h bytes)."""
+    def decode_run(batch, k_steps, w_steps, e2e, reps=1, eng=None):
+        """-> (median seconds per step over `reps` timed regions of k_steps, kernel launches per step,
+        h2d bytes, d2h bytes, [seconds per step of every region])."""
+        eng = eng or main_eng
         sch = llmengine.ContinuousBatchScheduler(eng, None, max_concurrent=batch, max_prefill_tokens_per_step=PREFILL_TOKENS)
         for p in prompts(batch, CONTEXT):
-            sch.enqueue(p, 2 * (k_steps + w_steps) + batch + 8)  # early requests decode while later prompts prefill
+            sch.enqueue(p, 2 * (k_steps * reps + w_steps) + batch + 8)  # early requests decode while later prompts prefill
         for _ in range(2 * batch + 8):  # prefill (untimed): one prompt a step
             if sch.core.num_running == batch:
                 break
@@ -208,16 +214,19 @@ def run_ours(args):
         torch.cuda.synchronize()
         check(f"warm-up steps of batch {batch}")
         eng.ops.launches = 0
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t_wall = time.perf_counter()
-        start.record()
-        for _ in range(k_steps):
-            one_step()
-        stop.record()
-        torch.cuda.synchronize()
-        wall = time.perf_counter() - t_wall
-        dev = start.elapsed_time(stop) / 1e3
-        launches = eng.ops.launches / k_steps
+        regions = []
+        for _ in range(reps):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t_wall = time.perf_counter()
+            start.record()
+            for _ in range(k_steps):
+                one_step()
+            stop.record()
+            torch.cuda.synchronize()
+            wall = time.perf_counter() - t_wall
+            dev = start.elapsed_time(stop) / 1e3
+            regions.append((max(dev, wall) if e2e else dev) / k_steps)
+        launches = eng.ops.launches / (k_steps * reps)
         check(f"timed steps of batch {batch}" + (" through the scheduler" if e2e else ""))
         if e2e and eng.cuda_graphs and eng.graphs is not None:
             h2d, d2h = eng.graphs.h2d_bytes, eng.graphs.d2h_bytes
@@ -226,7 +235,7 @@ def run_ours(args):
         # drain: finish the requests and give their pages back
         for r in list(sch._cm.request_ids()):
             sch._cm.release(r)
-        return (max(dev, wall) if e2e else dev) / k_steps, launches, h2d, d2h
+        return statistics.median(regions), launches, h2d, d2h, regions
 
     def prefill_run(k_steps, w_steps):
         times = []
@@ -234,6 +243,7 @@ def run_ours(args):
             ids = prompts(1, PREFILL_TOKENS)[0]
             e = H.StepEntries()
             rid = 10 ** 9 + i
+            eng = main_eng
             eng.cm.add_request(rid)
             assert eng.cm.reserve(rid, PREFILL_TOKENS)
             e.add(rid, ids, [PREFILL_TOKENS - 1])
@@ -253,22 +263,31 @@ def run_ours(args):
     clocks = ClockSampler()
     clocks.start()
     if "decode" in skip:  # profiling runs of the prefill alone
-        sec, launches = float("inf"), 0
+        sec, launches, regions = float("inf"), 0, [float("inf")]
     else:
-        sec, launches, _, _ = decode_run(args.batch, K, W, e2e=False)
+        sec, launches, _, _, regions = decode_run(args.batch, K, W, e2e=False, reps=R)
     clock_rec = clocks.stop()
     e2e_sec, h2d, d2h = sec, 0, 0
     if "e2e" not in skip:
-        e2e_sec, _, h2d, d2h = decode_run(args.batch, K, W, e2e=True)
+        e2e_sec, _, h2d, d2h, _ = decode_run(args.batch, K, W, e2e=True, reps=R)
     pre_sec = prefill_run(max(2, min(K, 5)), max(1, min(W, 3))) if "prefill" not in skip else float("inf")
     points = {}
     if args.points:
         for b in (1, 64):
-            s, *_ = decode_run(b, max(4, K // 2), W, e2e=False)
+            s, *_ = decode_run(b, max(4, K // 2), W, e2e=False, reps=min(R, 3))
             points[f"decode_b{b}"] = round(b / s, 1)
+            points[f"decode_b{b}_ms"] = round(s * 1e3, 4)
+            points[f"decode_b{b}_hbm_frac"] = round(decode_bytes(g, layers, b, CONTEXT + W + K // 2) / s / 1e9 / pk["hbm_gbs"], 4)
+        # the true 32-bit path of the same model (CUDA-core products, float32 cache): what the oracle costs
+        fp32_blocks = args.batch * (CONTEXT + 64) // BLOCK_SIZE + 16
+        eng32 = llmengine.Engine(tmp.name, "fp32", block_size=BLOCK_SIZE, num_blocks=fp32_blocks, max_concurrent=args.batch)
+        eng32.configure_cache()
+        s, *_ = decode_run(args.batch, 4, 3, e2e=False, eng=eng32)
+        points[f"decode_b{args.batch}_fp32"] = round(args.batch / s, 1)
+        points[f"decode_b{args.batch}_fp32_ms"] = round(s * 1e3, 3)
 
     value = args.batch / sec
-    bytes_step = decode_bytes(g, layers, args.batch, CONTEXT + W + K // 2)
+    bytes_step = decode_bytes(g, layers, args.batch, CONTEXT + W + K * R // 2)
     achieved = bytes_step / sec / 1e9 if sec != float("inf") else 0.0
     pf = flops_of_prefill(g, layers, PREFILL_TOKENS)
     rec = {
@@ -283,6 +302,8 @@ def run_ours(args):
                    "vocab": g["vocab_size"], "tied_embeddings": bool(g["tie_word_embeddings"]), "kv_block_size": BLOCK_SIZE,
                    "prefill_tokens": PREFILL_TOKENS, "l2": "step reads > 2 GB of weights: inputs larger than L2",
                    "peaks": pk["source"]},
+        "spread": ({"reps": R, "min_ms": round(min(regions) * 1e3, 4), "max_ms": round(max(regions) * 1e3, 4)}
+                   if sec != float("inf") else None),
         "e2e": {"value": round(args.batch / e2e_sec, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": int(round(launches * K)),
         "prefill": {"value": round(PREFILL_TOKENS / pre_sec, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_sec * 1e3, 3),
@@ -363,6 +384,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--reps", type=int, default=5, help="how many times the K-step region is timed (the median is reported)")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the full configuration (named in `config`); 0: all")
     ap.add_argument("--geometry", choices=sorted(GEOMETRIES), default="1b", help="layer sizes: Llama 3.2 1B (default), 3.2 3B, 3.1 8B")
     ap.add_argument("--no-points", dest="points", action="store_false", help="skip the batch 1 and 64 points")
