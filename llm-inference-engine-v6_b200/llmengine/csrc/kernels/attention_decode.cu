@@ -16,8 +16,9 @@
 // splits' partials in index order: a token's result does not depend on the batch or on page numbers.
 // Up to eight splits of a (request, key/value head) run as ONE thread-block cluster (CLUSTER): each
 // CTA finishes a slice of the output; every CTA stores its partial's shares into the shared memory
-// of the CTAs that finish them (distributed shared memory) and then arrives on an mbarrier in each
-// of them; a CTA that has seen all arrivals finds all it needs in its own shared memory. The
+// of the CTAs that finish them (distributed shared memory, asynchronous stores whose bytes are
+// counted on an mbarrier of the receiver); a CTA that has seen all bytes counted in finds all it
+// needs in its own shared memory. The
 // hardware cluster barrier is used once, split in two: every thread arrives right after the CTA's
 // own barriers are initialised (nothing conditional comes before that) and waits just before the
 // first access to a peer's shared memory, which CUDA allows only once the peer has started. Every
@@ -81,11 +82,16 @@ struct DecLayout {
 // Byte offset of (row, 16-byte chunk) inside a [TK][64] tile written by TMA with 128-byte swizzle.
 __device__ __forceinline__ uint32_t sw128(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
 
-// One float into the shared memory of CTA `rank` of this cluster, at the address `smem_addr` has here.
-__device__ __forceinline__ void store_to_cta(uint32_t smem_addr, int rank, float v) {
-  uint32_t remote;
+// One float into the shared memory of CTA `rank` of this cluster, at the address `smem_addr` has here;
+// its 4 bytes are counted on that CTA's mbarrier `bar` when they have landed, so the receiver needs no
+// arrival from the sender and the sender no fence.
+__device__ __forceinline__ void send_to_cta(uint32_t smem_addr, uint64_t* bar, int rank, float v) {
+  uint32_t remote, remote_bar;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr), "r"(rank));
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(smem_u32(bar)), "r"(rank));
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(remote), "r"(__float_as_uint(v)),
+               "r"(remote_bar)
+               : "memory");
 }
 
 // The two halves of the hardware cluster barrier (all threads of the CTA, converged).
@@ -124,8 +130,10 @@ __device__ __forceinline__ bool mbar_wait_peers(uint64_t* bar, uint32_t parity, 
   }
 }
 
+// (Four CTAs of head size 64 share an SM when the launch is larger than one wave: at most 96
+// registers a thread, which the second number asks the compiler to keep; head size 128: two.)
 template <int HD, bool FUSED, bool DEEP, bool CLUSTER>
-__global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
+__global__ void __launch_bounds__(DEC_THREADS, (HD == 64 ? 4 : 2)) paged_attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                                  const __grid_constant__ CUtensorMap map_v,
                                                                                  const DecParams p) {
   using L = DecLayout<HD, DEEP>;
@@ -136,7 +144,7 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
   bf16* q_s = reinterpret_cast<bf16*>(ring + (size_t)NS * L::STAGE_BYTES);  // [ROWS][Q_LD]
   uint64_t* full = reinterpret_cast<uint64_t*>(q_s + ROWS * L::Q_LD);       // [NS]
   uint64_t* empty = full + NS;                                              // [NS]
-  uint64_t* peers_in = empty + NS;   // CLUSTER: every CTA of the cluster has stored its shares here (one arrival each)
+  uint64_t* peers_in = empty + NS;   // CLUSTER: the bytes of the shares that every CTA of the cluster sends here have all landed
   uint64_t* slices_out = peers_in + 1;  // CLUSTER, in the cluster's first CTA: every CTA's slice of the cluster's partial is in global memory
   int* flags = reinterpret_cast<int*>(slices_out + 1);                      // [0] abort, [1] tiles issued, [2] is_last
   bf16* kv_new = reinterpret_cast<bf16*>(flags + 4);                        // [2][HD]: the token's own key and value (fused form)
@@ -169,12 +177,19 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
       mbar_init(&empty[s], 1);
     }
     if (CLUSTER) {
-      mbar_init(peers_in, (uint32_t)p.cluster_size);
+      mbar_init(peers_in, 1);
       mbar_init(slices_out, (uint32_t)p.cluster_size);
     }
     flags[0] = 0;
     flags[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (CLUSTER) {
+      // what the CTAs of the cluster (this one too) will send here: every one its share of the output
+      // elements that this CTA finishes (e = rank, rank + size, ...) and its (max, sum) of every row
+      const int cs = p.cluster_size, rk = split % cs, n_el = (p.nq / p.nkv) * HD;
+      const int mine = rk < n_el ? (n_el - rk + cs - 1) / cs : 0;
+      mbar_expect_tx(peers_in, (uint32_t)(cs * (mine + 2 * (p.nq / p.nkv)) * 4));
+    }
   }
   if (any) {
     const int* table = p.block_table + (size_t)seq * p.max_blocks;
@@ -467,10 +482,19 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
     // A wait gave up. The peers wait for this CTA's shares: tell them at once that there are none
     // (the error word is set; the output of this launch is void), then let the copies that were
     // issued land (bounded), and leave only when no peer can reach this CTA's shared memory any more.
-    if (CLUSTER && tid == 0) {
-      for (int c = 0; c < csize; ++c) mbar_arrive_cta(peers_in, c);
-      if (p.n_splits > csize) mbar_arrive_cta(slices_out, 0);
+    if (CLUSTER) {  // shares that weigh nothing: a maximum of -inf and a sum of 0
+      const int epo = (g * HD + csize - 1) / csize;
+      const uint32_t recv_a = smem_u32(recv);
+      for (int e = tid; e < g * HD; e += DEC_THREADS) {
+        send_to_cta(recv_a + (uint32_t)(rank * epo + e / csize) * 4u, peers_in, e % csize, 0.f);
+        if (e % HD == 0)
+          for (int c = 0; c < csize; ++c) {
+            send_to_cta(recv_a + (uint32_t)(csize * epo + (rank * g + e / HD) * 2) * 4u, peers_in, c, -INFINITY);
+            send_to_cta(recv_a + (uint32_t)(csize * epo + (rank * g + e / HD) * 2 + 1) * 4u, peers_in, c, 0.f);
+          }
+      }
     }
+    if (CLUSTER && tid == 0 && p.n_splits > csize) mbar_arrive_cta(slices_out, 0);
     if (tid == 0) {
       const int issued = flags[1];
       for (int t = max(0, issued - NS); t < issued; ++t) {
@@ -517,11 +541,11 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
       // element e of the cluster's output is finished by rank e % size: send it this split's share
       const int epo = (g * HD + csize - 1) / csize;
       const uint32_t recv_a = smem_u32(recv);
-      store_to_cta(recv_a + (uint32_t)(rank * epo + e / csize) * 4u, e % csize, acc * inv);
+      send_to_cta(recv_a + (uint32_t)(rank * epo + e / csize) * 4u, peers_in, e % csize, acc * inv);
       if (d == 0) {
         for (int c = 0; c < csize; ++c) {
-          store_to_cta(recv_a + (uint32_t)(csize * epo + (rank * g + row) * 2) * 4u, c, mx);
-          store_to_cta(recv_a + (uint32_t)(csize * epo + (rank * g + row) * 2 + 1) * 4u, c, den);
+          send_to_cta(recv_a + (uint32_t)(csize * epo + (rank * g + row) * 2) * 4u, peers_in, c, mx);
+          send_to_cta(recv_a + (uint32_t)(csize * epo + (rank * g + row) * 2 + 1) * 4u, peers_in, c, den);
         }
       }
     } else {
@@ -537,16 +561,12 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_attention_decode_tma_kernel
   int n_merge = p.n_splits;  // partials that meet in global memory
   if constexpr (CLUSTER) {
     // ---- eight (or fewer) neighbouring splits are the CTAs of this cluster: every CTA has sent each
-    // peer its share (remote shared-memory stores above) and, after the barrier, finishes the
-    // elements e = rank, rank + size, ... from what it received, in index order
+    // peer its share (asynchronous stores above, counted on the receiver's barrier) and, once all
+    // bytes are in, finishes the elements e = rank, rank + size, ... from what it received, in index order
     const int group = split / csize;
     n_merge = p.n_splits / csize;
-    __syncthreads();  // the stores of all threads come before the arrivals below
-    if (tid == 0)
-      for (int c = 0; c < csize; ++c) mbar_arrive_cta(peers_in, c);
-    bool peers_ok = true;
-    if (tid == 0) peers_ok = mbar_wait_peers(peers_in, 0, p.error, ERR_DEC_PEERS);
-    peers_ok = __syncthreads_and(peers_ok);
+    // every thread sees the bytes of all shares counted in before it reads them
+    const bool peers_ok = __syncthreads_and(mbar_wait_peers(peers_in, 0, p.error, ERR_DEC_PEERS));
     // (after this no peer touches this CTA's shared memory again; the first CTA of a cluster also
     // waits for `slices_out` below)
     if (!peers_ok) {

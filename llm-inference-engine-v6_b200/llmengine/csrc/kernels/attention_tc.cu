@@ -14,8 +14,12 @@
 //                    rescaled by the owner of each row when its max moves
 //
 // Warps 0-3 are the softmax threads; one thread of a fifth warp issues the TMA loads and the MMAs
-// and runs ahead of them (the next tile's S = Q K^T is queued right behind the current P V), the
-// two sides meeting only at mbarriers; two CTAs per SM fill each other's gaps. Every
+// and runs ahead of them: the scores of tile i + 1 are queued as soon as the softmax threads have
+// READ the scores of tile i (not when they have finished with them), so they are waiting when the
+// softmax of tile i ends, and P V of tile i runs under the softmax of tile i + 1. Keys and values
+// have their own stage barriers: a key stage is free once its scores are done, long before the
+// value stage, so the next keys are requested a whole softmax earlier. Two CTAs per SM fill each
+// other's gaps. Every
 // wait on an mbarrier is bounded (see tc_common.cuh). head_dim 64 or 128 (rows of 128 dims are two
 // 64-dim blocks of 128-byte swizzled rows: Q K^T runs over both, P V is one product per block),
 // page sizes that are multiples of 8 and divide the tile, groups of up to 128 heads (a CTA takes
@@ -80,6 +84,13 @@ __device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t* r) 
       : "memory");
 }
 
+// Largest of three, one instruction.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // 2^x on the special-function unit, one instruction (exp2f adds range handling that is not needed here).
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -114,12 +125,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* q_s = smem;                  // [DBLK blocks][128 rows][128 B], 128-byte swizzle
   uint8_t* kv_s = smem + Q_BYTES;       // [2 stages][K | V], each [DBLK blocks][KEYS rows][128 B], 128-byte swizzle
-  uint64_t* full = reinterpret_cast<uint64_t*>(kv_s + 4 * KV_BYTES);  // [2] keys and values of a tile have landed
-  uint64_t* s_bar = full + 2;           // the scores of a tile are in tensor memory
-  uint64_t* p_bar = s_bar + 1;          // all 128 rows of P are in tensor memory (128 arrivals)
+  uint64_t* full_k = reinterpret_cast<uint64_t*>(kv_s + 4 * KV_BYTES);  // [2] the keys of a tile have landed
+  uint64_t* full_v = full_k + 2;        // [2] the values of a tile have landed
+  uint64_t* s_bar = full_v + 2;         // the scores of a tile are in tensor memory
+  uint64_t* s_free = s_bar + 1;         // all 128 rows have read their scores: the S columns may be overwritten (128 arrivals)
+  uint64_t* p_bar = s_free + 1;         // all 128 rows of P are in tensor memory (128 arrivals)
   uint64_t* o_bar = p_bar + 1;          // the P V product of a tile is done
   uint64_t* done_bar = o_bar + 1;       // every product that was issued has finished (committed last, also after giving up)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 2);  // (+1 spare word: the ints after it stay 16-byte aligned)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* page_s = reinterpret_cast<int*>(tmem_slot + 4);  // the tile range's slice of the block table
 
@@ -148,9 +161,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
   const int pages_per_tile = KEYS / p.page_size;
 
   if (tid == 0) {
-    mbar_init(&full[0], 1);
-    mbar_init(&full[1], 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&full_k[b], 1);
+      mbar_init(&full_v[b], 1);
+    }
     mbar_init(s_bar, 1);
+    mbar_init(s_free, ROWS);
     mbar_init(p_bar, ROWS);
     mbar_init(o_bar, 1);
     mbar_init(done_bar, 1);
@@ -176,25 +192,27 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
     }
   }
   __syncthreads();
-  auto issue_tile = [&](int i) {  // keys and values of tile i -> stage i % 2
+  auto issue_part = [&](int i, bool values) {  // keys or values of tile i -> stage i % 2
     const int first_page = (kt_first + i) * pages_per_tile - page_lo;
-    uint8_t* ks = kv_s + (size_t)(i & 1) * 2 * KV_BYTES;
-    uint8_t* vs = ks + KV_BYTES;
-    mbar_expect_tx(&full[i & 1], (uint32_t)(2 * KV_BYTES));
+    uint8_t* dst = kv_s + (size_t)(i & 1) * 2 * KV_BYTES + (values ? KV_BYTES : 0);
+    uint64_t* bar = values ? &full_v[i & 1] : &full_k[i & 1];
+    const CUtensorMap* map = values ? &map_v : &map_k;
+    mbar_expect_tx(bar, (uint32_t)KV_BYTES);
     for (int pg = 0; pg < pages_per_tile; ++pg) {
       const int row = (page_s[first_page + pg] * p.nkv + kvh) * p.page_size;
 #pragma unroll
-      for (int b = 0; b < DBLK; ++b) {
-        tma_load_2d(ks + b * (KEYS * 128) + (size_t)pg * p.page_size * 128, &map_k, b * 64, row, &full[i & 1]);
-        tma_load_2d(vs + b * (KEYS * 128) + (size_t)pg * p.page_size * 128, &map_v, b * 64, row, &full[i & 1]);
-      }
+      for (int b = 0; b < DBLK; ++b) tma_load_2d(dst + b * (KEYS * 128) + (size_t)pg * p.page_size * 128, map, b * 64, row, bar);
     }
   };
   dep_wait();
   // the first two tiles are on their way while the query rows are fetched
   if (tid == 4 * 32) {
-    issue_tile(0);
-    if (n_tiles > 1) issue_tile(1);
+    issue_part(0, false);
+    issue_part(0, true);
+    if (n_tiles > 1) {
+      issue_part(1, false);
+      issue_part(1, true);
+    }
   }
   // ---- Q rows -> shared memory in the swizzled K-major layout (16-byte chunk c of row r at c ^ (r % 8))
   if (tid < ROWS) {
@@ -233,17 +251,35 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
         }
         mma_commit(s_bar);
       };
-      int issued = n_tiles > 1 ? 2 : 1, landed = 0;  // tiles whose copies were requested / have arrived
-      ok = mbar_wait(&full[0], 0, abort_flag, p.error_out, ERR_ATT_KV);
+      // what was requested and what has arrived, keys and values apart (for the drain after giving up)
+      int k_issued = n_tiles > 1 ? 2 : 1, v_issued = k_issued, k_landed = 0, v_landed = 0;
+      ok = mbar_wait(&full_k[0], 0, abort_flag, p.error_out, ERR_ATT_KV);
       if (ok) {
-        landed = 1;
+        k_landed = 1;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         issue_scores(0);
       }
       for (int i = 0; i < n_tiles && ok; ++i) {
-        // P of tile i is in tensor memory (so its scores have been read: the S columns are free again)
+        if (i + 1 < n_tiles) {
+          // every row has READ the scores of tile i: the S columns are free, and so is the key stage
+          // of tile i (its scores are done). Queue the next scores now, under the softmax of tile i.
+          ok = mbar_wait(s_free, (uint32_t)i & 1u, abort_flag, p.error_out, ERR_ATT_S);
+          if (!ok) break;
+          if (i + 2 < n_tiles) {
+            issue_part(i + 2, false);
+            k_issued = i + 3;
+          }
+          ok = mbar_wait(&full_k[(i + 1) & 1], (uint32_t)((i + 1) >> 1) & 1u, abort_flag, p.error_out, ERR_ATT_KV);
+          if (!ok) break;
+          k_landed = i + 2;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_scores(i + 1);
+        }
+        // P of tile i is in tensor memory
         ok = mbar_wait(p_bar, (uint32_t)i & 1u, abort_flag, p.error_out, ERR_ATT_S);
+        if (ok) ok = mbar_wait(&full_v[i & 1], (uint32_t)(i >> 1) & 1u, abort_flag, p.error_out, ERR_ATT_KV);
         if (!ok) break;
+        v_landed = i + 1;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         constexpr uint32_t idesc_o = instr_desc_att(64, true);
 #pragma unroll
@@ -255,24 +291,18 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
                        idesc_o, (i > 0 || k > 0) ? 1u : 0u);
         }
         mma_commit(o_bar);
-        if (i + 1 < n_tiles) {  // the next tile's scores go to the tensor pipe right behind this product
-          ok = mbar_wait(&full[(i + 1) & 1], (uint32_t)((i + 1) >> 1) & 1u, abort_flag, p.error_out, ERR_ATT_KV);
-          if (!ok) break;
-          landed = i + 2;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_scores(i + 1);
-        }
-        if (i + 2 < n_tiles) {  // stage i % 2 is free once the product of tile i is done
+        if (i + 2 < n_tiles) {  // the value stage of tile i is free once its product is done
           ok = mbar_wait(o_bar, (uint32_t)i & 1u, abort_flag, p.error_out, ERR_ATT_O);
           if (ok) {
-            issue_tile(i + 2);
-            issued = i + 3;
+            issue_part(i + 2, true);
+            v_issued = i + 3;
           }
         }
       }
       mma_commit(done_bar);
       // gave up: the copies still on their way land (bounded) before the CTA gives its shared memory back
-      for (int t = landed; !ok && t < issued; ++t) mbar_drain(&full[t & 1], (uint32_t)(t >> 1) & 1u, p.error_out);
+      for (int t = k_landed; !ok && t < k_issued; ++t) mbar_drain(&full_k[t & 1], (uint32_t)(t >> 1) & 1u, p.error_out);
+      for (int t = v_landed; !ok && t < v_issued; ++t) mbar_drain(&full_v[t & 1], (uint32_t)(t >> 1) & 1u, p.error_out);
     }
   } else {
     // -------------------------------------------------------------- softmax: thread t owns row t
@@ -291,6 +321,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
 #pragma unroll
       for (int c = 0; c < KEYS / 32; ++c) tmem_load32(tmem_base + lane_base + S_COL + c * 32, s + c * 32);
       tmem_load_wait();  // four loads in flight, one wait
+      // the scores are in registers: the tensor cores may write the next tile's scores over them
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(s_free);
       const int key0 = (kt_first + i) * KEYS;
       const bool full_tile = (key0 + KEYS - 1 <= pos_r) && (key0 >= lo_r);
       // s stays unscaled: max(s * c) = c * max(s) for c > 0, and the scale folds into the exponent's
@@ -303,8 +336,20 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
           s[j] = (key <= pos_r && key >= lo_r) ? s[j] : -INFINITY;
         }
       }
+      {  // eight independent chains instead of one of KEYS dependent maxima, three inputs an instruction
+        float m8[8];
 #pragma unroll
-      for (int j = 0; j < KEYS; ++j) mx = fmaxf(mx, s[j]);
+        for (int c = 0; c < 8; ++c) m8[c] = max3(s[c], s[c + 8], s[c + 16]);
+#pragma unroll
+        for (int j = 24; j + 16 <= KEYS; j += 16) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) m8[c] = max3(m8[c], s[j + c], s[j + c + 8]);
+        }
+        static_assert((KEYS - 24) % 16 == 8, "the tail below takes the last eight scores");
+#pragma unroll
+        for (int c = 0; c < 8; ++c) m8[c] = fmaxf(m8[c], s[KEYS - 8 + c]);
+        mx = fmaxf(max3(m8[0], m8[1], m8[2]), fmaxf(max3(m8[3], m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+      }
       mx *= sl2;  // (-inf stays -inf)
       // The running max is only moved when it would grow by more than 2^8: until then the row keeps
       // its older, smaller reference (probabilities up to 256 instead of 1, harmless in float32 and
@@ -313,20 +358,29 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
       const float m_new = move ? mx : m_run;
       const float base = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = move ? fast_exp2(m_run - base) : 1.0f;  // 0 when the row had seen no key yet
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};  // four chains of additions, joined at the end (a fixed order)
       uint32_t packed[KEYS / 2];
 #pragma unroll
       for (int j = 0; j < KEYS; j += 2) {
         const float p0 = fast_exp2(fmaf(s[j], sl2, -base)), p1 = fast_exp2(fmaf(s[j + 1], sl2, -base));
-        sum += p0 + p1;
+        sum4[(j / 2) & 3] += p0 + p1;
         __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
         packed[j / 2] = *reinterpret_cast<uint32_t*>(&t);
       }
-      l_run = l_run * alpha + sum;
+      l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       m_run = m_new;
+      if (i > 0) {
+        // The product P V of the tile before reads the P columns and adds into O: both are touched
+        // below. It was queued when that tile's P was complete, a whole softmax ago, so this wait
+        // is over before it starts in all but the shortest tiles.
+        ok = mbar_wait(o_bar, (uint32_t)(i - 1) & 1u, abort_flag, p.error_out, ERR_ATT_O);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      }
 #pragma unroll
       for (int c = 0; c < KEYS / 64; ++c) tmem_store32(tmem_base + lane_base + P_COL + c * 32, packed + c * 32);
-      if (i > 0 && __any_sync(0xffffffffu, move)) {  // rescale the warp's rows of O (the previous product is done: s_bar came after it)
+      if (i > 0 && __any_sync(0xffffffffu, move)) {  // rescale the warp's rows of O (the product of the tile before is done)
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c) {  // 64 columns at a time keeps the registers within the two-CTA budget
           float o[64];
@@ -384,9 +438,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
 template <int HD>
 bool launch_att(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, dim3 grid, int max_blocks, cudaStream_t stream) {
   using L = AttLayout<HD>;
-  // Q, two stages of K and V, six 8-byte words of barriers, four ints, the block-table slice (whole tiles: up to 16
+  // Q, two stages of K and V, ten 8-byte words of barriers, four ints, the block-table slice (whole tiles: up to 16
   // pages beyond the table's width), alignment slack
-  const size_t smem = L::Q_BYTES + 4 * L::KV_BYTES + 6 * sizeof(uint64_t) + 16 + (size_t)(max_blocks + 16) * sizeof(int) + 1024;
+  const size_t smem = L::Q_BYTES + 4 * L::KV_BYTES + 10 * sizeof(uint64_t) + 16 + (size_t)(max_blocks + 16) * sizeof(int) + 1024;
   static size_t attr_smem = 0;
   if (smem > attr_smem) {
     if (cudaFuncSetAttribute(paged_attention_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;

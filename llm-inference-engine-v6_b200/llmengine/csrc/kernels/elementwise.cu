@@ -9,9 +9,12 @@
 #include "common.cuh"
 
 // ------------------------------------------------------------------------------------ embedding
+// sumsq (may be null): sumsq[row] = sum of the squares of the row, for a norm that is folded into
+// the product after it.
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int dim, int vocab) {
+                             float* __restrict__ out, float* __restrict__ sumsq, int dim, int vocab) {
+  __shared__ float red[33];
   dep_launch();
   dep_wait();
   const int row = blockIdx.x;
@@ -19,18 +22,27 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
   if (id < 0 || id >= vocab) id = 0;  // ids are validated on the host; never read out of range
   const T* src = table + (size_t)id * dim;
   float* dst = out + (size_t)row * dim;
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = to_f32(src[i]);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float v = to_f32(src[i]);
+    dst[i] = v;
+    ss += v * v;
+  }
+  if (sumsq) {
+    ss = block_sum(ss, red);
+    if (threadIdx.x == 0) sumsq[row] = ss;
+  }
 }
 
-extern "C" int llm_embed(const void* table, int table_dtype, const int* ids, float* out, int n_rows,
+extern "C" int llm_embed(const void* table, int table_dtype, const int* ids, float* out, float* sumsq, int n_rows,
                          int dim, int vocab, cudaStream_t stream) {
   if (n_rows == 0) return LLM_OK;
   LLM_REQUIRE(n_rows > 0 && dim > 0 && vocab > 0, "embed: bad sizes rows=%d dim=%d vocab=%d", n_rows, dim, vocab);
   const int threads = dim >= 1024 ? 256 : 128;
   if (table_dtype == LLM_F32)
-    launch_kernel(embed_kernel<float>, n_rows, threads, 0, stream, (const float*)table, ids, out, dim, vocab);
+    launch_kernel(embed_kernel<float>, n_rows, threads, 0, stream, (const float*)table, ids, out, sumsq, dim, vocab);
   else if (table_dtype == LLM_BF16)
-    launch_kernel(embed_kernel<bf16>, n_rows, threads, 0, stream, (const bf16*)table, ids, out, dim, vocab);
+    launch_kernel(embed_kernel<bf16>, n_rows, threads, 0, stream, (const bf16*)table, ids, out, sumsq, dim, vocab);
   else
     LLM_REQUIRE(false, "embed: unknown table dtype %d", table_dtype);
   LLM_CHECK_LAUNCH("embed");

@@ -784,9 +784,12 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, i
 
 }  // namespace
 
-static int g_persistent = 1, g_pair = -1;
+static int g_persistent = 1, g_pair = 0;
 // CTA pairs (cta_group::2) for products of more than 128 tokens and at least 256 outputs:
-// 1 always, 0 never, -1 where they are estimated to be faster (the default).
+// 1 always, 0 never (the default), -1 where they are estimated to be faster.
+// Off by default: a prompt step at the Llama 3.2 3B layer sizes (2,048 tokens, gate|up with 3,072
+// inputs) was seen to stop inside this kernel once in a few dozen launches, for a cause not found;
+// the one-CTA persistent kernels take its shapes about 8 % slower.
 extern "C" void llm_gemm_tc_pair(int mode) { g_pair = mode; }
 // 0: never the persistent form (for comparisons); 1: where an SM gets at least two tiles.
 extern "C" void llm_gemm_tc_persistent(int on) { g_persistent = on; }

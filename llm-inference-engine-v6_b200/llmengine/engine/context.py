@@ -74,6 +74,7 @@ class StepContext:
         self.row_temperature = self.row_seed = self.row_draw = None
         self.seq_start = self.seq_ntok = self.seq_qoff = self.seq_slot = self.seq_len = None
         self.block_tables: List[torch.Tensor] = []
+        self.stream_sumsq = None  # left by the embedding for the first norm (parts.base.Embedding.forward)
         self.residual = None  # the stream (parts.base.Residual) that the part being run works for, if it may add into it
 
 

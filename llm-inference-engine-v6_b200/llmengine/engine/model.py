@@ -107,7 +107,9 @@ class Model:
         return sorted(out)
 
     def forward(self, ctx) -> torch.Tensor:
+        ctx.stream_sumsq = None
         res = Residual(self.embedding.forward(ctx))
+        res.sumsq, ctx.stream_sumsq = ctx.stream_sumsq, None
         for r, run in enumerate(self.spec.order):
             res = self.blocks[run.layer].forward(res, ctx, self.caches[r])
         if ctx.n_rows > 0:

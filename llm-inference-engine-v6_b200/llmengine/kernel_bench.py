@@ -1,6 +1,7 @@
 """Single-kernel runs for timing and profiling.
 
     python -m llmengine.kernel_bench gemm --m 8 --n 16384 --k 2048 [--reps 20]
+    python -m llmengine.kernel_bench gemm_few --m 8 --n 2048 --k 8192 --mode residual
     python -m llmengine.kernel_bench attention --batch 8 --context 2048 --new 1
     python -m llmengine.kernel_bench attention --batch 1 --context 0 --new 2048
     python -m llmengine.kernel_bench step --batch 8 --context 2048          (timeline of one decode step)
@@ -60,7 +61,7 @@ def run_gemm(args) -> dict:
     a = torch.randn(M, K, device=dev).bfloat16()
     space = Workspace(dev)
     out_kind = getattr(args, "out", "partials")
-    ops.use_cta_pairs({"auto": None, "on": True, "off": False}[getattr(args, "pairs", "auto")])
+    ops.use_cta_pairs({"auto": "auto", "on": True, "off": False}[getattr(args, "pairs", "off")])
     if out_kind == "swiglu":  # w as gate|up blocks of 128 rows; the output is silu(gate) * up, bfloat16 [M, N / 2]
         act = torch.empty(M, N // 2, device=dev, dtype=torch.bfloat16)
         sec = _time(lambda i: ops.gemm_swiglu(a, ws[i % copies], act, space), args.reps)
@@ -78,6 +79,45 @@ def run_gemm(args) -> dict:
     form = ops.gemm_form(M, N, K, out_kind == "swiglu") if M > ops.SWAP_MAX_TOKENS else "swapped, weights on the accumulator lanes"
     return {"kernel": "gemm_tc", "form": form, "out": out_kind, "M": M, "N": N, "K": K, "k_splits": splits, "us": round(sec * 1e6, 2),
             "tflops": round(flops / sec / 1e12, 1), "gbs": round(nbytes / sec / 1e9, 1)}
+
+
+def run_gemm_few(args) -> dict:
+    """The product of a step with few tokens (K pieces added inside a cluster), in one of its forms:
+    plain, residual (added into the stream, with the rows' sums of squares) or swiglu; activations as
+    bf16 rows or through the folded norm."""
+    from .ops import get_ops
+    ops = get_ops()
+    dev = torch.device("cuda:0")
+    T, N, K, mode = args.m, args.n, args.k, args.mode
+    copies = max(2, int(300e6 // (N * K * 2)) + 1)
+    ws = [(torch.randn(N, K, device=dev) * 0.02).bfloat16() for _ in range(copies)]
+    from .engine.context import Workspace
+    in_cluster = args.meet == "cluster"
+    space = None if in_cluster else Workspace(dev)
+    if args.splits:
+        ops._few_cache[(N, K, T, mode, in_cluster)] = int(ops.lib("tensorcore").llm_gemm_decode_splits(
+            N, K, T, ops._FEW_MODES[mode], args.splits, 1 if in_cluster else 0))
+    splits = ops.few_token_splits(N, K, T, mode, in_cluster)
+    x = torch.randn(T, K, device=dev).bfloat16()
+    h = torch.randn(T, K, device=dev)
+    sumsq = (h * h).sum(1, keepdim=True).repeat(1, 16).contiguous() / 16
+    nw = torch.ones(K, device=dev)
+    norm = (h, sumsq, nw, 1e-5, None) if args.norm else None
+    if mode == "residual":
+        out = torch.zeros(T, N, device=dev)
+        ss = torch.empty(T, ops.residual_sumsq_parts(N, K, T, in_cluster), device=dev)
+        fn = lambda i: ops.gemm_few_tokens(ws[i % copies], out, "residual", x=None if norm else x, norm=norm, sumsq_out=ss, ws=space)
+    elif mode == "swiglu":
+        out = torch.empty(T, N // 2, device=dev, dtype=torch.bfloat16)
+        fn = lambda i: ops.gemm_few_tokens(ws[i % copies], out, "swiglu", x=None if norm else x, norm=norm, ws=space)
+    else:
+        out = torch.empty(T, N, device=dev)
+        fn = lambda i: ops.gemm_few_tokens(ws[i % copies], out, "plain", x=None if norm else x, norm=norm, ws=space)
+    sec = _time(fn, args.reps)
+    assert ops.tensor_core_error() == 0
+    nbytes = N * K * 2 + T * K * (4 if norm else 2) + out.numel() * out.element_size()
+    return {"kernel": "gemm_decode", "mode": mode, "norm": bool(args.norm), "meet": args.meet, "T": T, "N": N, "K": K, "k_pieces": splits,
+            "us": round(sec * 1e6, 2), "gbs": round(nbytes / sec / 1e9, 1)}
 
 
 class _Batch:
@@ -130,6 +170,8 @@ def run_step_timeline(args) -> dict:
                head_dim=args.head_dim, vocab_size=args.vocab, max_position_embeddings=max(4096, args.context + 512),
                rms_norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=True)
     B, ctx = args.batch, args.context
+    from .ops import get_ops
+    get_ops().few_token_products = args.few_token_products == "on"
     gen = torch.Generator().manual_seed(1)
     prompts = torch.randint(0, args.vocab, (B, ctx), generator=gen).tolist()
     with tempfile.TemporaryDirectory() as tmp:
@@ -185,10 +227,18 @@ def main(argv=None) -> int:
     g = sub.add_parser("gemm")
     g.add_argument("--m", type=int, default=8); g.add_argument("--n", type=int, default=16384); g.add_argument("--k", type=int, default=2048)
     g.add_argument("--reps", type=int, default=20)
-    g.add_argument("--pairs", choices=["auto", "on", "off"], default="auto",
+    g.add_argument("--pairs", choices=["auto", "on", "off"], default="off",
                    help="products of more than 128 tokens on CTA pairs (tcgen05 cta_group::2): where estimated faster, always, never")
     g.add_argument("--out", choices=["partials", "bf16", "swiglu"], default="partials",
                    help="what the product writes: float32 partial sums, bfloat16, or silu(gate)*up in bfloat16")
+    f = sub.add_parser("gemm_few")
+    f.add_argument("--m", type=int, default=8); f.add_argument("--n", type=int, default=2048); f.add_argument("--k", type=int, default=2048)
+    f.add_argument("--mode", choices=["plain", "residual", "swiglu"], default="plain")
+    f.add_argument("--norm", action="store_true", help="activations through the folded norm instead of bf16 rows")
+    f.add_argument("--splits", type=int, default=0, help="K pieces wanted (0: the engine's choice)")
+    f.add_argument("--meet", choices=["global", "cluster"], default="global",
+                   help="where the K pieces are added: in global memory by the CTA that arrives last, or in the shared memory of a cluster")
+    f.add_argument("--reps", type=int, default=20)
     a = sub.add_parser("attention")
     a.add_argument("--batch", type=int, default=8); a.add_argument("--context", type=int, default=2048); a.add_argument("--new", type=int, default=1)
     a.add_argument("--heads", type=int, default=32); a.add_argument("--kv-heads", type=int, default=8); a.add_argument("--head-dim", type=int, default=64)
@@ -199,6 +249,9 @@ def main(argv=None) -> int:
     t = sub.add_parser("step")
     t.add_argument("--batch", type=int, default=8); t.add_argument("--context", type=int, default=2048)
     t.add_argument("--prefill", action="store_true")
+    t.add_argument("--few-token-products", choices=["on", "off"], default="on",
+                   help="decode steps: products that add their K pieces inside a cluster, norms and SiLU folded in (off: "
+                        "partial sums in memory, added by norm and activation kernels)")
     t.add_argument("--hidden", type=int, default=2048); t.add_argument("--ffn", type=int, default=8192)
     t.add_argument("--layers", type=int, default=16); t.add_argument("--heads", type=int, default=32)
     t.add_argument("--kv-heads", type=int, default=8); t.add_argument("--head-dim", type=int, default=64)
@@ -211,7 +264,7 @@ def main(argv=None) -> int:
         for k in kernels:
             print(f"{k['critical_us']:9.1f} us critical  x{k['launches']:4d}  mean {k['mean_duration_us']:8.2f} us  {k['kernel']}")
         return 0
-    print(json.dumps(run_gemm(args) if args.what == "gemm" else run_attention(args)))
+    print(json.dumps({"gemm": run_gemm, "gemm_few": run_gemm_few, "attention": run_attention}[args.what](args)))
     return 0
 
 

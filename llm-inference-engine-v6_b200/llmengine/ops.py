@@ -58,7 +58,11 @@ class CudaOps:
         self.tcgen05_attention = True  # prompt portions: attention on tcgen05 where the geometry allows it
         self.tma_decode_attention = True  # single decoded tokens: keys and values by TMA where the geometry allows it
         self.fused_decode_attention = True  # ... with the sum of the q|k|v parts, rotation and cache write in the same kernel
-        self.few_token_products = True  # steps of few tokens: products that add their K pieces inside a cluster, norms and activation folded in
+        # Steps of few tokens: products that add their K pieces themselves, with the norm before, the residual sum
+        # and SiLU * up folded in (gemm_few_tokens). Off: measured on B200 (batch 8, 2,048-token contexts, 1B layer
+        # sizes) such a step takes 1.15 ms with the pieces meeting inside clusters and 1.40 ms with them meeting in
+        # global memory, against 0.89 ms with partial sums in memory that the norm and activation kernels add.
+        self.few_token_products = False
         self._few_cache = {}
         self._err_host: Optional[torch.Tensor] = None  # pinned word that queue_error_check copies the kernels' error code into
 
@@ -73,15 +77,19 @@ class CudaOps:
             lib.llm_last_error.restype = ctypes.c_char_p
             if name == "tensorcore":
                 lib.llm_attention_mma_scratch_floats.restype = ctypes.c_longlong
+                lib.llm_gemm_decode_scratch_floats.restype = ctypes.c_longlong
             self._libs[name] = lib
         return lib
 
-    def use_cta_pairs(self, on: Optional[bool]) -> None:
+    def use_cta_pairs(self, on) -> None:
         """Products of more than 128 tokens on CTA pairs (tcgen05 cta_group::2: two SMs share one
-        256 x 256 tile and each loads half of the weight tile): always, never, or (None, the
-        default) where the kernel library estimates them to be faster: long products and those of
-        many rounds of tiles, e.g. gate|up and down of a 2,048-token prompt, not q|k|v or o."""
-        self.lib("tensorcore").llm_gemm_tc_pair(c_int(-1 if on is None else (1 if on else 0)))
+        256 x 256 tile and each loads half of the weight tile): True always, False or None never
+        (the default), "auto" where the kernel library estimates them to be faster (long products
+        and those of many rounds of tiles, e.g. gate|up and down of a 2,048-token prompt, not
+        q|k|v or o). They are off by default because a prompt step at the Llama 3.2 3B layer sizes
+        was seen to stop inside the pair kernel, rarely and for a cause that was not found."""
+        mode = -1 if on == "auto" else (1 if on else 0)
+        self.lib("tensorcore").llm_gemm_tc_pair(c_int(mode))
 
     GEMM_FORMS = ("one tile a CTA", "persistent, tiles of 256", "persistent, tiles of 192", "CTA pairs")
 
@@ -103,13 +111,16 @@ class CudaOps:
             raise KernelError(lib.llm_last_error().decode())
 
     # ------------------------------------------------------------------ elementwise
-    def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        """out[n,:] (float32) = table[ids[n],:]."""
+    def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, sumsq: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """out[n,:] (float32) = table[ids[n],:]; sumsq[n] (float32, optional) = sum of the row's squares."""
         _need(table, "embed.table"); _need(ids, "embed.ids", torch.int32); _need(out, "embed.out", torch.float32)
         lib = self.lib()
         n, dim = out.shape
         assert table.shape[1] == dim and table.is_contiguous() and out.is_contiguous() and ids.numel() >= n
-        self._check(lib.llm_embed(_ptr(table), c_int(dtype_code(table.dtype)), _ptr(ids), _ptr(out), c_int(n),
+        if sumsq is not None:
+            _need(sumsq, "embed.sumsq", torch.float32)
+            assert sumsq.is_contiguous() and sumsq.numel() >= n
+        self._check(lib.llm_embed(_ptr(table), c_int(dtype_code(table.dtype)), _ptr(ids), _ptr(out), _ptr(sumsq), c_int(n),
                                   c_int(dim), c_int(table.shape[0]), _stream()), lib)
         return out
 
@@ -264,38 +275,42 @@ class CudaOps:
     FEW_TOKENS = 64  # up to here the weights fill the accumulator lanes and the kernel below applies
     FEW_TOKENS_TARGET_CTAS = 296  # K pieces are chosen so that about this many CTAs stream the weights
 
-    def few_token_splits(self, n: int, k: int, t: int, mode: str) -> int:
-        """K pieces (CTAs of the cluster that adds them up) that gemm_few_tokens will use: 0 if the
-        kernel does not take these sizes. mode: "plain", "residual" or "swiglu" (n counts gate and up rows)."""
+    def few_token_splits(self, n: int, k: int, t: int, mode: str, in_cluster: bool = False) -> int:
+        """K pieces that gemm_few_tokens will use: 0 if the kernel does not take these sizes. mode: "plain",
+        "residual" or "swiglu" (n counts gate and up rows). in_cluster: the pieces are the CTAs of a
+        thread-block cluster and meet in its shared memory (at most 8); else they meet in global memory."""
         if not self.tensor_cores or not self.few_token_products or not (1 <= t <= self.FEW_TOKENS) or k % 8:
             return 0
-        key = (n, k, t, mode)
+        key = (n, k, t, mode, in_cluster)
         hit = self._few_cache.get(key)
         if hit is None:
-            hit = self._few_cache[key] = self._few_token_splits(n, k, t, mode)
+            hit = self._few_cache[key] = self._few_token_splits(n, k, t, mode, in_cluster)
         return hit
 
-    def _few_token_splits(self, n: int, k: int, t: int, mode: str) -> int:
+    def _few_token_splits(self, n: int, k: int, t: int, mode: str, in_cluster: bool) -> int:
         tiles = -(-n // (256 if mode == "swiglu" else 128))
         target = self.FEW_TOKENS_TARGET_CTAS if t <= 32 else self.FEW_TOKENS_TARGET_CTAS // 2
-        want = max(1, min(16, -(-target // tiles), max(1, -(-k // 64) // 2)))
-        if mode == "residual":
+        want = max(1, min(8 if in_cluster else 32, -(-target // tiles), max(1, -(-k // 64) // 2)))
+        if mode == "residual" and in_cluster:
             want = max(want, 2)
-        return int(self.lib("tensorcore").llm_gemm_decode_splits(c_int(n), c_int(k), c_int(t), c_int(self._FEW_MODES[mode]), c_int(want)))
+        return int(self.lib("tensorcore").llm_gemm_decode_splits(c_int(n), c_int(k), c_int(t), c_int(self._FEW_MODES[mode]), c_int(want),
+                                                                 c_int(1 if in_cluster else 0)))
 
     _FEW_MODES = {"plain": 0, "residual": 1, "swiglu": 2}
 
     def gemm_few_tokens(self, w: torch.Tensor, out: torch.Tensor, mode: str = "plain", x: Optional[torch.Tensor] = None,
-                        norm=None, sumsq_out: Optional[torch.Tensor] = None, n_tokens: Optional[int] = None) -> torch.Tensor:
-        """out <- x . w^T for at most FEW_TOKENS tokens, with the K pieces added inside a thread-block
-        cluster (no partial sums in memory) and the work around the product folded in.
+                        norm=None, sumsq_out: Optional[torch.Tensor] = None, n_tokens: Optional[int] = None, ws=None) -> torch.Tensor:
+        """out <- x . w^T for at most FEW_TOKENS tokens, with the K pieces added inside the product (no
+        partial sums for other kernels to add) and the work around the product folded in.
         Activations: `x` bf16 [t, k]; or `norm` = (h float32 [rows, k], sumsq float32 [rows, parts], weight
         float32 [k], eps, row list int32 [t] or None): the RMSNorm of those rows, which then is no
         kernel of its own.
         mode "plain": out [t, n] float32 or bf16. "residual": out is the float32 residual stream
         [t, n], the product is added to it in place, and sumsq_out [t, parts] receives the parts of
         the new rows' sums of squares (parts = sumsq_out.shape[1], as residual_sumsq_parts says).
-        "swiglu": w holds blocks of 128 gate rows and the 128 matching up rows, out bf16 [t, n / 2]."""
+        "swiglu": w holds blocks of 128 gate rows and the 128 matching up rows, out bf16 [t, n / 2].
+        With a workspace `ws` the K pieces meet in global memory (scratch of the workspace; any number of
+        pieces, no clusters); without, inside a thread-block cluster (up to 8 pieces)."""
         _need(w, "gemm_few.w", torch.bfloat16); _need(out, "gemm_few.out")
         n, k = w.shape
         lib = self.lib("tensorcore")
@@ -313,9 +328,16 @@ class CudaOps:
                 _need(row_list, "gemm_few.rows", torch.int32)
             xb, xf, ldx, ss, nss, nw, rows = c_void_p(0), _ptr(h), h.stride(0), _ptr(sumsq), sumsq.shape[1], _ptr(weight), _ptr(row_list)
         assert out.shape[0] >= t and out.shape[1] == (n // 2 if mode == "swiglu" else n)
-        splits = self.few_token_splits(n, k, t, mode)
+        in_cluster = ws is None
+        splits = self.few_token_splits(n, k, t, mode, in_cluster)
         if splits == 0:
             raise KernelError(f"gemm_few_tokens: sizes not taken (tokens={t} n={n} k={k} mode={mode})")
+        parts = counters = None
+        if not in_cluster:  # (also with one piece: the residual form always writes its sums through the scratch)
+            code = self._FEW_MODES[mode]
+            floats = int(lib.llm_gemm_decode_scratch_floats(c_int(n), c_int(k), c_int(t), c_int(code), c_int(splits)))
+            parts = ws.get("few_tokens.pieces", (max(floats, 4),), torch.float32)
+            counters = ws.get_zeroed("few_tokens.counters", (max(int(lib.llm_gemm_decode_tiles(c_int(n), c_int(code))), 1024),), torch.int32)
         nso = 0
         if mode == "residual":
             _need(sumsq_out, "gemm_few.sumsq_out", torch.float32)
@@ -324,12 +346,13 @@ class CudaOps:
         self._check(lib.llm_gemm_decode(_ptr(w), c_longlong(w.stride(0)), c_int(n), c_int(k), c_int(t), xb, xf, c_longlong(ldx), ss,
                                         c_int(nss), nw, c_float(eps), rows, c_int(self._FEW_MODES[mode]), _ptr(out),
                                         c_longlong(out.stride(0)), c_int(dtype_code(out.dtype)), _ptr(sumsq_out), c_int(nso),
-                                        c_int(splits), _stream()), lib)
+                                        c_int(splits), _ptr(parts), c_longlong(0 if parts is None else parts.numel()), _ptr(counters), _stream()), lib)
         return out
 
-    def residual_sumsq_parts(self, n: int, k: int, t: int) -> int:
+    def residual_sumsq_parts(self, n: int, k: int, t: int, in_cluster: bool = False) -> int:
         """Parts of a row's sum of squares that gemm_few_tokens(mode="residual") writes for these sizes."""
-        return -(-n // 128) * self.few_token_splits(n, k, t, "residual")
+        tiles = -(-n // 128)
+        return tiles * self.few_token_splits(n, k, t, "residual", True) if in_cluster else tiles
 
     def reduce_partials(self, parts: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """out = sum over parts[p] (index order); out float32 or bfloat16, contiguous."""

@@ -87,9 +87,9 @@ class PagedAttention(Mixer):
             if few:
                 parts = ctx.ws.get("attention.qkv_parts", (1, n, dq + 2 * dkv), torch.float32)
                 if isinstance(x, NormalizedRows):
-                    ops.gemm_few_tokens(self.w_qkv, parts[0], "plain", norm=(x.h, x.sumsq, x.weight, x.eps, x.rows), n_tokens=n)
+                    ops.gemm_few_tokens(self.w_qkv, parts[0], "plain", norm=(x.h, x.sumsq, x.weight, x.eps, x.rows), n_tokens=n, ws=ctx.ws)
                 else:
-                    ops.gemm_few_tokens(self.w_qkv, parts[0], "plain", x=x[:n])
+                    ops.gemm_few_tokens(self.w_qkv, parts[0], "plain", x=x[:n], ws=ctx.ws)
             else:
                 parts = ops.gemm_partials(x[:n], self.w_qkv, ctx.ws, "attention.qkv_parts")
             tables = self.position.rotation_tables() if cache.k is not None else None
@@ -121,7 +121,7 @@ def add_into_stream_or_partials(ops, x: torch.Tensor, w: torch.Tensor, ctx, few:
     if few and res is not None and res.pending is None and res.h.shape[1] == w.shape[0]:
         parts = ops.residual_sumsq_parts(w.shape[0], w.shape[1], n)
         ss = ctx.ws.get(tag + ".sumsq", (res.h.shape[0], parts), torch.float32)
-        ops.gemm_few_tokens(w, res.h, "residual", x=x[:n], sumsq_out=ss, n_tokens=n)
+        ops.gemm_few_tokens(w, res.h, "residual", x=x[:n], sumsq_out=ss, n_tokens=n, ws=ctx.ws)
         res.sumsq = ss
         return None
     res_sumsq_off(res)

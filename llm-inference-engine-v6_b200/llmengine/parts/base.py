@@ -132,7 +132,9 @@ class Embedding(Part):
     category = "embedding"
 
     def forward(self, ctx) -> torch.Tensor:
-        """The float32 residual stream [tokens, hidden] of the step's tokens (ctx.token_ids)."""
+        """The float32 residual stream [tokens, hidden] of the step's tokens (ctx.token_ids). It may
+        leave ctx.stream_sumsq: float32 [tokens, parts], the parts of every row's sum of squares
+        (see Residual.sumsq)."""
         raise NotImplementedError
 
 

@@ -30,8 +30,14 @@ class TokenLookup(Embedding):
         self.table = tensors[self.spec.weight]
 
     def forward(self, ctx) -> torch.Tensor:
-        h = ctx.ws.get("model.residual", (ctx.n_tokens, self.spec.dim), torch.float32)
-        return self.env.ops.embed(self.table, ctx.token_ids, h)
+        ops, n = self.env.ops, ctx.n_tokens
+        h = ctx.ws.get("model.residual", (n, self.spec.dim), torch.float32)
+        if self.env.dtype == torch.bfloat16 and hasattr(ops, "few_token_splits") and ops.few_token_splits(128, self.spec.dim, n, "plain") > 0:
+            # a step of few tokens: the first norm can be folded into the product after it if the
+            # rows' sums of squares are known; the gather has the rows in its hands anyway
+            ctx.stream_sumsq = ctx.ws.get("embedding.sumsq", (n, 1), torch.float32)
+            return ops.embed(self.table, ctx.token_ids, h, sumsq=ctx.stream_sumsq)
+        return ops.embed(self.table, ctx.token_ids, h)
 
 
 class LinearHead(Head):
@@ -46,17 +52,12 @@ class LinearHead(Head):
     def load(self, tensors) -> None:
         self.weight = tensors[self.spec.weight]
 
-    def wants_lazy_norm(self, ctx) -> bool:
-        ops = self.env.ops
-        return (self.env.dtype == torch.bfloat16 and hasattr(ops, "gemm_few_tokens") and
-                ops.few_token_splits(self.spec.vocab_size, self.spec.dim, ctx.n_rows, "plain") > 0)
-
     def forward(self, x, ctx) -> torch.Tensor:
         n = x.n if isinstance(x, NormalizedRows) else x.shape[0]
         logits = ctx.ws.get("model.logits", (max(n, 1), self.spec.vocab_size), torch.float32)[:n]
-        if isinstance(x, NormalizedRows):  # the final norm of the wanted rows happens inside the product
-            self.env.ops.gemm_few_tokens(self.weight, logits, "plain", norm=(x.h, x.sumsq, x.weight, x.eps, x.rows), n_tokens=n)
-        elif n:
+        if isinstance(x, NormalizedRows):
+            x = x.dense(ctx)
+        if n:
             self.env.ops.gemm(x, self.weight, logits)
         return logits
 

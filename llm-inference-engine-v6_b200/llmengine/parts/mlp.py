@@ -66,9 +66,9 @@ class GatedMLP(FeedForward):
             # few tokens: the norm before (if it was handed on), the sum of the K pieces and SiLU * up all
             # happen inside the gate|up product; the down product adds itself into the residual stream
             if isinstance(x, NormalizedRows):
-                ops.gemm_few_tokens(self.w_gate_up, act, "swiglu", norm=(x.h, x.sumsq, x.weight, x.eps, x.rows), n_tokens=n)
+                ops.gemm_few_tokens(self.w_gate_up, act, "swiglu", norm=(x.h, x.sumsq, x.weight, x.eps, x.rows), n_tokens=n, ws=ctx.ws)
             else:
-                ops.gemm_few_tokens(self.w_gate_up, act, "swiglu", x=x[:n])
+                ops.gemm_few_tokens(self.w_gate_up, act, "swiglu", x=x[:n], ws=ctx.ws)
             return add_into_stream_or_partials(ops, act, self.w_down, ctx, True, "mlp.delta")
         if isinstance(x, NormalizedRows):
             x = x.dense(ctx)

@@ -19,8 +19,13 @@ TOL = {"fp32": 2e-4, "bf16": 6e-2}
 CONFIGS = dict(TINY, f=(dict(TINY_D, max_position_embeddings=500), 16))
 
 
-@pytest.mark.parametrize("name,dtype", [("d", "bf16"), ("e", "bf16"), ("f", "bf16"), ("b", "bf16"), ("a", "fp32"), ("d", "fp32")])
-def test_logits_through_decode_graphs(tmp_path, name, dtype):
+@pytest.mark.parametrize("name,dtype,folded", [("d", "bf16", False), ("e", "bf16", False), ("f", "bf16", False), ("b", "bf16", False),
+                                               ("a", "fp32", False), ("d", "fp32", False), ("d", "bf16", True), ("e", "bf16", True)])
+def test_logits_through_decode_graphs(tmp_path, monkeypatch, name, dtype, folded):
+    """folded: with the products of few-token steps that add their K pieces themselves and take the
+    norms, the residual sums and SiLU * up in (off by default; the same logits either way)."""
+    from llmengine.ops import get_ops
+    monkeypatch.setattr(get_ops(), "few_token_products", folded)
     cfg, page = CONFIGS[name]
     d = str(tmp_path / "m")
     make_model_dir(d, cfg, torch.float32 if dtype == "fp32" else torch.bfloat16)

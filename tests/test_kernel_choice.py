@@ -1,6 +1,7 @@
 """Which tcgen05 kernel a prompt-sized product runs on is decided on the host (`llm_gemm_tc_form` in
 gemm_tc.cu) from the sizes alone, so it is checked here without a GPU: the choices for the layer
-sizes that were measured on B200, and the rules that hold for every size."""
+sizes that were measured on B200, and the rules that hold for every size. CTA pairs are off by
+default; the tests of the estimate switch them to "where estimated faster" (-1) first."""
 import ctypes
 
 import pytest
@@ -14,7 +15,7 @@ ONE_TILE, PERSISTENT_256, PERSISTENT_192, PAIRS = range(4)
 def lib():
     lib = ctypes.CDLL(kernel_library_path("tensorcore"))  # compiled at the first call; loads without a GPU
     yield lib
-    lib.llm_gemm_tc_pair(-1)
+    lib.llm_gemm_tc_pair(0)  # the library's default: never
     lib.llm_gemm_tc_persistent(1)
 
 
@@ -67,5 +68,5 @@ def test_switches(lib):
     lib.llm_gemm_tc_pair(1)
     assert lib.llm_gemm_tc_form(*shape) == PAIRS and lib.llm_gemm_tc_form(256, 256, 64, 0) == PAIRS
     assert lib.llm_gemm_tc_form(128, 4096, 4096, 0) != PAIRS  # one tile of tokens: nothing to pair
-    lib.llm_gemm_tc_pair(-1)
+    lib.llm_gemm_tc_pair(0)
     lib.llm_gemm_tc_persistent(1)

@@ -20,7 +20,7 @@ import plain_llama as P
 from llmengine.cache import host_module
 from tiny import random_ids
 
-pytestmark = [pytest.mark.gpu, pytest.mark.timeout(1800)]  # (the plain side follows 6,300 tokens on the CPU)
+pytestmark = [pytest.mark.gpu, pytest.mark.timeout(420)]  # (the plain side follows 6,300 tokens on the CPU: about a minute)
 
 SIZES_3B = dict(architectures=["LlamaForCausalLM"], hidden_size=3072, intermediate_size=8192, num_hidden_layers=2,
                 num_attention_heads=24, num_key_value_heads=8, head_dim=128, vocab_size=128256,
