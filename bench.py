@@ -317,6 +317,72 @@ def run_ours(args):
     return 0
 
 
+def run_workload(args):
+    """The serving workloads that go with the larger geometries: `serve` = 32 requests with prompts of
+    16 to 2,048 random tokens and 256 new tokens each through the continuous-batching scheduler;
+    `long` = one prompt of 16,384 tokens in portions of 2,048, then 512 decoded tokens. Prints one JSON
+    line of its own (not the contract's line): tokens a second over the whole run, and how much of the
+    wall time of the steps the device was busy (the rest is the host: planning, batch building,
+    launching the kernels of prompt and mixed steps one by one)."""
+    import torch
+    import llmengine
+
+    torch.cuda.set_device(0)
+    base, full_layers, model_name, _ = GEOMETRIES[args.geometry]
+    layers = args.layers if args.layers > 0 else full_layers
+    gen = torch.Generator().manual_seed(2)
+    if args.workload == "serve":
+        lens = torch.randint(16, 2049, (32,), generator=gen).tolist()
+        new, budget, conc, max_pos = 256, args.budget, 32, 8192
+    else:
+        lens, new, budget, conc, max_pos = [16384], 512, 2048, 1, 32768
+    g = dict(base, num_hidden_layers=layers, max_position_embeddings=max_pos)
+    tmp = tempfile.TemporaryDirectory(prefix="llmengine_bench_")
+    llmengine.write_random_model(tmp.name, g, seed=0, dtype=torch.bfloat16)
+    pages = sum((n + new + BLOCK_SIZE - 1) // BLOCK_SIZE + 1 for n in lens) + 8
+    eng = llmengine.Engine(tmp.name, "bf16", block_size=BLOCK_SIZE, num_blocks=pages, max_concurrent=conc)
+    eng.configure_cache()
+    prompts = [torch.randint(0, g["vocab_size"], (n,), generator=gen).tolist() for n in lens]
+
+    def run():
+        sch = llmengine.ContinuousBatchScheduler(eng, None, max_concurrent=conc, max_prefill_tokens_per_step=budget)
+        for p in prompts:
+            sch.enqueue(p, new)
+        wall = dev = 0.0
+        steps = kinds = 0
+        torch.cuda.synchronize()
+        t_all = time.perf_counter()
+        while True:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            a.record()
+            more = sch.step()
+            b.record()
+            b.synchronize()
+            wall += time.perf_counter() - t0
+            dev += a.elapsed_time(b) / 1e3
+            steps += 1
+            if not more:
+                break
+        total = time.perf_counter() - t_all
+        sch.core.finalize()
+        out = sum(len(r.token_ids) - r.prompt_len for r in sch.results)
+        assert all(r.finish_reason == "length" for r in sch.results)
+        return total, wall, dev, steps, out
+
+    run()  # warm-up: kernels loaded, graphs captured, workspaces sized
+    total, wall, dev, steps, out = run()
+    code = eng.ops.tensor_core_error()
+    if code:
+        raise RuntimeError(f"a tensor-core kernel gave up a wait (code {code})")
+    print(json.dumps({"workload": args.workload, "model": model_name, "layers": layers, "requests": len(lens),
+                      "prompt_tokens": sum(lens), "new_tokens": out, "budget": budget, "steps": steps,
+                      "seconds": round(total, 4), "tokens_per_s": round((sum(lens) + out) / total, 1),
+                      "decoded_tokens_per_s": round(out / total, 1),
+                      "device_busy_share": round(dev / wall, 4), "host_share": round(1 - dev / wall, 4)}), flush=True)
+    return 0
+
+
 def run_reference(args):
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
 
@@ -390,6 +456,9 @@ def main():
     ap.add_argument("--no-points", dest="points", action="store_false", help="skip the batch 1 and 64 points")
     ap.add_argument("--skip", default="", help="comma list of parts to leave out: decode,e2e,prefill,points (for profiling runs)")
     ap.add_argument("--no-cuda-graphs", dest="graphs", action="store_false", help="launch decode steps kernel by kernel")
+    ap.add_argument("--workload", choices=["decode", "serve", "long"], default="decode",
+                    help="decode: the contract's line (default). serve / long: the workloads of the 3B and 8B configurations, a line of their own")
+    ap.add_argument("--budget", type=int, default=2048, help="serve: prompt tokens a step (max_prefill_tokens_per_step)")
     ap.add_argument("--reference-setup-limit", type=float, default=900.0, help="seconds the reference arm may spend filling contexts")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
@@ -400,6 +469,8 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload != "decode":
+        return run_workload(args)
     return run_ours(args)
 
 

@@ -1,10 +1,12 @@
 """Builds the package's native code in-tree, at first use, and finds it again afterwards.
 
-Two kinds of library:
+Three kinds of library:
   * kernel libraries: CUDA sources under csrc/kernels compiled by nvcc for sm_100a only into a
     shared object of `extern "C"` launchers (loaded with ctypes);
   * the host library: C++17 sources under csrc/host (cache manager, batch builder, scheduler)
-    compiled by g++ into a pybind11 module.
+    compiled by g++ into a pybind11 module;
+  * the reference library: plain C++ twins of the kernels under csrc/ref (scalar loops on host
+    memory), which only the tests load.
 
 A library's file name carries a hash of its sources and flags, so an up-to-date build is found
 without compiling and a stale one is never loaded. Objects are built in parallel; while a build
@@ -40,6 +42,8 @@ KERNEL_LIBRARIES: Dict[str, List[str]] = {
     "tensorcore": ["status.cu", "gemm_tc.cu", "gemm_decode.cu", "attention_mma.cu", "attention_tc.cu", "attention_decode.cu"],
 }
 HOST_SOURCES = ["cache_manager.cpp", "scheduler.cpp", "bindings.cpp"]
+REF_DIR = os.path.join(HERE, "ref")
+REF_SOURCES = ["kernels_ref.cpp"]  # plain C++ twins of the kernels: what the kernel tests compare with
 
 
 class BuildError(RuntimeError):
@@ -183,9 +187,27 @@ def host_module_path(build: bool = True) -> str:
     return out
 
 
+def reference_library_path(build: bool = True) -> str:
+    """Path of the plain C++ twins of the kernels (a shared library of `extern "C"` functions on host
+    memory, loaded with ctypes by the tests); compiled first if needed and allowed."""
+    srcs = [os.path.join(REF_DIR, s) for s in REF_SOURCES]
+    flags = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-fno-fast-math", "-Wall", "-Wextra"]
+    out = os.path.join(_build_dir(), f"libllmengine_ref_{_hash(srcs, flags, [])}.so")
+    if os.path.isfile(out):
+        return out
+    if not build:
+        raise BuildError("the reference library is not built")
+    cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+    if not cxx:
+        raise BuildError("no C++ compiler found (g++)")
+    _compile_and_link([cxx], srcs, flags, ["-shared"], out, "plain C++ twins of the kernels")
+    _drop_stale(os.path.dirname(out), "libllmengine_ref_", out)
+    return out
+
+
 def build_all() -> Dict[str, str]:
     """Builds every library; returns name -> path."""
-    out = {"host": host_module_path()}
+    out = {"host": host_module_path(), "ref": reference_library_path()}
     for name in KERNEL_LIBRARIES:
         out[name] = kernel_library_path(name)
     return out
