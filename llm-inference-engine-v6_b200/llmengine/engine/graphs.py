@@ -10,6 +10,7 @@ buffer and sampler output, so that nothing it points at is ever moved by a later
 """
 from __future__ import annotations
 
+import time
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -115,7 +116,9 @@ class DecodeGraphs:
         c.refill(entries)
         c.graph.replay()
         eng.ops.launches += c.kernels
+        t0 = time.perf_counter()
         torch.cuda.current_stream().synchronize()
+        eng.sampler.wait_seconds += time.perf_counter() - t0
         eng.raise_if_kernel_error()
         self.h2d_bytes, self.d2h_bytes = c.buffers.h2d_bytes, 4 * cap
         self.last = c

@@ -7,6 +7,7 @@ so the same request yields the same tokens whatever else is batched with it. T =
 """
 from __future__ import annotations
 
+import time
 from typing import List, Optional
 
 import torch
@@ -14,6 +15,7 @@ import torch
 
 class Sampler:
     def __init__(self, ops, device: torch.device):
+        self.wait_seconds = 0.0  # host time spent waiting for the device to finish a step (statistics)
         self.ops, self.device = ops, device
         self._out: Optional[torch.Tensor] = None
         self._host: Optional[torch.Tensor] = None
@@ -55,7 +57,9 @@ class Sampler:
         _, host = self._buffers(n)
         host[:n].copy_(dev, non_blocking=True)
         if self.device.type == "cuda":
+            t0 = time.perf_counter()
             torch.cuda.current_stream().synchronize()
+            self.wait_seconds += time.perf_counter() - t0
         return host[:n].tolist()
 
     def greedy(self, logits: torch.Tensor) -> List[int]:
