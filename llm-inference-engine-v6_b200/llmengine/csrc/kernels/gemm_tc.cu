@@ -669,6 +669,12 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
   if (warp == 0) {
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
   }
+  // The pair leaves together, after BOTH halves of the pair-wide release: without this barrier one
+  // CTA can release and exit while the other has not yet executed its half, and with programmatic
+  // dependent launch the next kernel's CTA is placed on the freed SM at once and allocates tensor
+  // memory there while the pair-wide release that covers this SM is still half done. (A precaution:
+  // it did not end the rare stop for which this kernel is off by default.)
+  cluster_sync_all();
 }
 
 template <typename TO, bool SWIGLU>

@@ -9,6 +9,7 @@ to library or CPU code.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -78,6 +79,10 @@ class CudaOps:
             if name == "tensorcore":
                 lib.llm_attention_mma_scratch_floats.restype = ctypes.c_longlong
                 lib.llm_gemm_decode_scratch_floats.restype = ctypes.c_longlong
+                # "auto", "on" or "off" (see use_cta_pairs; for measurements, pairs are not safe to serve with)
+                pairs = os.environ.get("LLMENGINE_CTA_PAIRS", "").strip().lower()
+                if pairs in ("auto", "on", "off"):
+                    lib.llm_gemm_tc_pair(c_int({"auto": -1, "on": 1, "off": 0}[pairs]))
             self._libs[name] = lib
         return lib
 
