@@ -63,6 +63,7 @@ struct DecParams {
   int* error;
   // fused form only
   const float* qkv_parts; int n_parts; long long part_stride;  // [n_parts][tokens][(nq + 2 nkv) * hd], parts part_stride floats apart
+  RowScale rs;  // the 1/rms that the q|k|v sums are still owed (sumsq null: none)
   const float* cos_t; const float* sin_t;                       // [positions][hd / 2], or null: no rotation
   bf16* kcache; bf16* vcache;                                   // where the token's own key and value are written
 };
@@ -258,6 +259,7 @@ __global__ void __launch_bounds__(DEC_THREADS, (HD == 64 ? 4 : 2)) paged_attenti
       const int n_items = g * HALF + (own_key_here ? 2 * HALF : 0);
       const int width = (p.nq + 2 * p.nkv) * HD;
       const float* prow = p.qkv_parts + (size_t)tok * width;
+      const float row_sc = row_scale(p.rs, (size_t)tok);
       for (int c = tid; c < (ROWS - g) * (HD / 8); c += DEC_CONSUMERS)  // rows beyond the group are zeros
         *reinterpret_cast<uint4*>(q_s + (g + c / (HD / 8)) * L::Q_LD + (c % (HD / 8)) * 8) = make_uint4(0, 0, 0, 0);
       for (int item = tid; item < n_items; item += DEC_CONSUMERS) {
@@ -288,6 +290,8 @@ __global__ void __launch_bounds__(DEC_THREADS, (HD == 64 ? 4 : 2)) paged_attenti
             b += vb[u];
           }
         }
+        a *= row_sc;
+        b *= row_sc;
         float ra = a, rb = b;
         if (kind != 2 && p.cos_t) {
           const float cs = p.cos_t[(size_t)pos * HALF + i], sn = p.sin_t[(size_t)pos * HALF + i];
@@ -806,10 +810,12 @@ extern "C" int llm_paged_attention_decode_fused(const float* qkv_parts, int n_pa
                                                 const int* seq_start, const int* seq_qoff, const int* block_table,
                                                 int max_blocks, void* out, long long ld_out, int n_seqs, int nq, int nkv, int hd,
                                                 int page_size, float scale, int window, int n_splits, int split_keys,
-                                                float* scratch, int* done_count, cudaStream_t stream) {
+                                                float* scratch, int* done_count, const float* sumsq, int n_sumsq,
+                                                float inv_dim, float eps, cudaStream_t stream) {
   if (n_seqs == 0) return LLM_OK;
   LLM_REQUIRE(llm_attention_decode_supported(nq, nkv, hd, page_size, 8, ld_out),
               "attention_decode: geometry not supported (nq=%d nkv=%d hd=%d page=%d)", nq, nkv, hd, page_size);
+  LLM_REQUIRE(sumsq == nullptr || n_sumsq > 0, "attention_decode: a row scale needs its parts");
   LLM_REQUIRE(qkv_parts != nullptr && n_parts >= 1 && part_stride >= (long long)n_seqs * (nq + 2 * nkv) * hd,
               "attention_decode: bad partial sums");
   LLM_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "attention_decode: cos and sin come together");
@@ -819,6 +825,7 @@ extern "C" int llm_paged_attention_decode_fused(const float* qkv_parts, int n_pa
   p.scale = scale; p.out = (bf16*)out; p.ld_out = ld_out;
   p.n_splits = n_splits; p.split_keys = split_keys; p.done_count = done_count;
   p.qkv_parts = qkv_parts; p.n_parts = n_parts; p.part_stride = part_stride; p.cos_t = cos_t; p.sin_t = sin_t;
+  p.rs = RowScale{sumsq, n_sumsq, inv_dim, eps};
   p.kcache = (bf16*)kcache; p.vcache = (bf16*)vcache;
   return decode_common(p, kcache, vcache, n_cache_pages, n_seqs, hd, scratch, true, stream);
 }

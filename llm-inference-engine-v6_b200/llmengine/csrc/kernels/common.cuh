@@ -90,6 +90,22 @@ static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) 
 // has finished and its writes are visible. EVERY kernel calls dep_wait() before it reads what an
 // earlier kernel wrote and before its first global write. dep_launch() lets the next kernel's
 // blocks be scheduled once all blocks of this one have called it (or left).
+// A per-row scalar that a consumer of partial sums multiplies in: 1 / sqrt(sum_j sumsq[row, j] * inv_dim + eps),
+// the 1/rms of a norm whose weight the producer of the operand has already applied (a per-row scalar
+// commutes with a product over the row). sumsq null: 1.
+struct RowScale {
+  const float* sumsq;
+  int n;
+  float inv_dim, eps;
+};
+__device__ __forceinline__ float row_scale(const RowScale& rs, size_t row) {
+  if (rs.sumsq == nullptr) return 1.0f;
+  const float* part = rs.sumsq + row * (size_t)rs.n;
+  float sum = 0.f;
+  for (int j = 0; j < rs.n; ++j) sum += part[j];  // index order
+  return 1.0f / sqrtf(sum * rs.inv_dim + rs.eps);
+}
+
 __device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

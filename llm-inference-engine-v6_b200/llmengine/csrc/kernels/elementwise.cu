@@ -10,10 +10,11 @@
 
 // ------------------------------------------------------------------------------------ embedding
 // sumsq (may be null): sumsq[row] = sum of the squares of the row, for a norm that is folded into
-// the product after it.
+// the product after it; scaled (may be null): the row times next_w in bfloat16, that product's operand.
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, float* __restrict__ sumsq, int dim, int vocab) {
+                             float* __restrict__ out, float* __restrict__ sumsq, int dim, int vocab,
+                             const float* __restrict__ next_w, bf16* __restrict__ scaled, long long ld_scaled) {
   __shared__ float red[33];
   dep_launch();
   dep_wait();
@@ -27,6 +28,7 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     const float v = to_f32(src[i]);
     dst[i] = v;
     ss += v * v;
+    if (scaled) scaled[(size_t)row * ld_scaled + i] = __float2bfloat16_rn(v * next_w[i]);
   }
   if (sumsq) {
     ss = block_sum(ss, red);
@@ -34,15 +36,18 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
   }
 }
 
+// next_w, scaled (both or neither): scaled [rows, ld_scaled] bf16 = next_w * row, the operand of the
+// product behind a norm with weight next_w whose 1/rms the product's consumer applies from sumsq.
 extern "C" int llm_embed(const void* table, int table_dtype, const int* ids, float* out, float* sumsq, int n_rows,
-                         int dim, int vocab, cudaStream_t stream) {
+                         int dim, int vocab, const float* next_w, void* scaled, long long ld_scaled, cudaStream_t stream) {
   if (n_rows == 0) return LLM_OK;
+  LLM_REQUIRE((next_w == nullptr) == (scaled == nullptr), "embed: the scaled copy needs the weight it is scaled with");
   LLM_REQUIRE(n_rows > 0 && dim > 0 && vocab > 0, "embed: bad sizes rows=%d dim=%d vocab=%d", n_rows, dim, vocab);
   const int threads = dim >= 1024 ? 256 : 128;
   if (table_dtype == LLM_F32)
-    launch_kernel(embed_kernel<float>, n_rows, threads, 0, stream, (const float*)table, ids, out, sumsq, dim, vocab);
+    launch_kernel(embed_kernel<float>, n_rows, threads, 0, stream, (const float*)table, ids, out, sumsq, dim, vocab, next_w, (bf16*)scaled, ld_scaled);
   else if (table_dtype == LLM_BF16)
-    launch_kernel(embed_kernel<bf16>, n_rows, threads, 0, stream, (const bf16*)table, ids, out, sumsq, dim, vocab);
+    launch_kernel(embed_kernel<bf16>, n_rows, threads, 0, stream, (const bf16*)table, ids, out, sumsq, dim, vocab, next_w, (bf16*)scaled, ld_scaled);
   else
     LLM_REQUIRE(false, "embed: unknown table dtype %d", table_dtype);
   LLM_CHECK_LAUNCH("embed");
@@ -291,7 +296,7 @@ extern "C" int llm_reduce_partials(const float* partials, int n_partials, long l
 // partials: [parts, rows, 2*ff] float32 (gate | up); out [rows, ff] = silu(sum gate) * (sum up).
 template <typename T>
 __global__ void silu_mul_partials_kernel(const float* __restrict__ partials, int n_partials, size_t stride,
-                                         T* __restrict__ out, int ff, size_t total, int block) {
+                                         T* __restrict__ out, int ff, size_t total, int block, const RowScale rs) {
   dep_launch();
   dep_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -316,21 +321,26 @@ __global__ void silu_mul_partials_kernel(const float* __restrict__ partials, int
       u += uv[k];
     }
   }
+  const float sc = row_scale(rs, r);  // the norm before the product, when its 1/rms is still owed
+  g *= sc;
+  u *= sc;
   const float s = g / (1.0f + expf(-g));
   out[i] = from_f32<T>(s * u);
 }
 
 extern "C" int llm_silu_mul_partials(const float* partials, int n_partials, long long stride, void* out, int out_dtype,
-                                     int n_rows, int ff, int block, cudaStream_t stream) {
+                                     int n_rows, int ff, int block, const float* sumsq, int n_sumsq, float inv_dim, float eps,
+                                     cudaStream_t stream) {
   if (n_rows == 0) return LLM_OK;
+  const RowScale rs{sumsq, n_sumsq, inv_dim, eps};
   LLM_REQUIRE(n_rows > 0 && ff > 0 && n_partials >= 1, "silu_mul_partials: bad sizes");
   LLM_REQUIRE(block >= 0 && (block == 0 || ff % block == 0), "silu_mul_partials: column block %d does not divide %d", block, ff);
   const size_t total = (size_t)n_rows * ff;
   const int blocks = ceil_div((long long)total, 256);
   if (out_dtype == LLM_F32)
-    launch_kernel(silu_mul_partials_kernel<float>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (float*)out, ff, total, block);
+    launch_kernel(silu_mul_partials_kernel<float>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (float*)out, ff, total, block, rs);
   else if (out_dtype == LLM_BF16)
-    launch_kernel(silu_mul_partials_kernel<bf16>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (bf16*)out, ff, total, block);
+    launch_kernel(silu_mul_partials_kernel<bf16>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (bf16*)out, ff, total, block, rs);
   else
     LLM_REQUIRE(false, "silu_mul_partials: unknown dtype %d", out_dtype);
   LLM_CHECK_LAUNCH("silu_mul_partials");

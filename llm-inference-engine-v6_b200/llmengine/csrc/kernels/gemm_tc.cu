@@ -89,16 +89,38 @@ __device__ __forceinline__ void store_row16<bf16>(bf16* dst, const float* v, int
   }
 }
 
+// What the swapped form (few tokens) can do behind its product, so that no kernel of its own has to:
+//   EPI_MEET   the K splits of a tile of outputs meet: each CTA writes its partial sums, the one that
+//              arrives last adds them in index order, adds the sum into the float32 residual stream
+//              h, writes bf16(next_w * h) for the product that follows the next norm, and this
+//              tile's part of every token's sum of squares of the new stream (the norm's 1/rms is
+//              then applied by whoever consumes that product: a per-token scalar commutes with it);
+//   EPI_SCALE  every token's results are divided by the root mean square that the parts of its sum
+//              of squares give (the norm before this product, whose weight is already in the operand).
+enum : int { EPI_NONE = 0, EPI_MEET = 1, EPI_SCALE = 2 };
+struct EpiArgs {
+  float* h = nullptr; long long ld_h = 0;              // MEET: residual stream [tokens, ld_h]
+  const float* next_w = nullptr;                       // MEET: weight of the norm that follows (null: no scaled copy)
+  bf16* scaled = nullptr; long long ld_scaled = 0;     // MEET: bf16(next_w * h) [tokens, ld_scaled]
+  float* sumsq = nullptr; int n_sumsq = 0;             // MEET: [tokens, n_sumsq], column = this tile of outputs
+  int* counters = nullptr;                             // MEET: one per tile of outputs, zero between launches
+  const float* in_sumsq = nullptr; int n_in_sumsq = 0; // SCALE: [tokens, n_in_sumsq] parts of the sums of squares
+  float inv_dim = 0.f, eps = 0.f;                      // SCALE: 1 / sqrt(sum * inv_dim + eps)
+};
+
 // grid: (tiles of A rows, tiles of B rows, K splits); block: 128 threads.
 // SWIGLU (token tiles of 256 outputs only): the weight rows come in blocks of 256 = 128 rows of the
 // gate projection followed by the 128 matching rows of the up projection, so one accumulator tile
 // holds both; the epilogue writes silu(gate) * up, 128 columns per tile, and the 2x wider
 // intermediate never goes to memory.
-template <int BN, bool SWAP, typename TO, bool SWIGLU = false>
+template <int BN, bool SWAP, typename TO, bool SWIGLU = false, int EPI = EPI_NONE>
 __global__ void __launch_bounds__(128)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TO* __restrict__ out,
                    int RA, int RB, int k_tiles, int k_tiles_per_split, long long ldo, long long split_stride, int stages,
-                   int* __restrict__ error_out) {
+                   int* __restrict__ error_out, const EpiArgs epi) {
+  static_assert(EPI == EPI_NONE || (SWAP && !SWIGLU && BN <= 64), "the epilogue options belong to the swapped form with few tokens");
+  __shared__ float s_tok[EPI == EPI_NONE ? 1 : 4 * 64];  // SCALE: 1/rms of the tokens; MEET: the warps' parts of the sums of squares
+  __shared__ int s_last;
   constexpr int B_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
@@ -200,6 +222,15 @@ __global__ void __launch_bounds__(128)
   dep_wait();  // every thread: no global write before the previous kernels have finished
 
   // ------------------------------------------------------------------ epilogue: all four warps
+  if (EPI == EPI_SCALE) {
+    if ((int)threadIdx.x < RB - b_row0 && threadIdx.x < BN) {
+      const float* part = epi.in_sumsq + (size_t)(b_row0 + threadIdx.x) * epi.n_in_sumsq;
+      float sum = 0.f;
+      for (int j = 0; j < epi.n_in_sumsq; ++j) sum += part[j];  // index order
+      s_tok[threadIdx.x] = 1.0f / sqrtf(sum * epi.inv_dim + epi.eps);
+    }
+    __syncthreads();
+  }
   bool ready = n_iter > 0;
   if (ready) ready = mbar_wait(acc_ready, 0, abort_flag, error_out, ERR_EPILOGUE);
   ready = __all_sync(0xffffffffu, ready);  // a warp reads tensor memory together or not at all
@@ -243,9 +274,65 @@ __global__ void __launch_bounds__(128)
         if (ra < RA) {
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            if (rb0 + i < RB) o[(size_t)(rb0 + i) * ldo + ra] = from_f32<TO>(v[i]);  // lanes write consecutive addresses
+            if (rb0 + i < RB) {
+              const float r = EPI == EPI_SCALE ? v[i] * s_tok[c0 + i] : v[i];
+              o[(size_t)(rb0 + i) * ldo + ra] = from_f32<TO>(r);  // lanes write consecutive addresses
+            }
         }
       }
+    }
+  }
+  if (EPI == EPI_MEET) {
+    // The K splits of this tile of outputs meet. Every CTA has written its partial sums above; the
+    // one that counts itself last (also one that gave up: nobody may wait for it) finishes the tile.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(&epi.counters[blockIdx.x], 1) == (int)gridDim.z - 1;
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      const int splits = (int)gridDim.z, n_tok = min(RB, BN);
+      float acc[BN];
+#pragma unroll
+      for (int t = 0; t < BN; ++t) acc[t] = 0.f;
+      if (ra < RA) {
+        // a round of 64 loads is issued before any of them is added: added one by one as they come
+        // they would be so many dependent trips to L2
+        constexpr int U = BN <= 16 ? 4 : (BN <= 32 ? 2 : 1);
+        const float* part = reinterpret_cast<const float*>(out) + ra;
+        for (int z0 = 0; z0 < splits; z0 += U) {
+          float v[U][BN];
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int t = 0; t < BN; ++t)
+              v[u][t] = (z0 + u < splits && t < n_tok) ? __ldcg(part + (size_t)(z0 + u) * split_stride + (size_t)t * ldo) : 0.f;
+#pragma unroll
+          for (int u = 0; u < U; ++u)  // index order; the zeros of a short last round change nothing
+#pragma unroll
+            for (int t = 0; t < BN; ++t) acc[t] += v[u][t];
+        }
+      }
+      const float wn = (epi.next_w != nullptr && ra < RA) ? epi.next_w[ra] : 0.f;
+#pragma unroll
+      for (int t = 0; t < BN; ++t) {
+        float sq = 0.f;
+        if (t < n_tok && ra < RA) {
+          float* hp = epi.h + (size_t)t * epi.ld_h + ra;
+          const float hn = *hp + acc[t];
+          *hp = hn;
+          if (epi.scaled != nullptr) epi.scaled[(size_t)t * epi.ld_scaled + ra] = __float2bfloat16_rn(hn * wn);
+          sq = hn * hn;
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+        if (lane == 0) s_tok[warp * 64 + t] = sq;
+      }
+      __syncthreads();
+      if ((int)threadIdx.x < n_tok && epi.sumsq != nullptr)
+        epi.sumsq[(size_t)threadIdx.x * epi.n_sumsq + blockIdx.x] =
+            (s_tok[threadIdx.x] + s_tok[64 + threadIdx.x]) + (s_tok[128 + threadIdx.x] + s_tok[192 + threadIdx.x]);
+      if (threadIdx.x == 0) epi.counters[blockIdx.x] = 0;  // left at zero for the next launch
     }
   }
   // a role gave up: products that were issued may still run; the stages and tensor memory are theirs until then
@@ -764,27 +851,29 @@ inline bool prefer_pairs(int mode, int M, int N, int K, bool allow_192 = true) {
   return rounds_pair * 256 * 0.92f < (float)cost_single && rounds_pair * k_tiles >= 64;
 }
 
-template <int BN, bool SWAP, typename TO, bool SWIGLU = false>
+template <int BN, bool SWAP, typename TO, bool SWIGLU = false, int EPI = EPI_NONE>
 int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, int splits, long long ldo,
-              long long split_stride, int stages, cudaStream_t stream) {
+              long long split_stride, int stages, cudaStream_t stream, const EpiArgs& epi = EpiArgs()) {
   constexpr int STAGE_BYTES = A_BYTES + BN * BK * 2;
   const int k_tiles = (K + BK - 1) / BK;
   int per_split = (k_tiles + splits - 1) / splits;
   splits = (k_tiles + per_split - 1) / per_split;
-  stages = std::min(stages, (227 * 1024 - 2048) / STAGE_BYTES);
+  stages = std::min(stages, (227 * 1024 - 4096) / STAGE_BYTES);
   if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
   const size_t smem = (size_t)stages * STAGE_BYTES + (2 * stages + 1) * sizeof(uint64_t) + 16 + 1024;
-  auto kernel = gemm_tc_kernel<BN, SWAP, TO, SWIGLU>;
+  auto kernel = gemm_tc_kernel<BN, SWAP, TO, SWIGLU, EPI>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+    cudaFuncAttributes fa;  // static and dynamic shared memory share the 227 KB
+    const int fixed = cudaFuncGetAttributes(&fa, kernel) == cudaSuccess ? (int)((fa.sharedSizeBytes + 1023) / 1024) * 1024 : 4096;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - fixed) != cudaSuccess) {
       llm_set_error("gemm_tc: cannot raise the shared memory limit");
       return LLM_ERR_LAUNCH;
     }
     attr_set = true;
   }
   dim3 grid((RA + BM - 1) / BM, (RB + BN - 1) / BN, splits);
-  launch_kernel(kernel, grid, 128, smem, stream, ma, mb, (TO*)out, RA, RB, k_tiles, per_split, ldo, split_stride, stages, error_word());
+  launch_kernel(kernel, grid, 128, smem, stream, ma, mb, (TO*)out, RA, RB, k_tiles, per_split, ldo, split_stride, stages, error_word(), epi);
   return LLM_OK;
 }
 
@@ -882,6 +971,61 @@ extern "C" int llm_gemm_tc(const void* a, const void* w, void* out, int M, int N
   }
   if (rc != LLM_OK) return rc;
   LLM_CHECK_LAUNCH("gemm_tc");
+  return LLM_OK;
+}
+
+// The swapped form (at most 64 tokens) with the K splits meeting inside the product (EPI_MEET):
+// parts [splits, M, N] float32 scratch; h [M, ld_h] float32 += a . w^T; scaled [M, ld_scaled] bf16 =
+// next_w * h (skipped when next_w or scaled is null); sumsq [M, n_sumsq] float32 with n_sumsq =
+// ceil(N / 128): column j is the part of the rows' sums of squares that outputs 128 j .. 128 j + 127
+// contribute; counters: ceil(N / 128) ints, zero before the first launch and left at zero.
+extern "C" int llm_gemm_tc_meet(const void* a, const void* w, float* parts, int M, int N, int K, long long lda, long long ldw,
+                                int splits, float* h, long long ld_h, const float* next_w, void* scaled, long long ld_scaled,
+                                float* sumsq, int n_sumsq, int* counters, int stages, cudaStream_t stream) {
+  if (M == 0 || N == 0) return LLM_OK;
+  LLM_REQUIRE(llm_gemm_tc_supported(a, w, M, N, K, lda, ldw), "gemm_tc_meet: operands must be 16-byte aligned with K and row strides multiples of 8");
+  LLM_REQUIRE(M <= 64, "gemm_tc_meet: at most 64 tokens, got %d", M);
+  LLM_REQUIRE(splits >= 1 && stages >= 2 && stages <= 12, "gemm_tc_meet: splits %d, stages %d", splits, stages);
+  LLM_REQUIRE(h != nullptr && counters != nullptr && parts != nullptr, "gemm_tc_meet: stream, counters and scratch are needed");
+  LLM_REQUIRE(sumsq == nullptr || n_sumsq == (N + BM - 1) / BM, "gemm_tc_meet: %d parts of the sums of squares for %d outputs", n_sumsq, N);
+  LLM_REQUIRE(error_word() != nullptr, "gemm_tc_meet: cannot allocate the error word");
+  const int bn = M > 32 ? 64 : (M > 16 ? 32 : 16);
+  CUtensorMap ma, mb;
+  LLM_REQUIRE(tensor_map_for(w, N, K, ldw, BM, &ma) && tensor_map_for(a, M, K, lda, bn, &mb), "gemm_tc_meet: cuTensorMapEncodeTiled failed");
+  EpiArgs epi;
+  epi.h = h; epi.ld_h = ld_h; epi.next_w = next_w; epi.scaled = static_cast<bf16*>(scaled); epi.ld_scaled = ld_scaled;
+  epi.sumsq = sumsq; epi.n_sumsq = n_sumsq; epi.counters = counters;
+  int rc;
+  const long long split_stride = (long long)M * N;
+  if (bn == 64) rc = launch_tc<64, true, float, false, EPI_MEET>(ma, mb, parts, N, M, K, splits, N, split_stride, std::min(stages, 8), stream, epi);
+  else if (bn == 32) rc = launch_tc<32, true, float, false, EPI_MEET>(ma, mb, parts, N, M, K, splits, N, split_stride, std::min(stages, 8), stream, epi);
+  else rc = launch_tc<16, true, float, false, EPI_MEET>(ma, mb, parts, N, M, K, splits, N, split_stride, std::min(stages, 8), stream, epi);
+  if (rc != LLM_OK) return rc;
+  LLM_CHECK_LAUNCH("gemm_tc_meet");
+  return LLM_OK;
+}
+
+// The swapped form (at most 64 tokens, no K splits) with every token's results divided by the root
+// mean square that in_sumsq [M, n_in] gives: out [M, ldo] float32 = (a . w^T) / sqrt(sum_j in_sumsq[m, j] * inv_dim + eps).
+extern "C" int llm_gemm_tc_scaled(const void* a, const void* w, float* out, int M, int N, int K, long long lda, long long ldw,
+                                  long long ldo, const float* in_sumsq, int n_in, float inv_dim, float eps, int stages,
+                                  cudaStream_t stream) {
+  if (M == 0 || N == 0) return LLM_OK;
+  LLM_REQUIRE(llm_gemm_tc_supported(a, w, M, N, K, lda, ldw), "gemm_tc_scaled: operands must be 16-byte aligned with K and row strides multiples of 8");
+  LLM_REQUIRE(M <= 64, "gemm_tc_scaled: at most 64 tokens, got %d", M);
+  LLM_REQUIRE(in_sumsq != nullptr && n_in > 0 && stages >= 2 && stages <= 12, "gemm_tc_scaled: the parts of the sums of squares are needed");
+  LLM_REQUIRE(error_word() != nullptr, "gemm_tc_scaled: cannot allocate the error word");
+  const int bn = M > 32 ? 64 : (M > 16 ? 32 : 16);
+  CUtensorMap ma, mb;
+  LLM_REQUIRE(tensor_map_for(w, N, K, ldw, BM, &ma) && tensor_map_for(a, M, K, lda, bn, &mb), "gemm_tc_scaled: cuTensorMapEncodeTiled failed");
+  EpiArgs epi;
+  epi.in_sumsq = in_sumsq; epi.n_in_sumsq = n_in; epi.inv_dim = inv_dim; epi.eps = eps;
+  int rc;
+  if (bn == 64) rc = launch_tc<64, true, float, false, EPI_SCALE>(ma, mb, out, N, M, K, 1, ldo, 0, std::min(stages, 8), stream, epi);
+  else if (bn == 32) rc = launch_tc<32, true, float, false, EPI_SCALE>(ma, mb, out, N, M, K, 1, ldo, 0, std::min(stages, 8), stream, epi);
+  else rc = launch_tc<16, true, float, false, EPI_SCALE>(ma, mb, out, N, M, K, 1, ldo, 0, std::min(stages, 8), stream, epi);
+  if (rc != LLM_OK) return rc;
+  LLM_CHECK_LAUNCH("gemm_tc_scaled");
   return LLM_OK;
 }
 

@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(128)
                          const int* __restrict__ positions, const int* __restrict__ token_seq,
                          const int* __restrict__ block_table, int max_blocks, const float* __restrict__ cos_t,
                          const float* __restrict__ sin_t, T* __restrict__ kcache, T* __restrict__ vcache, int nq, int nkv,
-                         int hd, int page_size) {
+                         int hd, int page_size, const RowScale rs) {
   dep_launch();
   dep_wait();
   const int t = blockIdx.x;
@@ -66,6 +66,9 @@ __global__ void __launch_bounds__(128)
         b += vb[u];
       }
     }
+    const float sc = row_scale(rs, (size_t)t);  // the norm before the product, when its 1/rms is still owed
+    a *= sc;
+    b *= sc;
   } else {
     a = to_f32(row[col_a]);
     b = to_f32(row[col_b]);
@@ -164,8 +167,11 @@ extern "C" int llm_rope_kv_write(void* qkv, long long ld_qkv, int dtype, const f
                                  long long part_stride, const int* positions,
                                  const int* token_seq, const int* block_table, int max_blocks,
                                  const float* cos_t, const float* sin_t, void* kcache, void* vcache,
-                                 int n_tokens, int nq, int nkv, int hd, int page_size, cudaStream_t stream) {
+                                 int n_tokens, int nq, int nkv, int hd, int page_size, const float* sumsq, int n_sumsq,
+                                 float inv_dim, float eps, cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
+  const RowScale rs{sumsq, n_sumsq, inv_dim, eps};
+  LLM_REQUIRE(!sumsq || (parts && n_sumsq > 0), "rope_kv_write: a row scale goes with partial sums");
   LLM_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0 && hd > 0 && hd % 2 == 0 && page_size > 0,
               "rope_kv_write: bad sizes tokens=%d nq=%d nkv=%d hd=%d page=%d", n_tokens, nq, nkv, hd, page_size);
   LLM_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "rope_kv_write: cos and sin tables go together");
@@ -188,11 +194,11 @@ extern "C" int llm_rope_kv_write(void* qkv, long long ld_qkv, int dtype, const f
   if (dtype == LLM_F32)
     launch_kernel(rope_kv_write_kernel<float>, grid, threads, 0, stream, (float*)qkv, ld_qkv, parts, n_parts,
                   (size_t)part_stride, positions, token_seq, block_table, max_blocks, cos_t, sin_t, (float*)kcache,
-                  (float*)vcache, nq, nkv, hd, page_size);
+                  (float*)vcache, nq, nkv, hd, page_size, rs);
   else if (dtype == LLM_BF16)
     launch_kernel(rope_kv_write_kernel<bf16>, grid, threads, 0, stream, (bf16*)qkv, ld_qkv, parts, n_parts,
                   (size_t)part_stride, positions, token_seq, block_table, max_blocks, cos_t, sin_t, (bf16*)kcache,
-                  (bf16*)vcache, nq, nkv, hd, page_size);
+                  (bf16*)vcache, nq, nkv, hd, page_size, rs);
   else
     LLM_REQUIRE(false, "rope_kv_write: unknown dtype %d", dtype);
   LLM_CHECK_LAUNCH("rope_kv_write");

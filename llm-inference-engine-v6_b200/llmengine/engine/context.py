@@ -76,6 +76,9 @@ class StepContext:
         self.block_tables: List[torch.Tensor] = []
         self.stream_sumsq = None  # left by the embedding for the first norm (parts.base.Embedding.forward)
         self.residual = None  # the stream (parts.base.Residual) that the part being run works for, if it may add into it
+        self.stream_prescaled = None  # (rows times the first norm's weight, that weight), left by the embedding likewise
+        self.next_norm = None  # the norm that reads the stream after the part being run has written it, if known
+        self.norm_after_block = None  # the norm that reads the stream after the block being run
 
 
 class StepBuffers:

@@ -226,6 +226,7 @@ class Engine:
         spaces = [self.ws] + ([c.buffers.ws for c in self.graphs.captured.values()] if self.graphs is not None else [])
         for ws in spaces:
             ws.zero("attention.split_counters")
+            ws.zero("gemm.meet_counters")
         from ..ops import KernelError
         what = getattr(self.ops, "ERROR_CODES", {}).get(code, "unknown code")
         raise KernelError(f"a tensor-core kernel gave up a bounded wait (code {code}: {what}); the step's results are void")

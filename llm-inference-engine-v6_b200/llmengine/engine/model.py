@@ -107,11 +107,18 @@ class Model:
         return sorted(out)
 
     def forward(self, ctx) -> torch.Tensor:
-        ctx.stream_sumsq = None
+        order = self.spec.order
+        ctx.stream_sumsq = ctx.stream_prescaled = None
+        # who reads the residual stream next: a part that writes it may leave that norm's input prepared
+        ctx.next_norm = self.blocks[order[0].layer].first_norm() if order else self.final_norm
         res = Residual(self.embedding.forward(ctx))
         res.sumsq, ctx.stream_sumsq = ctx.stream_sumsq, None
-        for r, run in enumerate(self.spec.order):
+        if ctx.stream_prescaled is not None:
+            (res.prescaled, res.prescaled_weight), ctx.stream_prescaled = ctx.stream_prescaled, None
+        for r, run in enumerate(order):
+            ctx.norm_after_block = self.blocks[order[r + 1].layer].first_norm() if r + 1 < len(order) else self.final_norm
             res = self.blocks[run.layer].forward(res, ctx, self.caches[r])
+        ctx.next_norm = ctx.norm_after_block = None
         if ctx.n_rows > 0:
             if self.final_norm.can_defer and self.head.wants_lazy_norm(ctx):
                 x = self.final_norm.forward(res, ctx, rows=ctx.logit_rows, n_rows=ctx.n_rows, lazy=True)

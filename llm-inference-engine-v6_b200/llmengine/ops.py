@@ -36,6 +36,26 @@ def _ptr(t: Optional[torch.Tensor]):
     return c_void_p(0) if t is None else c_void_p(t.data_ptr())
 
 
+class RowScale:
+    """A per-token scalar that a consumer of partial sums still has to multiply in: the 1/rms of a
+    norm whose weight is already in the product's operand. sumsq: float32 [tokens, parts], the parts
+    of every token's sum of squares; the scalar is 1 / sqrt(sum(parts) / dim + eps)."""
+
+    def __init__(self, sumsq: torch.Tensor, dim: int, eps: float):
+        assert sumsq.dtype == torch.float32 and sumsq.dim() == 2 and sumsq.is_contiguous()
+        self.sumsq, self.dim, self.eps = sumsq, int(dim), float(eps)
+
+    def args(self):
+        return (_ptr(self.sumsq), c_int(self.sumsq.shape[1]), c_float(1.0 / self.dim), c_float(self.eps))
+
+
+_NO_ROW_SCALE = (c_void_p(0), c_int(0), c_float(0.0), c_float(0.0))
+
+
+def _row_scale_args(rs: Optional["RowScale"]):
+    return _NO_ROW_SCALE if rs is None else rs.args()
+
+
 def _stream():
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
@@ -64,6 +84,19 @@ class CudaOps:
         # sizes) such a step takes 1.15 ms with the pieces meeting inside clusters and 1.40 ms with them meeting in
         # global memory, against 0.89 ms with partial sums in memory that the norm and activation kernels add.
         self.few_token_products = False
+        # Steps of few tokens: the last product of a sub-layer adds its K splits inside itself (the CTA of
+        # each tile of outputs that finishes last), adds the sum into the residual stream and leaves
+        # weight * stream and the rows' sums of squares for the norm that follows, which then is no kernel
+        # of its own: its 1/rms is multiplied in where the next product's partial sums are consumed.
+        # Correct (tests/test_meet_products_gpu.py, and the engine's tests with it switched on) and off:
+        # a decode step of batch 8 at the Llama 3.2 1B sizes takes 1.22 ms with it against 0.87 ms
+        # without. The finishing CTA's tail (fence, counter, reading the other splits back from L2) is
+        # as long as the norm kernel it replaces, and while the norm kernel ran, the CTAs of the next
+        # product were already resident and fetching weights, which they cannot be beside this product's
+        # CTAs (shared memory). It also moves the bfloat16 rounding of a norm's output (weight * x is
+        # rounded before 1/rms is applied), so steps of few tokens and prompt steps would no longer
+        # round alike.
+        self.meet_products = False
         self._few_cache = {}
         self._err_host: Optional[torch.Tensor] = None  # pinned word that queue_error_check copies the kernels' error code into
 
@@ -116,8 +149,10 @@ class CudaOps:
             raise KernelError(lib.llm_last_error().decode())
 
     # ------------------------------------------------------------------ elementwise
-    def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, sumsq: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """out[n,:] (float32) = table[ids[n],:]; sumsq[n] (float32, optional) = sum of the row's squares."""
+    def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, sumsq: Optional[torch.Tensor] = None,
+              next_w: Optional[torch.Tensor] = None, scaled: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """out[n,:] (float32) = table[ids[n],:]; sumsq[n] (float32, optional) = sum of the row's squares;
+        scaled[n,:] (bfloat16, optional, with next_w float32 [dim]) = next_w * out[n,:]."""
         _need(table, "embed.table"); _need(ids, "embed.ids", torch.int32); _need(out, "embed.out", torch.float32)
         lib = self.lib()
         n, dim = out.shape
@@ -125,8 +160,14 @@ class CudaOps:
         if sumsq is not None:
             _need(sumsq, "embed.sumsq", torch.float32)
             assert sumsq.is_contiguous() and sumsq.numel() >= n
+        ld_scaled = 0
+        if scaled is not None:
+            _need(scaled, "embed.scaled", torch.bfloat16); _need(next_w, "embed.next_w", torch.float32)
+            assert scaled.shape[0] >= n and scaled.shape[1] == dim and next_w.numel() == dim and next_w.is_contiguous()
+            ld_scaled = scaled.stride(0)
         self._check(lib.llm_embed(_ptr(table), c_int(dtype_code(table.dtype)), _ptr(ids), _ptr(out), _ptr(sumsq), c_int(n),
-                                  c_int(dim), c_int(table.shape[0]), _stream()), lib)
+                                  c_int(dim), c_int(table.shape[0]), _ptr(next_w if scaled is not None else None), _ptr(scaled),
+                                  c_longlong(ld_scaled), _stream()), lib)
         return out
 
     def rmsnorm(self, h: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -176,7 +217,8 @@ class CudaOps:
                                      c_int(block), _stream()), lib)
         return out
 
-    def gemm_swiglu(self, a: torch.Tensor, w_blocked: torch.Tensor, out: torch.Tensor, ws=None) -> torch.Tensor:
+    def gemm_swiglu(self, a: torch.Tensor, w_blocked: torch.Tensor, out: torch.Tensor, ws=None,
+                    row_scale: Optional[RowScale] = None) -> torch.Tensor:
         """out [m, ff] = silu(gate) * up where gate | up = a @ w_blocked.T and w_blocked [2*ff, k] holds
         blocks of 128 gate rows followed by the 128 matching up rows. With many tokens in bfloat16
         the activation is applied in the product's epilogue and the [m, 2*ff] intermediate never
@@ -186,6 +228,7 @@ class CudaOps:
         ff = out.shape[1]
         assert w_blocked.shape == (2 * ff, k) and out.shape[0] == m and out.is_contiguous() and ff % 128 == 0
         if m > self.SWAP_MAX_TOKENS and self._tc_usable(a, w_blocked):
+            assert row_scale is None, "a row scale is applied where partial sums are consumed (few tokens)"
             lib = self.lib("tensorcore")
             self._check(lib.llm_gemm_tc_swiglu(_ptr(a), _ptr(w_blocked), _ptr(out), c_int(m), c_int(ff), c_int(k),
                                                c_longlong(a.stride(0)), c_longlong(w_blocked.stride(0)),
@@ -193,7 +236,8 @@ class CudaOps:
             return out
         assert ws is not None, "gemm_swiglu needs a workspace when it cannot fuse"
         if m <= self.SWAP_MAX_TOKENS:
-            return self.silu_mul_partials(self.gemm_partials(a, w_blocked, ws, "swiglu.parts"), out, block=128)
+            return self.silu_mul_partials(self.gemm_partials(a, w_blocked, ws, "swiglu.parts"), out, block=128, row_scale=row_scale)
+        assert row_scale is None, "a row scale is applied where partial sums are consumed (few tokens)"
         gate_up = ws.get("swiglu.gate_up", (m, 2 * ff), a.dtype)
         self.gemm(a, w_blocked, gate_up)
         return self.silu_mul(gate_up, out, block=128)
@@ -275,6 +319,56 @@ class CudaOps:
         parts = ws.get(tag, (1, M, N), torch.float32)
         self.gemm(a, w, parts[0])
         return parts
+
+    def row_scale(self, sumsq: torch.Tensor, dim: int, eps: float) -> RowScale:
+        return RowScale(sumsq, dim, eps)
+
+    def can_meet(self, a: torch.Tensor, w: torch.Tensor) -> bool:
+        """Whether gemm_meet / gemm_scaled take these operands (few tokens on the tensor-core kernel)."""
+        return self.meet_products and a.shape[0] <= self.SWAP_MAX_TOKENS and self._tc_usable(a, w)
+
+    def gemm_meet(self, a: torch.Tensor, w: torch.Tensor, h: torch.Tensor, ws, tag: str, next_w: Optional[torch.Tensor] = None,
+                  scaled: Optional[torch.Tensor] = None, sumsq: Optional[torch.Tensor] = None) -> None:
+        """h[:m] (float32 stream) += a @ w.T for m <= SWAP_MAX_TOKENS tokens, with the K splits of the product
+        added inside it (in index order, by the CTA of each tile of outputs that finishes last), so that
+        no other kernel has to read partial sums. Beside it, for the norm that follows: scaled[:m]
+        (bfloat16) = next_w * h, the operand of the product behind that norm, and sumsq [m, ceil(n / 128)]
+        (float32) = the parts of every row's sum of squares; the norm's 1/rms is owed by whoever consumes
+        that product (RowScale)."""
+        _need(a, "gemm_meet.a", torch.bfloat16); _need(w, "gemm_meet.w", torch.bfloat16); _need(h, "gemm_meet.h", torch.float32)
+        M, K = a.shape
+        N = w.shape[0]
+        assert self.can_meet(a, w) and w.shape[1] == K and h.shape[0] >= M and h.shape[1] == N
+        tiles = (N + 127) // 128
+        splits = self._splits_for(M, N, K)
+        parts = ws.get(tag, (splits, M, N), torch.float32)
+        counters = ws.get_zeroed("gemm.meet_counters", (tiles,), torch.int32)
+        n_sumsq = 0
+        if sumsq is not None:
+            _need(sumsq, "gemm_meet.sumsq", torch.float32)
+            assert sumsq.is_contiguous() and sumsq.shape[0] >= M and sumsq.shape[1] == tiles
+            n_sumsq = tiles
+        if scaled is not None:
+            _need(scaled, "gemm_meet.scaled", torch.bfloat16); _need(next_w, "gemm_meet.next_w", torch.float32)
+            assert scaled.shape[0] >= M and scaled.shape[1] == N and next_w.numel() == N and next_w.is_contiguous()
+        lib = self.lib("tensorcore")
+        self._check(lib.llm_gemm_tc_meet(_ptr(a), _ptr(w), _ptr(parts), c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)),
+                                         c_longlong(w.stride(0)), c_int(splits), _ptr(h), c_longlong(h.stride(0)),
+                                         _ptr(next_w if scaled is not None else None), _ptr(scaled),
+                                         c_longlong(scaled.stride(0) if scaled is not None else 0), _ptr(sumsq), c_int(n_sumsq),
+                                         _ptr(counters), c_int(3), _stream()), lib)
+
+    def gemm_scaled(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, row_scale: RowScale) -> torch.Tensor:
+        """out [m, n] (float32) = (a @ w.T) * row_scale, for m <= SWAP_MAX_TOKENS tokens, in one kernel."""
+        _need(a, "gemm_scaled.a", torch.bfloat16); _need(w, "gemm_scaled.w", torch.bfloat16); _need(out, "gemm_scaled.out", torch.float32)
+        M, K = a.shape
+        N = w.shape[0]
+        assert self.can_meet(a, w) and w.shape[1] == K and out.shape == (M, N) and row_scale.sumsq.shape[0] >= M
+        lib = self.lib("tensorcore")
+        self._check(lib.llm_gemm_tc_scaled(_ptr(a), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)),
+                                           c_longlong(w.stride(0)), c_longlong(out.stride(0)), *row_scale.args(), c_int(3),
+                                           _stream()), lib)
+        return out
 
     # ------------------------------------------------------------------ products of a step with few tokens
     FEW_TOKENS = 64  # up to here the weights fill the accumulator lanes and the kernel below applies
@@ -368,15 +462,17 @@ class CudaOps:
                                             c_int(dtype_code(out.dtype)), c_longlong(out.numel()), _stream()), lib)
         return out
 
-    def silu_mul_partials(self, parts: torch.Tensor, out: torch.Tensor, block: int = 0) -> torch.Tensor:
+    def silu_mul_partials(self, parts: torch.Tensor, out: torch.Tensor, block: int = 0,
+                          row_scale: Optional[RowScale] = None) -> torch.Tensor:
         """parts float32 [p, n, 2*ff] (gate | up partial sums, columns laid out as in silu_mul)
-        -> out [n, ff] = silu(gate) * up."""
+        -> out [n, ff] = silu(gate) * up; with row_scale, gate and up of row n are first multiplied by it."""
         _need(parts, "silu_mul.parts", torch.float32); _need(out, "silu_mul.out")
         n, ff = out.shape
         assert parts.is_contiguous() and out.is_contiguous() and parts.shape[1:] == (n, 2 * ff)
         lib = self.lib()
         self._check(lib.llm_silu_mul_partials(_ptr(parts), c_int(parts.shape[0]), c_longlong(parts.stride(0)), _ptr(out),
-                                              c_int(dtype_code(out.dtype)), c_int(n), c_int(ff), c_int(block), _stream()), lib)
+                                              c_int(dtype_code(out.dtype)), c_int(n), c_int(ff), c_int(block),
+                                              *_row_scale_args(row_scale), _stream()), lib)
         return out
 
     def tensor_core_error(self) -> int:
@@ -429,11 +525,13 @@ class CudaOps:
     def rope_kv_write(self, qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,
                       block_table: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                       kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor], n_tokens: int, nq: int,
-                      nkv: int, hd: int, parts: Optional[torch.Tensor] = None) -> None:
+                      nkv: int, hd: int, parts: Optional[torch.Tensor] = None, row_scale: Optional[RowScale] = None) -> None:
         """Rotates q and k of qkv [n, (nq+2nkv)*hd] in place by the tables cos/sin [max_pos, hd/2]
         and writes k, v of each token into its page: kcache/vcache [pages, nkv, page_size, hd].
         With `parts` (float32 [p, n, width] partial sums of the q|k|v product) the values are the
-        sums over parts; then only the q section of qkv is written (k and v go to the cache)."""
+        sums over parts (times row_scale, if given); then only the q section of qkv is written (k and v
+        go to the cache)."""
+        assert row_scale is None or parts is not None
         _need(qkv, "rope.qkv"); _need(positions, "rope.positions", torch.int32)
         _need(token_seq, "rope.token_seq", torch.int32); _need(block_table, "rope.block_table", torch.int32)
         page_size = 1
@@ -456,7 +554,7 @@ class CudaOps:
                                           _ptr(parts), c_int(n_parts), c_longlong(pstride), _ptr(positions), _ptr(token_seq), _ptr(block_table),
                                           c_int(block_table.shape[1]), _ptr(cos), _ptr(sin), _ptr(kcache),
                                           _ptr(vcache), c_int(n_tokens), c_int(nq), c_int(nkv), c_int(hd),
-                                          c_int(page_size), _stream()), lib)
+                                          c_int(page_size), *_row_scale_args(row_scale), _stream()), lib)
 
     # decoding: the key range is cut at absolute multiples of `split_keys` (a multiple of 64); see _split_policy
     ATTENTION_TARGET_CTAS = 592
@@ -510,9 +608,10 @@ class CudaOps:
 
     def paged_attention_decode_fused(self, parts: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                                      kcache: torch.Tensor, vcache: torch.Tensor, batch, block_table: torch.Tensor,
-                                     out: torch.Tensor, nq: int, nkv: int, hd: int, scale: float, window: int = 0) -> torch.Tensor:
+                                     out: torch.Tensor, nq: int, nkv: int, hd: int, scale: float, window: int = 0,
+                                     row_scale: Optional[RowScale] = None) -> torch.Tensor:
         """A step of single tokens, from the q|k|v product's partial sums (float32 [p, n, (nq+2nkv)*hd],
-        added in index order): rotation of q and k by cos/sin [positions, hd/2] (none if both are
+        added in index order, times row_scale if given): rotation of q and k by cos/sin [positions, hd/2] (none if both are
         None), the write of k and v into the token's page, and attention over the cache, in one kernel."""
         _need(parts, "attention.parts", torch.float32); _need(kcache, "attention.kcache", torch.bfloat16)
         _need(vcache, "attention.vcache", torch.bfloat16); _need(out, "attention.out", torch.bfloat16)
@@ -531,7 +630,7 @@ class CudaOps:
             c_longlong(kcache.shape[0]), _ptr(batch.seq_start), _ptr(batch.seq_qoff), _ptr(block_table),
             c_int(block_table.shape[1]), _ptr(out), c_longlong(out.stride(0)), c_int(batch.n_seqs), c_int(nq), c_int(nkv),
             c_int(hd), c_int(kcache.shape[2]), c_float(scale), c_int(window), c_int(n_splits), c_int(split_keys),
-            _ptr(scratch), _ptr(counters), _stream()), lib)
+            _ptr(scratch), _ptr(counters), *_row_scale_args(row_scale), _stream()), lib)
         return out
 
     def paged_attention(self, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, batch,

@@ -70,8 +70,15 @@ class PagedAttention(Mixer):
                 ops.few_token_splits(self.w_qkv.shape[0], s.hidden, n, "plain") > 0 and
                 ops.few_token_splits(s.hidden, s.num_heads * s.head_dim, n, "residual") > 0)
 
+    def _takes_prescaled(self, ctx) -> bool:
+        """The step has few enough tokens for the q|k|v product to come as partial sums, and whoever
+        finishes them (the attention kernel or the position encoding) takes the norm's 1/rms as a row scale."""
+        ops = self.env.ops
+        return (self.env.dtype == torch.bfloat16 and getattr(ops, "meet_products", False) and ctx.n_tokens <= 64 and
+                self.position.takes_partial_sums and self.position.takes_row_scale)
+
     def wants_lazy_norm(self, ctx) -> bool:
-        return self._few_tokens(ctx) and self.position.takes_partial_sums
+        return (self._few_tokens(ctx) and self.position.takes_partial_sums) or self._takes_prescaled(ctx)
 
     def forward(self, x, ctx, cache: LayerCache) -> Optional[torch.Tensor]:
         s, ops, n = self.spec, self.env.ops, ctx.n_tokens
@@ -79,8 +86,15 @@ class PagedAttention(Mixer):
         qkv = ctx.ws.get("attention.qkv", (n, dq + 2 * dkv), self.env.dtype)
         att = ctx.ws.get("attention.out", (n, dq), self.env.dtype)
         few = self._few_tokens(ctx)
-        if isinstance(x, NormalizedRows) and not (few and cache.writes and self.position.takes_partial_sums):
-            x = x.dense(ctx)
+        row_scale = None
+        if isinstance(x, NormalizedRows):
+            if (x.prescaled is not None and x.rows is None and cache.writes and cache.k is not None and self._takes_prescaled(ctx)
+                    and ops.can_meet(x.prescaled[:n], self.w_qkv)):
+                # the rows times the norm's weight are there already: the product runs on them, and the
+                # norm's 1/rms goes in where the product's partial sums are finished
+                row_scale, x, few = x.row_scale(ops), x.prescaled, False
+            elif not (few and cache.writes and self.position.takes_partial_sums):
+                x = x.dense(ctx)
         if n <= 64 and cache.writes and self.position.takes_partial_sums:
             # few tokens: the product comes as float32 sums (in parts, unless the K pieces were added
             # inside the product), finished by the position kernel or by the attention kernel
@@ -95,11 +109,13 @@ class PagedAttention(Mixer):
             tables = self.position.rotation_tables() if cache.k is not None else None
             if tables is not None and ops.decode_attention_fusable(ctx, cache.k, s.num_heads, s.num_kv_heads, s.head_dim, att):
                 # single decoded tokens: summing the parts, rotation and the cache write happen inside the attention kernel
+                extra = {} if row_scale is None else {"row_scale": row_scale}
                 ops.paged_attention_decode_fused(parts, tables[0], tables[1], cache.k, cache.v, ctx,
                                                  ctx.block_tables[cache.group], att, s.num_heads, s.num_kv_heads,
-                                                 s.head_dim, self.scale, s.window)
+                                                 s.head_dim, self.scale, s.window, **extra)
                 return self._output(att, ctx, few)
-            self.position.rotate_and_store(qkv, ctx, cache, s.num_heads, s.num_kv_heads, s.head_dim, parts=parts)
+            extra = {} if row_scale is None else {"row_scale": row_scale}
+            self.position.rotate_and_store(qkv, ctx, cache, s.num_heads, s.num_kv_heads, s.head_dim, parts=parts, **extra)
         else:
             ops.gemm(x[:n], self.w_qkv, qkv, ctx.ws)
             self.position.rotate_and_store(qkv, ctx, cache, s.num_heads, s.num_kv_heads, s.head_dim)
@@ -118,19 +134,33 @@ def add_into_stream_or_partials(ops, x: torch.Tensor, w: torch.Tensor, ctx, few:
     product adds itself into the stream and leaves the parts of the rows' sums of squares there
     (so that the next norm need not run); otherwise it returns float32 partial sums."""
     res, n = ctx.residual, ctx.n_tokens
+    if (not few and res is not None and res.pending is None and res.h.shape[1] == w.shape[0] and x.dtype == torch.bfloat16 and
+            hasattr(ops, "gemm_meet") and ops.can_meet(x[:n], w)):
+        # few tokens: the K splits meet inside the product, which adds their sum into the stream and
+        # leaves, for the norm that reads the stream next, its weight times the stream and the parts of
+        # the rows' sums of squares
+        nxt = getattr(ctx, "next_norm", None)
+        wn = nxt.prescale_weight() if nxt is not None else None
+        if wn is not None and (wn.numel() != w.shape[0] or wn.dtype != torch.float32):
+            wn = None
+        ss = ctx.ws.get("stream.sumsq", (res.h.shape[0], (w.shape[0] + 127) // 128), torch.float32)
+        scaled = ctx.ws.get("stream.prescaled", tuple(res.h.shape), torch.bfloat16) if wn is not None else None
+        ops.gemm_meet(x[:n], w, res.h, ctx.ws, tag, next_w=wn, scaled=scaled, sumsq=ss)
+        res.sumsq, res.prescaled, res.prescaled_weight = ss, scaled, wn
+        return None
     if few and res is not None and res.pending is None and res.h.shape[1] == w.shape[0]:
         parts = ops.residual_sumsq_parts(w.shape[0], w.shape[1], n)
         ss = ctx.ws.get(tag + ".sumsq", (res.h.shape[0], parts), torch.float32)
         ops.gemm_few_tokens(w, res.h, "residual", x=x[:n], sumsq_out=ss, n_tokens=n, ws=ctx.ws)
-        res.sumsq = ss
+        res.sumsq, res.prescaled, res.prescaled_weight = ss, None, None
         return None
     res_sumsq_off(res)
     return ops.gemm_partials(x, w, ctx.ws, tag)
 
 
 def res_sumsq_off(res) -> None:
-    if res is not None:
-        res.sumsq = None  # a delta is on its way: the sums of squares no longer describe the stream
+    if res is not None:  # a delta is on its way: what was left beside the stream no longer describes it
+        res.sumsq = res.prescaled = res.prescaled_weight = None
 
 
 register_part("mixer", "attention", PagedAttention)

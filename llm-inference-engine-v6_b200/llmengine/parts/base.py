@@ -75,6 +75,12 @@ class Residual:
         self.h = h
         self.pending: Optional[torch.Tensor] = None
         self.sumsq: Optional[torch.Tensor] = None  # valid only while pending is None and h is untouched since
+        # beside sumsq, what the product that last added into the stream may also leave for the norm that
+        # comes next (ctx.next_norm): the stream's rows times that norm's weight, in the engine dtype. The
+        # norm's 1/rms is a scalar per row, so the product behind the norm can run on these rows as they
+        # are and the scalar be multiplied in where that product's results are consumed (ops.RowScale).
+        self.prescaled: Optional[torch.Tensor] = None
+        self.prescaled_weight: Optional[torch.Tensor] = None  # the weight tensor prescaled was made with
 
 
 @dataclass
@@ -89,9 +95,14 @@ class NormalizedRows:
     rows: Optional[torch.Tensor]
     n: int
     norm: "Norm"
+    prescaled: Optional[torch.Tensor] = None  # weight * h in the engine dtype (all rows of h), if the producer left it
 
     def dense(self, ctx) -> torch.Tensor:
         return self.norm.run(self.h, ctx, self.rows, self.n)
+
+    def row_scale(self, ops):
+        """The 1/rms of the rows as the kernels take it (for consumers of a product of `prescaled`)."""
+        return ops.row_scale(self.sumsq, self.h.shape[1], self.eps)
 
 
 class Part:
@@ -151,6 +162,12 @@ class Norm(Part):
     category = "norm"
     can_defer = False  # True: forward(..., lazy=True) may return NormalizedRows
 
+    def prescale_weight(self) -> Optional[torch.Tensor]:
+        """For a norm of the form (weight * x) * s(x) with s a scalar per row that only needs the row's
+        sum of squares: the float32 weight [dim], so that whoever writes the stream last can leave
+        weight * x beside it (Residual.prescaled). None (the default): this norm runs as it is."""
+        return None
+
     def forward(self, res: Residual, ctx, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> torch.Tensor:
         """Adds res.pending into res.h (when `rows` is None) and returns the normalised rows in the
         engine dtype. With `rows`, only those source rows are normalised and res is left alone.
@@ -164,6 +181,9 @@ class PositionEncoding(Part):
     # True if rotate_and_store takes `parts`: float32 [p, tokens, width] partial sums of the q|k|v
     # product to be added (in index order) while encoding, instead of finished values in qkv.
     takes_partial_sums = False
+    # True if rotate_and_store also takes `row_scale` beside `parts` (when the layer writes its cache):
+    # a scalar per token that the sums are multiplied with before anything else (ops.RowScale).
+    takes_row_scale = False
 
     def rotation_tables(self):
         """For mixers that fold the encoding into their own kernel: (cos, sin) float32 tables
@@ -205,5 +225,12 @@ class Block(Part):
     def cache_needs(self) -> Sequence[object]:
         return ()
 
+    def first_norm(self) -> Optional[Norm]:
+        """The norm that reads the residual stream first in this block, if the block begins with one: the
+        model tells the part that writes the stream before it (ctx.next_norm)."""
+        return None
+
     def forward(self, res: Residual, ctx, cache: LayerCache) -> Residual:
+        """ctx.norm_after_block: the norm that reads the stream after this block (the next block's
+        first, or the model's final norm), or None."""
         raise NotImplementedError

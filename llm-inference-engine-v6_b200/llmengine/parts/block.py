@@ -35,13 +35,18 @@ class PreNormBlock(Block):
         for p in (self.norm1, self.mixer, self.norm2, self.feed_forward):
             p.load(tensors)
 
+    def first_norm(self):
+        return self.norm1
+
     def forward(self, res: Residual, ctx, cache: LayerCache) -> Residual:
         ctx.residual = res  # a part whose last product can add into the stream itself returns None
         x = self._norm(self.norm1, self.mixer, res, ctx)
+        ctx.next_norm = self.norm2  # who reads the stream after the mixer has written it
         res.pending = self.mixer.forward(x, ctx, cache)
         x = self._norm(self.norm2, self.feed_forward, res, ctx)
+        ctx.next_norm = getattr(ctx, "norm_after_block", None)
         res.pending = self.feed_forward.forward(x, ctx)
-        ctx.residual = None
+        ctx.residual = ctx.next_norm = None
         return res
 
     @staticmethod

@@ -56,8 +56,12 @@ class GatedMLP(FeedForward):
                 ops.few_token_splits(2 * s.intermediate, s.hidden, n, "swiglu") > 0 and
                 ops.few_token_splits(s.hidden, s.intermediate, n, "residual") > 0)
 
+    def _takes_prescaled(self, ctx) -> bool:
+        ops = self.env.ops
+        return self.env.dtype == torch.bfloat16 and getattr(ops, "meet_products", False) and ctx.n_tokens <= 64
+
     def wants_lazy_norm(self, ctx) -> bool:
-        return self._few_tokens(ctx)
+        return self._few_tokens(ctx) or self._takes_prescaled(ctx)
 
     def forward(self, x, ctx) -> Optional[torch.Tensor]:
         s, ops, n = self.spec, self.env.ops, ctx.n_tokens
@@ -70,18 +74,23 @@ class GatedMLP(FeedForward):
             else:
                 ops.gemm_few_tokens(self.w_gate_up, act, "swiglu", x=x[:n], ws=ctx.ws)
             return add_into_stream_or_partials(ops, act, self.w_down, ctx, True, "mlp.delta")
+        extra = {}
         if isinstance(x, NormalizedRows):
-            x = x.dense(ctx)
-        res_sumsq_off(ctx.residual)
+            if (x.prescaled is not None and x.rows is None and self._takes_prescaled(ctx) and
+                    ops.can_meet(x.prescaled[:n], self.w_gate_up)):
+                # the product runs on weight * rows; the norm's 1/rms goes in where its partial sums are added
+                extra, x = {"row_scale": x.row_scale(ops)}, x.prescaled
+            else:
+                x = x.dense(ctx)
         if self.blocked:
-            ops.gemm_swiglu(x[:n], self.w_gate_up, act, ctx.ws)
+            ops.gemm_swiglu(x[:n], self.w_gate_up, act, ctx.ws, **extra)
         elif n <= 64:  # few tokens: the products may come as partial sums, added by their consumers
-            ops.silu_mul_partials(ops.gemm_partials(x[:n], self.w_gate_up, ctx.ws, "mlp.gate_up_parts"), act)
+            ops.silu_mul_partials(ops.gemm_partials(x[:n], self.w_gate_up, ctx.ws, "mlp.gate_up_parts"), act, **extra)
         else:
             gate_up = ctx.ws.get("mlp.gate_up", (n, 2 * s.intermediate), self.env.dtype)
             ops.gemm(x[:n], self.w_gate_up, gate_up)
             ops.silu_mul(gate_up, act)
-        return ops.gemm_partials(act, self.w_down, ctx.ws, "mlp.delta")
+        return add_into_stream_or_partials(ops, act, self.w_down, ctx, False, "mlp.delta")
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

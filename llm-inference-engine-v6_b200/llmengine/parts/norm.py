@@ -30,14 +30,18 @@ class RMSNorm(Norm):
         if lazy and res.pending is None and res.sumsq is not None:
             # the stream is up to date and the sums of squares of its rows are known: whoever
             # consumes the rows computes (w * x) / rms(x) while it loads them
-            return NormalizedRows(res.h, res.sumsq, self.weight, self.spec.eps, rows, n, self)
+            pre = res.prescaled if res.prescaled_weight is self.weight else None
+            return NormalizedRows(res.h, res.sumsq, self.weight, self.spec.eps, rows, n, self, pre)
         out = ctx.ws.get("norm.out" if rows is None else "norm.rows_out", (n, self.spec.dim), self.env.dtype)
         self.env.ops.rmsnorm(res.h, self.weight, self.spec.eps, out, delta=res.pending, rows=rows, n_rows=n)
         if rows is None:
             if res.pending is not None:
-                res.sumsq = None  # the stream has moved on
+                res.sumsq = res.prescaled = res.prescaled_weight = None  # the stream has moved on
             res.pending = None
         return out
+
+    def prescale_weight(self):
+        return self.weight
 
     def run(self, h: torch.Tensor, ctx, rows, n: int) -> torch.Tensor:
         """The norm's kernel on rows of a stream that has nothing pending (NormalizedRows.dense)."""

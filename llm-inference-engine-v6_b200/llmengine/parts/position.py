@@ -78,11 +78,14 @@ class RotaryPosition(PositionEncoding):
     def rotation_tables(self):
         return self.cos, self.sin
 
-    def rotate_and_store(self, qkv, ctx, cache: LayerCache, num_heads, num_kv_heads, head_dim, parts=None) -> None:
+    takes_row_scale = True
+
+    def rotate_and_store(self, qkv, ctx, cache: LayerCache, num_heads, num_kv_heads, head_dim, parts=None, row_scale=None) -> None:
         write = cache.writes and cache.k is not None
+        extra = {} if row_scale is None else {"row_scale": row_scale}
         self.env.ops.rope_kv_write(qkv, ctx.positions, ctx.token_seq, ctx.block_tables[cache.group], self.cos, self.sin,
                                    cache.k if write else None, cache.v if write else None, ctx.n_tokens, num_heads,
-                                   num_kv_heads, head_dim, parts=parts)
+                                   num_kv_heads, head_dim, parts=parts, **extra)
 
 
 class NoPosition(PositionEncoding):
@@ -91,11 +94,15 @@ class NoPosition(PositionEncoding):
     def rotation_tables(self):
         return None, None
 
-    def rotate_and_store(self, qkv, ctx, cache: LayerCache, num_heads, num_kv_heads, head_dim, parts=None) -> None:
+    takes_row_scale = True
+
+    def rotate_and_store(self, qkv, ctx, cache: LayerCache, num_heads, num_kv_heads, head_dim, parts=None, row_scale=None) -> None:
         if cache.writes and cache.k is not None:
+            extra = {} if row_scale is None else {"row_scale": row_scale}
             self.env.ops.rope_kv_write(qkv, ctx.positions, ctx.token_seq, ctx.block_tables[cache.group], None, None,
-                                       cache.k, cache.v, ctx.n_tokens, num_heads, num_kv_heads, head_dim, parts=parts)
+                                       cache.k, cache.v, ctx.n_tokens, num_heads, num_kv_heads, head_dim, parts=parts, **extra)
         elif parts is not None:
+            assert row_scale is None, "a row scale is taken only where the layer writes its cache"
             self.env.ops.reduce_partials(parts, qkv)
 
 

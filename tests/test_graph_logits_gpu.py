@@ -20,12 +20,16 @@ CONFIGS = dict(TINY, f=(dict(TINY_D, max_position_embeddings=500), 16))
 
 
 @pytest.mark.parametrize("name,dtype,folded", [("d", "bf16", False), ("e", "bf16", False), ("f", "bf16", False), ("b", "bf16", False),
-                                               ("a", "fp32", False), ("d", "fp32", False), ("d", "bf16", True), ("e", "bf16", True)])
+                                               ("a", "fp32", False), ("d", "fp32", False), ("d", "bf16", "few"), ("e", "bf16", "few"),
+                                               ("d", "bf16", "meet"), ("e", "bf16", "meet"), ("f", "bf16", "meet")])
 def test_logits_through_decode_graphs(tmp_path, monkeypatch, name, dtype, folded):
-    """folded: with the products of few-token steps that add their K pieces themselves and take the
-    norms, the residual sums and SiLU * up in (off by default; the same logits either way)."""
+    """folded (options that are off by default; the same logits either way): "few": the products of
+    few-token steps add their K pieces themselves and take the norms, the residual sums and SiLU * up in;
+    "meet": the last product of a sub-layer adds its K splits and the residual itself and leaves the next
+    norm's input, whose 1/rms goes in where the next product's partial sums are consumed."""
     from llmengine.ops import get_ops
-    monkeypatch.setattr(get_ops(), "few_token_products", folded)
+    monkeypatch.setattr(get_ops(), "few_token_products", folded == "few")
+    monkeypatch.setattr(get_ops(), "meet_products", folded == "meet")
     cfg, page = CONFIGS[name]
     d = str(tmp_path / "m")
     make_model_dir(d, cfg, torch.float32 if dtype == "fp32" else torch.bfloat16)
