@@ -21,6 +21,8 @@
 // The reference computes the same products with a scalar loop (matmul_f32, src/kernels.cpp:33-57).
 #include "tc_common.cuh"
 
+#include <type_traits>
+
 int* llm_tc_error_word() {
   // One int of device memory per process for the kernels' error codes, made at first use.
   static int* word = nullptr;
@@ -89,6 +91,55 @@ __device__ __forceinline__ void store_row16<bf16>(bf16* dst, const float* v, int
   }
 }
 
+// v += dst (float32 outputs that are added into what is there, e.g. the residual stream).
+template <typename TO>
+__device__ __forceinline__ void add_from16(const TO* dst, float* v, int valid, bool aligned) {}
+template <>
+__device__ __forceinline__ void add_from16<float>(const float* dst, float* v, int valid, bool aligned) {
+  if (valid == 16 && aligned) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 t = reinterpret_cast<const float4*>(dst)[i];
+      v[4 * i] += t.x; v[4 * i + 1] += t.y; v[4 * i + 2] += t.z; v[4 * i + 3] += t.w;
+    }
+  } else {
+    for (int i = 0; i < valid; ++i) v[i] += dst[i];
+  }
+}
+
+// A thread's accumulator row (BN columns from tensor-memory address `acc`) added into row `dst_row` of a
+// float32 matrix: out[c] += acc[c] for columns col0 .. col0 + BN - 1 below n_cols. The old values of 64
+// columns are requested together before the accumulator is read: fetched 16 at a time, behind each
+// tensor-memory load, they would be BN / 16 dependent trips to L2.
+template <int BN>
+__device__ __forceinline__ void add_accumulator_row(uint32_t acc, float* dst_row, bool row_ok, int col0, int n_cols) {
+  constexpr int G = BN >= 64 ? 64 : 16;
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += G) {
+    float old[G];
+#pragma unroll
+    for (int q = 0; q < G / 16; ++q) {
+      const int c = col0 + c0 + 16 * q;
+      float* dst = dst_row + c;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) old[16 * q + i] = 0.f;
+      if (row_ok && c < n_cols) add_from16<float>(dst, old + 16 * q, min(16, n_cols - c), (reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+    }
+#pragma unroll
+    for (int q = 0; q < G / 16; ++q) {
+      float v[16];
+      tmem_load16(acc + (uint32_t)(c0 + 16 * q), v);
+      const int c = col0 + c0 + 16 * q;
+      if (row_ok && c < n_cols) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] += old[16 * q + i];
+        float* dst = dst_row + c;
+        store_row16<float>(dst, v, min(16, n_cols - c), (reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+      }
+    }
+  }
+}
+
 // What the swapped form (few tokens) can do behind its product, so that no kernel of its own has to:
 //   EPI_MEET   the K splits of a tile of outputs meet: each CTA writes its partial sums, the one that
 //              arrives last adds them in index order, adds the sum into the float32 residual stream
@@ -117,7 +168,7 @@ template <int BN, bool SWAP, typename TO, bool SWIGLU = false, int EPI = EPI_NON
 __global__ void __launch_bounds__(128)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TO* __restrict__ out,
                    int RA, int RB, int k_tiles, int k_tiles_per_split, long long ldo, long long split_stride, int stages,
-                   int* __restrict__ error_out, const EpiArgs epi) {
+                   int* __restrict__ error_out, const EpiArgs epi, int add_into) {
   static_assert(EPI == EPI_NONE || (SWAP && !SWIGLU && BN <= 64), "the epilogue options belong to the swapped form with few tokens");
   __shared__ float s_tok[EPI == EPI_NONE ? 1 : 4 * 64];  // SCALE: 1/rms of the tokens; MEET: the warps' parts of the sums of squares
   __shared__ int s_last;
@@ -253,6 +304,9 @@ __global__ void __launch_bounds__(128)
         }
       }
     }
+  } else if (!SWAP && add_into && ready) {
+    if constexpr (!SWAP && std::is_same<TO, float>::value)  // out += product
+      add_accumulator_row<BN>(tmem_base + ((uint32_t)(warp * 32) << 16), reinterpret_cast<float*>(o) + (size_t)ra * ldo, ra < RA, b_row0, RB);
   } else if (ready || n_iter == 0) {
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -357,7 +411,7 @@ template <typename TO, bool SWIGLU, int BN>
 __global__ void __launch_bounds__(PERSIST_THREADS)
     gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                               TO* __restrict__ out, int RA, int RB, int k_tiles, long long ldo, int stages, int m_tiles,
-                              int n_tiles, int* __restrict__ error_out) {
+                              int n_tiles, int* __restrict__ error_out, int add_into) {
   static_assert(BN == 256 || BN == 192, "two accumulators of BN columns, 256 columns apart, in 512 columns of tensor memory");
   static_assert(!SWIGLU || BN == 256, "the gate|up blocks are 256 rows");
   constexpr int ACC_STRIDE = 256;  // tensor-memory columns from one accumulator to the other
@@ -501,6 +555,9 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
             store_row16<TO>(dst, gv, min(16, RB / 2 - col0), (reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
           }
         }
+      } else if (add_into) {
+        if constexpr (std::is_same<TO, float>::value)  // out += product
+          add_accumulator_row<BN>(acc, reinterpret_cast<float*>(out) + (size_t)ra * ldo, ra < RA, b_row0, RB);
       } else {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -789,7 +846,7 @@ int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int 
 
 template <typename TO, bool SWIGLU, int BN = 256>
 int launch_tc_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, long long ldo,
-                         int n_sms, cudaStream_t stream) {
+                         int n_sms, cudaStream_t stream, int add_into = 0) {
   constexpr int STAGE_BYTES = A_BYTES + BN * BK * 2;
   const int k_tiles = (K + BK - 1) / BK;
   const int stages = BN == 256 ? 4 : 5;
@@ -806,7 +863,7 @@ int launch_tc_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out
   const int m_tiles = (RA + BM - 1) / BM, n_tiles = (RB + BN - 1) / BN;
   const int grid = std::min(m_tiles * n_tiles, n_sms);
   launch_kernel(kernel, grid, PERSIST_THREADS, smem, stream, ma, mb, (TO*)out, RA, RB, k_tiles, ldo, stages, m_tiles, n_tiles,
-                error_word());
+                error_word(), add_into);
   return LLM_OK;
 }
 
@@ -853,7 +910,7 @@ inline bool prefer_pairs(int mode, int M, int N, int K, bool allow_192 = true) {
 
 template <int BN, bool SWAP, typename TO, bool SWIGLU = false, int EPI = EPI_NONE>
 int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, int splits, long long ldo,
-              long long split_stride, int stages, cudaStream_t stream, const EpiArgs& epi = EpiArgs()) {
+              long long split_stride, int stages, cudaStream_t stream, const EpiArgs& epi = EpiArgs(), int add_into = 0) {
   constexpr int STAGE_BYTES = A_BYTES + BN * BK * 2;
   const int k_tiles = (K + BK - 1) / BK;
   int per_split = (k_tiles + splits - 1) / splits;
@@ -873,7 +930,8 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, i
     attr_set = true;
   }
   dim3 grid((RA + BM - 1) / BM, (RB + BN - 1) / BN, splits);
-  launch_kernel(kernel, grid, 128, smem, stream, ma, mb, (TO*)out, RA, RB, k_tiles, per_split, ldo, split_stride, stages, error_word(), epi);
+  launch_kernel(kernel, grid, 128, smem, stream, ma, mb, (TO*)out, RA, RB, k_tiles, per_split, ldo, split_stride, stages, error_word(), epi,
+                add_into);
   return LLM_OK;
 }
 
@@ -920,10 +978,11 @@ extern "C" int llm_gemm_tc_supported(const void* a, const void* w, int M, int N,
 // swap = 0: tiles of 128 tokens; out dtype bf16 or f32; splits must be 1.
 // swap = 1: M <= 256 tokens; weights fill the accumulator lanes; with splits > 1, out is float32
 //           [splits, M, ldo] partials (split_stride elements apart) to be added by the consumer.
-extern "C" int llm_gemm_tc(const void* a, const void* w, void* out, int M, int N, int K, long long lda, long long ldw,
-                           long long ldo, int out_dtype, int swap, int splits, long long split_stride, int stages,
-                           cudaStream_t stream) {
+static int gemm_tc_impl(const void* a, const void* w, void* out, int M, int N, int K, long long lda, long long ldw,
+                        long long ldo, int out_dtype, int swap, int splits, long long split_stride, int stages,
+                        cudaStream_t stream, int add_into) {
   if (M == 0 || N == 0) return LLM_OK;
+  LLM_REQUIRE(!add_into || (!swap && out_dtype == LLM_F32), "gemm_tc: adding into the output needs token tiles and float32");
   LLM_REQUIRE(llm_gemm_tc_supported(a, w, M, N, K, lda, ldw), "gemm_tc: operands must be 16-byte aligned with K and row strides multiples of 8");
   LLM_REQUIRE(out_dtype == LLM_F32 || out_dtype == LLM_BF16, "gemm_tc: unknown out dtype %d", out_dtype);
   LLM_REQUIRE(splits >= 1 && (splits == 1 || (swap && out_dtype == LLM_F32)), "gemm_tc: K splits need the swapped form and float32 partials");
@@ -935,19 +994,20 @@ extern "C" int llm_gemm_tc(const void* a, const void* w, void* out, int M, int N
     const int bn = N >= 256 ? 256 : (N > 64 ? 128 : (N > 32 ? 64 : (N > 16 ? 32 : 16)));
     LLM_REQUIRE(tensor_map_for(a, M, K, lda, BM, &ma) && tensor_map_for(w, N, K, ldw, bn, &mb), "gemm_tc: cuTensorMapEncodeTiled failed");
 #define LLM_TC_CASE(BN_)                                                                                                   \
-  rc = (out_dtype == LLM_F32) ? launch_tc<BN_, false, float>(ma, mb, out, M, N, K, 1, ldo, 0, std::min(stages, BN_ == 256 ? 4 : 6), stream) \
+  rc = (out_dtype == LLM_F32) ? launch_tc<BN_, false, float>(ma, mb, out, M, N, K, 1, ldo, 0, std::min(stages, BN_ == 256 ? 4 : 6), stream, EpiArgs(), add_into) \
                               : launch_tc<BN_, false, bf16>(ma, mb, out, M, N, K, 1, ldo, 0, std::min(stages, BN_ == 256 ? 4 : 6), stream)
-    const int form = llm_gemm_tc_form(M, N, K, 0);
+    int form = llm_gemm_tc_form(M, N, K, 0);
+    if (form == FORM_PAIRS && add_into) form = use_persistent(M, N) ? FORM_PERSISTENT_256 : FORM_ONE_TILE;  // the pair kernel only stores
     if (form == FORM_PAIRS) {
       LLM_REQUIRE(tensor_map_for(w, N, K, ldw, 128, &mb), "gemm_tc: cuTensorMapEncodeTiled failed");
       rc = (out_dtype == LLM_F32) ? launch_tc_pair<float, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream)
                                   : launch_tc_pair<bf16, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream);
     } else if (form == FORM_PERSISTENT_192) {
       LLM_REQUIRE(tensor_map_for(w, N, K, ldw, 192, &mb), "gemm_tc: cuTensorMapEncodeTiled failed");
-      rc = (out_dtype == LLM_F32) ? launch_tc_persistent<float, false, 192>(ma, mb, out, M, N, K, ldo, sm_count(), stream)
+      rc = (out_dtype == LLM_F32) ? launch_tc_persistent<float, false, 192>(ma, mb, out, M, N, K, ldo, sm_count(), stream, add_into)
                                   : launch_tc_persistent<bf16, false, 192>(ma, mb, out, M, N, K, ldo, sm_count(), stream);
     } else if (form == FORM_PERSISTENT_256)
-      rc = (out_dtype == LLM_F32) ? launch_tc_persistent<float, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream)
+      rc = (out_dtype == LLM_F32) ? launch_tc_persistent<float, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream, add_into)
                                   : launch_tc_persistent<bf16, false>(ma, mb, out, M, N, K, ldo, sm_count(), stream);
     else if (bn == 256) LLM_TC_CASE(256);
     else if (bn == 128) LLM_TC_CASE(128);
@@ -972,6 +1032,20 @@ extern "C" int llm_gemm_tc(const void* a, const void* w, void* out, int M, int N
   if (rc != LLM_OK) return rc;
   LLM_CHECK_LAUNCH("gemm_tc");
   return LLM_OK;
+}
+
+extern "C" int llm_gemm_tc(const void* a, const void* w, void* out, int M, int N, int K, long long lda, long long ldw,
+                           long long ldo, int out_dtype, int swap, int splits, long long split_stride, int stages,
+                           cudaStream_t stream) {
+  return gemm_tc_impl(a, w, out, M, N, K, lda, ldw, ldo, out_dtype, swap, splits, split_stride, stages, stream, 0);
+}
+
+// out [M, ldo] float32 += a . w^T in tiles of 128 tokens (every output element is read, added to and
+// written by the one thread that holds its accumulator: the same float32 sum as a kernel that adds
+// the product afterwards, without the product ever going to memory).
+extern "C" int llm_gemm_tc_add(const void* a, const void* w, float* out, int M, int N, int K, long long lda, long long ldw,
+                               long long ldo, int stages, cudaStream_t stream) {
+  return gemm_tc_impl(a, w, out, M, N, K, lda, ldw, ldo, LLM_F32, 0, 1, 0, stages, stream, 1);
 }
 
 // The swapped form (at most 64 tokens) with the K splits meeting inside the product (EPI_MEET):

@@ -148,6 +148,13 @@ def add_into_stream_or_partials(ops, x: torch.Tensor, w: torch.Tensor, ctx, few:
         ops.gemm_meet(x[:n], w, res.h, ctx.ws, tag, next_w=wn, scaled=scaled, sumsq=ss)
         res.sumsq, res.prescaled, res.prescaled_weight = ss, scaled, wn
         return None
+    if (not few and res is not None and res.pending is None and res.h.shape[1] == w.shape[0] and x.dtype == torch.bfloat16 and
+            hasattr(ops, "gemm_add_into") and ops.can_add_into(x[:n], w)):
+        # a prompt-sized step: the product's epilogue adds into the stream (the same float32 sums as the
+        # next norm would have made from the product written out)
+        res_sumsq_off(res)
+        ops.gemm_add_into(x[:n], w, res.h)
+        return None
     if few and res is not None and res.pending is None and res.h.shape[1] == w.shape[0]:
         parts = ops.residual_sumsq_parts(w.shape[0], w.shape[1], n)
         ss = ctx.ws.get(tag + ".sumsq", (res.h.shape[0], parts), torch.float32)

@@ -18,9 +18,9 @@ DEV = "cuda:0"
 def ops():
     from llmengine.ops import get_ops
     o = get_ops()
-    before, o.meet_products = o.meet_products, True  # an option that is off by default
+    before, o.meet_products, o.add_into_stream = (o.meet_products, o.add_into_stream), True, True  # options that are off by default
     yield o
-    o.meet_products = before
+    o.meet_products, o.add_into_stream = before
 
 
 def rnd(*shape, dtype=torch.float32, seed=0, std=1.0):
@@ -140,3 +140,21 @@ def test_decoding_attention_and_rotation_take_the_row_scale(ops, nq, nkv, hd, pa
         qs.append((qkv[:, :nq * hd].float(), kc.float(), vc.float()))
     for x, y in zip(qs[0], qs[1]):
         torch.testing.assert_close(x, y, atol=4e-2, rtol=1.6e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 2048, 192), (129, 130, 64), (2048, 3072, 128), (1100, 8704, 256), (65, 509, 520)])
+def test_prompt_sized_product_that_adds_into_the_stream(ops, M, N, K):
+    """One tile a CTA and the persistent kernels (tiles of 256 and of 192 outputs): every element of
+    the stream is read, added to and written once, the same float32 sum as adding the product
+    afterwards (bit for bit); rows beyond the step's tokens stay as they are."""
+    a, w = rnd(M, K, dtype=torch.bfloat16, seed=20), rnd(N, K, dtype=torch.bfloat16, seed=21, std=0.05)
+    h0 = rnd(M + 2, N, seed=22, std=2.0)
+    assert ops.can_add_into(a, w)
+    h = h0.clone()
+    ops.gemm_add_into(a, w, h)
+    out = torch.empty(M, N, device=DEV)
+    ops.gemm(a, w, out)
+    assert torch.equal(h[:M], h0[:M] + out) and torch.equal(h[M:], h0[M:])
+    rows = torch.tensor(sorted({0, min(127, M - 1), min(128, M - 1), M - 1})).to(DEV)
+    torch.testing.assert_close(h[rows].double(), h0[rows].double() + a[rows].double() @ w.double().t(), atol=2e-5 * math.sqrt(K), rtol=2e-5)
+    assert ops.tensor_core_error() == 0
