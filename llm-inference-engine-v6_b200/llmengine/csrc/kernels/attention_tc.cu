@@ -128,8 +128,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
   uint64_t* full_k = reinterpret_cast<uint64_t*>(kv_s + 4 * KV_BYTES);  // [2] the keys of a tile have landed
   uint64_t* full_v = full_k + 2;        // [2] the values of a tile have landed
   uint64_t* s_bar = full_v + 2;         // the scores of a tile are in tensor memory
-  uint64_t* s_free = s_bar + 1;         // all 128 rows have read their scores: the S columns may be overwritten (128 arrivals)
-  uint64_t* p_bar = s_free + 1;         // all 128 rows of P are in tensor memory (128 arrivals)
+  uint64_t* s_free = s_bar + 1;         // all 128 rows have read their scores: the S columns may be overwritten (an arrival a warp)
+  uint64_t* p_bar = s_free + 1;         // all 128 rows of P are in tensor memory (an arrival a warp)
   uint64_t* o_bar = p_bar + 1;          // the P V product of a tile is done
   uint64_t* done_bar = o_bar + 1;       // every product that was issued has finished (committed last, also after giving up)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 2);  // (+1 spare word: the ints after it stay 16-byte aligned)
@@ -166,8 +166,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
       mbar_init(&full_v[b], 1);
     }
     mbar_init(s_bar, 1);
-    mbar_init(s_free, ROWS);
-    mbar_init(p_bar, ROWS);
+    mbar_init(s_free, ROWS / 32);  // one arrival a softmax warp
+    mbar_init(p_bar, ROWS / 32);
     mbar_init(o_bar, 1);
     mbar_init(done_bar, 1);
     *abort_flag = 0;
@@ -323,7 +323,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
       tmem_load_wait();  // four loads in flight, one wait
       // the scores are in registers: the tensor cores may write the next tile's scores over them
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(s_free);
+      __syncwarp();
+      if ((tid & 31) == 0) mbar_arrive(s_free);  // the loads above are warp-wide: one arrival stands for the 32 rows
       const int key0 = (kt_first + i) * KEYS;
       const bool full_tile = (key0 + KEYS - 1 <= pos_r) && (key0 >= lo_r);
       // s stays unscaled: max(s * c) = c * max(s) for c > 0, and the scale folds into the exponent's
@@ -396,7 +397,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(p_bar);
+      __syncwarp();
+      if ((tid & 31) == 0) mbar_arrive(p_bar);
     }
     // ---- the rows of O, normalised
     if (ok && n_tiles > 0) ok = mbar_wait(o_bar, (uint32_t)(n_tiles - 1) & 1u, abort_flag, p.error_out, ERR_ATT_O);

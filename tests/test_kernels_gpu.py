@@ -516,6 +516,38 @@ def test_attention_finds_one_far_key_among_hundreds(ops, dt, special, n_new):
             assert (o[h] - V[special, h // 2].float()).abs().max() < 0.05
 
 
+@pytest.mark.parametrize("nq,nkv,hd", [(32, 8, 64), (24, 8, 128)])
+@pytest.mark.parametrize("special", [0, 63, 64, 340, 341, 342, 1023, 1024, 2040])
+@pytest.mark.parametrize("n_new", [1, 40])
+def test_attention_finds_one_far_key_at_real_head_counts(ops, nq, nkv, hd, special, n_new):
+    """The same at the head counts and context lengths of real checkpoints (Llama 3.2 1B and 3B: 32
+    and 24 query heads over 8 key/value heads of 64 and 128, 2,048 keys, bfloat16): single tokens go
+    through the TMA decoding kernel with its key splits merged inside a cluster, portions of 40
+    through the tcgen05 kernel; the special key sits at the start, at tile and split edges and near
+    the end. Among 2,048 random keys a lost one would weigh 1/2048 and pass any tolerance."""
+    dt, page, L = torch.bfloat16, 16, 2048
+    g = nq // nkv
+    kc, vc, table, dense = _paged_setup(dt, nkv, hd, page, [L], L // page + 3, seed=special)
+    b = Batch([(L - n_new, n_new)])
+    q = rnd(n_new, nq * hd, dtype=dt, seed=27)
+    K, V = dense[0]
+    pg, off = int(table[0, special // page]), special % page
+    qs = q[n_new - 1].cpu().view(nq, hd).float()
+    for h in range(nkv):  # key `special` of every kv head := 16 / sqrt(hd) * (the first query of its group)
+        K[special, h] = (qs[h * g] * (16.0 / math.sqrt(hd))).to(dt)
+        kc[pg, h, off] = K[special, h].to(DEV)
+    out = torch.full((n_new, nq * hd), float("nan"), dtype=dt, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ops.paged_attention(q, kc, vc, b, table, out, nq, nkv, hd, scale, 0)
+    assert ops.tensor_core_error() == 0
+    for i in (0, n_new - 1):
+        ref = _attention_ref(q[i].cpu().view(nq, hd), K, V, L - n_new + i, nq, nkv, hd, scale, 0)
+        torch.testing.assert_close(out[i].float().cpu(), ref, **tol(dt, 2))
+    o = out[n_new - 1].float().cpu().view(nq, hd)
+    for h in range(nkv):  # score 16 |q|^2 / hd ~ 16 against ~N(0, 1): that key carries the row
+        assert (o[h * g] - V[special, h].float()).abs().max() < 0.05
+
+
 @pytest.mark.parametrize("dt", DTYPES)
 def test_attention_window_edge(ops, dt):
     """The key just outside the window must not count, the one just inside must."""
