@@ -172,6 +172,8 @@ def run_step_timeline(args) -> dict:
     B, ctx = args.batch, args.context
     from .ops import get_ops
     get_ops().few_token_products = args.few_token_products == "on"
+    get_ops().meet_products = args.meet_products == "on"
+    get_ops().add_into_stream = args.add_into_stream == "on"
     gen = torch.Generator().manual_seed(1)
     prompts = torch.randint(0, args.vocab, (B, ctx), generator=gen).tolist()
     with tempfile.TemporaryDirectory() as tmp:
@@ -249,9 +251,14 @@ def main(argv=None) -> int:
     t = sub.add_parser("step")
     t.add_argument("--batch", type=int, default=8); t.add_argument("--context", type=int, default=2048)
     t.add_argument("--prefill", action="store_true")
-    t.add_argument("--few-token-products", choices=["on", "off"], default="on",
-                   help="decode steps: products that add their K pieces inside a cluster, norms and SiLU folded in (off: "
-                        "partial sums in memory, added by norm and activation kernels)")
+    t.add_argument("--few-token-products", choices=["on", "off"], default="off",
+                   help="decode steps: products that add their K pieces inside a cluster, norms and SiLU folded in (off, the "
+                        "engine's default: partial sums in memory, added by norm and activation kernels)")
+    t.add_argument("--meet-products", choices=["on", "off"], default="off",
+                   help="decode steps: o and down add their K splits and the residual themselves and leave the next norm's input; "
+                        "the norms are no kernels of their own (off: the engine's default)")
+    t.add_argument("--add-into-stream", choices=["on", "off"], default="off",
+                   help="prompt steps: o and down add into the residual stream in their epilogue (off: the engine's default)")
     t.add_argument("--hidden", type=int, default=2048); t.add_argument("--ffn", type=int, default=8192)
     t.add_argument("--layers", type=int, default=16); t.add_argument("--heads", type=int, default=32)
     t.add_argument("--kv-heads", type=int, default=8); t.add_argument("--head-dim", type=int, default=64)
