@@ -10,7 +10,9 @@ buffer and sampler output, so that nothing it points at is ever moved by a later
 """
 from __future__ import annotations
 
+import gc
 import time
+import weakref
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -29,6 +31,7 @@ class _Captured:
         self.pad_to: Tuple[int, int, int, int] = (0, 0, 0, 0)
         self.kernels = 0  # kernel launches inside the graph
         self.logits: Optional[torch.Tensor] = None
+        self.layout = None  # where the step's arrays lie in the batch buffer (host module StepLayout)
 
 
 class DecodeGraphs:
@@ -36,10 +39,19 @@ class DecodeGraphs:
     MAX_GRAPHS = 48    # each graph owns its workspace (75 MB at 64 requests of this model): the oldest go first
 
     def __init__(self, engine):
-        self.engine = engine
+        # no reference cycle between the engine and its graphs: both then go away when the engine is
+        # dropped, not whenever the garbage collector next runs (which may be inside a later capture)
+        self._engine = weakref.ref(engine)
         self.captured: Dict[Tuple[int, int], _Captured] = {}
         self.h2d_bytes = self.d2h_bytes = 0  # of the last step (for measurements)
         self.last: Optional[_Captured] = None  # the graph that ran the last step
+
+    @property
+    def engine(self):
+        eng = self._engine()
+        if eng is None:
+            raise RuntimeError("the engine of these decode graphs is gone")
+        return eng
 
     def clear(self) -> None:
         self.captured.clear()
@@ -84,15 +96,24 @@ class DecodeGraphs:
         before = eng.ops.launches
         # the sampled tokens are written straight into pinned host memory: no copy to enqueue afterwards
         c.host_tokens = torch.zeros(cap, dtype=torch.int32, pin_memory=True)
-        with torch.cuda.graph(graph):
-            logits = eng.model.forward(ctx)
-            c.tokens = sampler.sample_device(logits, ctx, cap, out=c.host_tokens)
-            c.logits = logits  # of the last replay, padded rows included (read by tests)
-            eng.queue_error_check()
+        # Nothing may free device memory or destroy a graph while the stream is being recorded: a
+        # destructor that runs then (say, of an older graph that the collector finds at this moment)
+        # invalidates the capture or ends the process. So: collect before, and not during.
+        gc.collect()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                logits = eng.model.forward(ctx)
+                c.tokens = sampler.sample_device(logits, ctx, cap, out=c.host_tokens)
+                c.logits = logits  # of the last replay, padded rows included (read by tests)
+                eng.queue_error_check()
+        finally:
+            if gc_was_on:
+                gc.enable()
         c.kernels = eng.ops.launches - before
         c.graph = graph
-        layout = H.StepLayout.make(cap, cap, cap, blocks, eng.cm.num_groups)
-        c.refill = lambda entries: c.buffers.refill(eng.cm, entries, layout, eng.spec.vocab_size, eng.max_pos)
+        c.layout = H.StepLayout.make(cap, cap, cap, blocks, eng.cm.num_groups)
         return c
 
     def _graph_for(self, cap: int, blocks: int) -> _Captured:
@@ -113,7 +134,7 @@ class DecodeGraphs:
         cap = self._capacity(seqs)
         blocks = (blocks + self.BLOCK_BUCKET - 1) // self.BLOCK_BUCKET * self.BLOCK_BUCKET
         c = self._graph_for(cap, blocks)
-        c.refill(entries)
+        c.buffers.refill(eng.cm, entries, c.layout, eng.spec.vocab_size, eng.max_pos)
         c.graph.replay()
         eng.ops.launches += c.kernels
         t0 = time.perf_counter()
@@ -132,7 +153,7 @@ class DecodeGraphs:
         cap = self._capacity(seqs)
         blocks = (blocks + self.BLOCK_BUCKET - 1) // self.BLOCK_BUCKET * self.BLOCK_BUCKET
         c = self._graph_for(cap, blocks)
-        c.refill(entries)
+        c.buffers.refill(eng.cm, entries, c.layout, eng.spec.vocab_size, eng.max_pos)
         c.graph.replay()
         eng.ops.launches += c.kernels
         return c.tokens[:seqs]

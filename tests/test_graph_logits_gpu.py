@@ -104,3 +104,27 @@ def test_a_recorded_kernel_error_raises_at_the_step_and_the_engine_goes_on(tmp_p
     assert (list(r[1].token_ids), r[1].finish_reason) == before
     assert eng.ops.tensor_core_error() == 0 and eng.cm.free_pages(0) == 64
     eng.cm.check()
+
+
+def test_an_engine_with_graphs_goes_away_when_it_is_dropped(tmp_path):
+    """No reference cycle holds an engine that has recorded decode graphs: dropping it frees the
+    graphs and their memory at once, not at some later run of the garbage collector (which might
+    be in the middle of another engine's capture, where nothing may be destroyed)."""
+    import gc
+    import weakref
+    cfg, page = CONFIGS["d"]
+    d = str(tmp_path / "m")
+    make_model_dir(d, cfg, torch.bfloat16)
+    gc.collect()
+    gc.disable()
+    try:
+        eng = llmengine.Engine(d, "bf16", block_size=page, num_blocks=40, max_concurrent=4, cuda_graphs=True)
+        out, reason = eng.generate(random_ids(9, cfg["vocab_size"], 5), 6)
+        assert reason == "length" and len(out) >= 6 and eng.graphs is not None and len(eng.graphs.captured) >= 1
+        graphs = weakref.ref(eng.graphs)
+        captured = weakref.ref(next(iter(eng.graphs.captured.values())))
+        alive = weakref.ref(eng)
+        del eng
+        assert alive() is None and graphs() is None and captured() is None
+    finally:
+        gc.enable()

@@ -533,8 +533,8 @@ def test_attention_finds_one_far_key_at_real_head_counts(ops, nq, nkv, hd, speci
     K, V = dense[0]
     pg, off = int(table[0, special // page]), special % page
     qs = q[n_new - 1].cpu().view(nq, hd).float()
-    for h in range(nkv):  # key `special` of every kv head := 16 / sqrt(hd) * (the first query of its group)
-        K[special, h] = (qs[h * g] * (16.0 / math.sqrt(hd))).to(dt)
+    for h in range(nkv):  # key `special` of every kv head: along the first query of its group, with a score of 16
+        K[special, h] = (qs[h * g] * (16.0 * math.sqrt(hd) / float((qs[h * g] ** 2).sum()))).to(dt)
         kc[pg, h, off] = K[special, h].to(DEV)
     out = torch.full((n_new, nq * hd), float("nan"), dtype=dt, device=DEV)
     scale = 1.0 / math.sqrt(hd)
@@ -544,7 +544,7 @@ def test_attention_finds_one_far_key_at_real_head_counts(ops, nq, nkv, hd, speci
         ref = _attention_ref(q[i].cpu().view(nq, hd), K, V, L - n_new + i, nq, nkv, hd, scale, 0)
         torch.testing.assert_close(out[i].float().cpu(), ref, **tol(dt, 2))
     o = out[n_new - 1].float().cpu().view(nq, hd)
-    for h in range(nkv):  # score 16 |q|^2 / hd ~ 16 against ~N(0, 1): that key carries the row
+    for h in range(nkv):  # a score of 16 against 2,047 of ~N(0, 1): that key carries the row
         assert (o[h * g] - V[special, h].float()).abs().max() < 0.05
 
 
