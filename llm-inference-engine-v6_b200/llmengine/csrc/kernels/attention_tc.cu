@@ -437,6 +437,439 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS_ATT) : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------
+// Persistent form of the kernel above. A CTA of the kernel above lives for one query tile, and about
+// a third of its life at 2,048 tokens is not softmax: it sets up barriers and tensor memory, reads
+// its slice of the block table, waits for its first keys and its query rows, and at the end waits
+// for the last product, writes its rows and leaves, before the next CTA can start the same on its
+// slot. Here two CTAs an SM stay and take query tiles from a counter, longest first, and the warp
+// that issues copies and products runs ahead of the softmax warps ACROSS tiles of queries: while
+// they finish the last keys of one query tile and write its rows, the first keys and the query rows
+// of the next are already there and its first scores are done.
+//   * warp 5: lane 0 waits, fetches work items and issues the query rows' copy; every lane below
+//     pages-per-tile reads its page of a key tile from the block table and issues that copy; warp 4:
+//     one thread issues the products (a trip to L2 for a page number never delays a product);
+//   * query rows come by TMA, a box of (tokens of the tile) x 64 dims per head, so row r of the
+//     tile is (head r / tokens-per-tile, token r % tokens-per-tile);
+//   * every barrier completes once a key tile (keys, values: once a tile and stage), so the parities
+//     follow one counter of key tiles that runs on through the query tiles; the first product of a
+//     query tile overwrites the output of the one before, which its rows have long read out: they
+//     wrote this tile's probabilities, which the product waits for, after that;
+//   * work items travel from lane 0 of warp 5 to the other warps through a ring of eight in shared
+//     memory, one barrier a slot: the copying warp is at most four items ahead of the softmax warps.
+struct AttItem {
+  int seq, kvh, tok_base, pos0, n_tq, kt_first, n_tiles, hi;  // n_tiles 0: no more work
+};
+
+// Tokens of a query tile: a head's rows start 1,024 bytes apart or a multiple of it (the swizzle
+// pattern's period), so a multiple of 8 tokens; 0: the group is too large for this form.
+__host__ __device__ inline int persistent_tq_cap(int g) { return (ROWS / g) / 8 * 8; }
+
+template <int HD>
+__device__ __forceinline__ bool att_item(const AttnTcParams& p, int it, int n_seqs, int n_qtiles, AttItem* out) {
+  constexpr int KEYS = AttLayout<HD>::KEYS;
+  const int g = p.nq / p.nkv, tq_cap = persistent_tq_cap(g);
+  const int kvh = it % p.nkv, r = it / p.nkv, seq = r % n_seqs, z = r / n_seqs;
+  const int q0 = (n_qtiles - 1 - z) * tq_cap, ntok = p.seq_ntok[seq];  // late query tiles see the most keys: they go first
+  if (q0 >= ntok) return false;
+  out->seq = seq;
+  out->kvh = kvh;
+  out->n_tq = min(tq_cap, ntok - q0);
+  out->tok_base = p.seq_qoff[seq] + q0;
+  out->pos0 = p.seq_start[seq] + q0;
+  out->hi = out->pos0 + out->n_tq - 1;
+  const int lo = (p.window > 0) ? max(0, out->pos0 - p.window + 1) : 0;
+  out->kt_first = lo / KEYS;
+  out->n_tiles = out->hi / KEYS - out->kt_first + 1;
+  return true;
+}
+
+enum : int { ERR_ATT_ITEM = 14 };
+
+constexpr int ATT_PERSISTENT_THREADS = 192;  // warps 0-3: softmax; warp 4: one thread issues the products; warp 5: work items and copies
+
+template <int HD>
+__global__ void __launch_bounds__(ATT_PERSISTENT_THREADS, 2)
+    paged_attention_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                         const __grid_constant__ CUtensorMap map_v, const AttnTcParams p, int n_seqs, int n_qtiles,
+                                         int n_items, int* __restrict__ work) {  // work[0]: next item, work[1]: CTAs that are done
+  using L = AttLayout<HD>;
+  constexpr int KEYS = L::KEYS, DBLK = L::DBLK, Q_BYTES = L::Q_BYTES, KV_BYTES = L::KV_BYTES;
+  constexpr int S_COL = L::S_COL, P_COL = L::P_COL, O_COL = L::O_COL;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* q_s = smem;             // [DBLK blocks][128 rows][128 B], 128-byte swizzle
+  uint8_t* kv_s = smem + Q_BYTES;  // [2 stages][K | V], each [DBLK blocks][KEYS rows][128 B]
+  uint64_t* full_k = reinterpret_cast<uint64_t*>(kv_s + 4 * KV_BYTES);  // [2] the keys of a tile have landed in the stage
+  uint64_t* full_v = full_k + 2;   // [2] the values
+  uint64_t* empty_k = full_v + 2;  // [2] the scores that read the stage's keys are done
+  uint64_t* empty_v = empty_k + 2; // [2] the product that read the stage's values is done
+  uint64_t* q_full = empty_v + 2;  // the query rows of an item have landed
+  uint64_t* q_empty = q_full + 1;  // the last scores of an item are done: its query rows may be overwritten
+  uint64_t* s_bar = q_empty + 1;   // the scores of a key tile are in tensor memory
+  uint64_t* s_free = s_bar + 1;    // every row has read them (an arrival a softmax warp)
+  uint64_t* p_bar = s_free + 1;    // every row's probabilities are in tensor memory (an arrival a warp)
+  uint64_t* o_bar = p_bar + 1;     // the P V product of a key tile is done
+  uint64_t* done_bar = o_bar + 1;  // every product that was issued has finished
+  uint64_t* item_bar = done_bar + 1;  // [8] ring slot holds an item
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(item_bar + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  AttItem* ring = reinterpret_cast<AttItem*>(tmem_slot + 4);  // [8]
+
+  dep_launch();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = p.nq / p.nkv, tq_cap = persistent_tq_cap(g);
+  const int pages_per_tile = KEYS / p.page_size;
+
+  if (tid == 0) {
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&full_k[b], 1);
+      mbar_init(&full_v[b], 1);
+      mbar_init(&empty_k[b], 1);
+      mbar_init(&empty_v[b], 1);
+    }
+    mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
+    mbar_init(s_bar, 1);
+    mbar_init(s_free, ROWS / 32);
+    mbar_init(p_bar, ROWS / 32);
+    mbar_init(o_bar, 1);
+    mbar_init(done_bar, 1);
+    for (int b = 0; b < 8; ++b) mbar_init(&item_bar[b], 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS_ATT) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // rows of the query tile that no copy writes (128 is no multiple of every group size) read as zeros
+  for (int i = tid; i < Q_BYTES / 16; i += ATT_PERSISTENT_THREADS) reinterpret_cast<uint4*>(q_s)[i] = make_uint4(0, 0, 0, 0);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  dep_wait();  // queries, keys and values come from the kernels before; the work counter was left at zero by the launch before
+
+  if (warp == 5) {
+    // ------------------------------------------------------------------ the warp that fetches work and issues the copies
+    // Lane 0 waits and takes items from the counter; every lane below pages-per-tile issues its page's
+    // copy of a key tile. The stream of key tiles runs on through the items: keys of tile gt go to
+    // stage gt % 2 once the scores of tile gt - 2 are done (empty_k of the stage), values once the
+    // product of tile gt - 2 is done (empty_v), the query rows of an item once the last scores of the
+    // item before are done (q_empty). Each of these barriers belongs to one buffer and cannot complete
+    // again before this warp has filled the buffer again, so a wait here is never a phase behind.
+    struct Cur {  // a key tile of the CTA's stream: ring slot of its item, index in the item, tiles of the item (0: no more)
+      int slot, i, n;
+    };
+    int n_fetched = 0;
+    bool ok = true;
+    auto fetch = [&]() -> Cur {  // the first key tile of the next item with work
+      int slot = n_fetched & 7, n = 0;
+      if (lane == 0) {
+        AttItem item;
+        item.n_tiles = 0;
+        for (;;) {
+          const int it = atomicAdd(&work[0], 1);
+          if (it >= n_items) {
+            item.n_tiles = 0;
+            break;
+          }
+          if (att_item<HD>(p, it, n_seqs, n_qtiles, &item)) break;
+        }
+        ring[slot] = item;
+        n = item.n_tiles;
+        __threadfence_block();
+        mbar_arrive(&item_bar[slot]);
+      }
+      ++n_fetched;
+      n = __shfl_sync(0xffffffffu, n, 0);
+      __syncwarp();
+      return Cur{slot, 0, n};
+    };
+    auto next = [&](const Cur& c) -> Cur {
+      if (c.n == 0) return c;
+      if (c.i + 1 < c.n) return Cur{c.slot, c.i + 1, c.n};
+      return fetch();
+    };
+    // The first cache row of this lane's page of key tile c, through the block table; asked for a key
+    // tile ahead of its use.
+    auto page_row = [&](const Cur& c) -> int {
+      if (c.n == 0 || lane >= pages_per_tile) return 0;
+      const AttItem& item = ring[c.slot];
+      const int idx = ((item.kt_first + c.i) * KEYS) / p.page_size + lane;
+      int page = (idx < p.max_blocks && idx * p.page_size <= item.hi) ? p.block_table[(size_t)item.seq * p.max_blocks + idx] : -1;
+      if (page < 0) page = p.null_page;  // not held (beyond the newest key, or given back behind a window): finite values, probabilities of zero
+      return (page * p.nkv + item.kvh) * p.page_size;
+    };
+    auto issue_part = [&](int row, int gt, bool values) {  // keys or values of key tile gt of the stream -> stage gt % 2
+      uint8_t* dst = kv_s + (size_t)(gt & 1) * 2 * KV_BYTES + (values ? KV_BYTES : 0);
+      uint64_t* bar = values ? &full_v[gt & 1] : &full_k[gt & 1];
+      if (lane == 0) mbar_expect_tx(bar, (uint32_t)KV_BYTES);
+      __syncwarp();
+      if (lane < pages_per_tile) {
+        const CUtensorMap* map = values ? &map_v : &map_k;
+#pragma unroll
+        for (int b = 0; b < DBLK; ++b) tma_load_2d(dst + b * (KEYS * 128) + (size_t)lane * p.page_size * 128, map, b * 64, row, bar);
+      }
+      __syncwarp();
+    };
+    auto issue_q = [&](const Cur& c) {  // the query rows of c's item: a box of tq_cap tokens x 64 dims per head and block
+      if (lane == 0) {
+        const AttItem& item = ring[c.slot];
+        mbar_expect_tx(q_full, (uint32_t)(g * DBLK * tq_cap * 128));
+        for (int hg = 0; hg < g; ++hg)
+#pragma unroll
+          for (int b = 0; b < DBLK; ++b)
+            tma_load_2d(q_s + b * (ROWS * 128) + (size_t)hg * tq_cap * 128, &map_q, (item.kvh * g + hg) * HD + b * 64, item.tok_base, q_full);
+      }
+      __syncwarp();
+    };
+    auto wait0 = [&](uint64_t* bar, uint32_t parity, int code) -> bool {  // lane 0 waits, the warp learns the outcome
+      bool r = true;
+      if (lane == 0) r = mbar_wait(bar, parity, abort_flag, p.error_out, code);
+      return __shfl_sync(0xffffffffu, r, 0);
+    };
+    int kv_issued = 0, q_issued = 0;  // key tiles and items whose copies have been asked for (for the drain after giving up)
+    Cur c = fetch(), c1 = next(c);
+    int row = page_row(c);
+    for (int gt = 0; c.n > 0 && ok; ++gt) {
+      const int row1 = page_row(c1);  // used a key tile from now
+      if (c.i == 0) {  // a new item: its query rows, once the scores of the item before are done with theirs
+        if (q_issued > 0) {
+          ok = wait0(q_empty, (uint32_t)(q_issued - 1) & 1u, ERR_ATT_S);
+          if (!ok) break;
+        }
+        issue_q(c);
+        ++q_issued;
+      }
+      if (gt >= 2) {
+        ok = wait0(&empty_k[gt & 1], (uint32_t)((gt >> 1) - 1) & 1u, ERR_ATT_S);
+        if (!ok) break;
+      }
+      issue_part(row, gt, false);
+      if (gt >= 2) {
+        ok = wait0(&empty_v[gt & 1], (uint32_t)((gt >> 1) - 1) & 1u, ERR_ATT_O);
+        if (!ok) {
+          if (lane == 0) mbar_drain(&full_k[gt & 1], (uint32_t)(gt >> 1) & 1u, p.error_out);  // the keys just asked for
+          break;
+        }
+      }
+      issue_part(row, gt, true);
+      kv_issued = gt + 1;
+      c = c1;
+      c1 = next(c1);
+      row = row1;
+    }
+    if (!ok && lane == 0) {
+      // gave up: what was asked for lands (bounded) before the CTA gives its shared memory back; the other
+      // roles see the abort flag
+      for (int t = max(0, kv_issued - 2); t < kv_issued; ++t) {
+        mbar_drain(&full_k[t & 1], (uint32_t)(t >> 1) & 1u, p.error_out);
+        mbar_drain(&full_v[t & 1], (uint32_t)(t >> 1) & 1u, p.error_out);
+      }
+      if (q_issued > 0) mbar_drain(q_full, (uint32_t)(q_issued - 1) & 1u, p.error_out);
+    }
+  } else if (warp == 4) {
+    // ------------------------------------------------------------------ the thread that issues the products
+    if (lane == 0) {
+      bool ok = true;
+      int gt = 0;          // key tiles of the stream whose scores have been issued
+      int prev_first = 0;  // whether tile gt - 1 was the first of its item (its product overwrites the output)
+      auto issue_pv = [&](int t, bool first) {  // O (+)= P V of key tile t
+        ok = mbar_wait(p_bar, (uint32_t)t & 1u, abort_flag, p.error_out, ERR_ATT_S);
+        if (ok) ok = mbar_wait(&full_v[t & 1], (uint32_t)(t >> 1) & 1u, abort_flag, p.error_out, ERR_ATT_KV);
+        if (!ok) return;
+        // (the first product of an item overwrites the output of the item before: its rows wrote P of this
+        // tile after they had read that output out)
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        constexpr uint32_t idesc_o = instr_desc_att(64, true);
+#pragma unroll
+        for (int b = 0; b < DBLK; ++b) {
+          const uint64_t dv = smem_desc_sw128(smem_u32(kv_s + (size_t)(t & 1) * 2 * KV_BYTES + KV_BYTES + b * (KEYS * 128)));
+#pragma unroll
+          for (int k = 0; k < KEYS / 16; ++k)
+            mma_f16_ts(tmem_base + O_COL + (uint32_t)(b * 64), tmem_base + P_COL + (uint32_t)(k * 8), dv + (uint64_t)(k * (16 * 128 >> 4)),
+                       idesc_o, (!first || k > 0) ? 1u : 0u);
+        }
+        mma_commit(o_bar);
+        mma_commit(&empty_v[t & 1]);  // the value stage may be filled again once this product is done
+      };
+      for (int n_item = 0; ok; ++n_item) {
+        ok = mbar_wait(&item_bar[n_item & 7], (uint32_t)(n_item >> 3) & 1u, abort_flag, p.error_out, ERR_ATT_ITEM);
+        if (!ok) break;
+        const int n_tiles = ring[n_item & 7].n_tiles;
+        if (n_tiles == 0) break;
+        for (int i = 0; i < n_tiles && ok; ++i, ++gt) {
+          // the scores of tile gt: the S columns are free once every row has read those of the tile before;
+          // the first tile of an item also needs the item's query rows
+          if (gt > 0) ok = mbar_wait(s_free, (uint32_t)(gt - 1) & 1u, abort_flag, p.error_out, ERR_ATT_S);
+          if (ok && i == 0) ok = mbar_wait(q_full, (uint32_t)n_item & 1u, abort_flag, p.error_out, ERR_ATT_KV);
+          if (ok) ok = mbar_wait(&full_k[gt & 1], (uint32_t)(gt >> 1) & 1u, abort_flag, p.error_out, ERR_ATT_KV);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          constexpr uint32_t idesc_s = instr_desc_att(KEYS, false);
+#pragma unroll
+          for (int k = 0; k < HD / 16; ++k) {  // 16 dims a step: block k / 4, 32 bytes further along the swizzled row each step
+            const uint64_t dq = smem_desc_sw128(smem_u32(q_s + (k / 4) * (ROWS * 128)));
+            const uint64_t dk = smem_desc_sw128(smem_u32(kv_s + (size_t)(gt & 1) * 2 * KV_BYTES + (k / 4) * (KEYS * 128)));
+            mma_f16(tmem_base + S_COL, dq + (uint64_t)(2 * (k % 4)), dk + (uint64_t)(2 * (k % 4)), idesc_s, k > 0 ? 1u : 0u);
+          }
+          mma_commit(s_bar);
+          mma_commit(&empty_k[gt & 1]);              // the key stage may be filled again once these scores are done,
+          if (i == n_tiles - 1) mma_commit(q_empty);  // and after an item's last scores, the query rows
+          // and under the softmax of tile gt, the product of the tile before
+          if (gt > 0) issue_pv(gt - 1, prev_first != 0);
+          prev_first = (i == 0);
+        }
+      }
+      if (ok && gt > 0) issue_pv(gt - 1, prev_first != 0);
+      mma_commit(done_bar);  // also after giving up: arrives once every product that was issued has finished
+    }
+    } else {
+    // ------------------------------------------------------------------ softmax: thread t owns row t
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const int hg = tid / tq_cap, tq_row = tid - hg * tq_cap;  // rows are (head, token): the query rows came a head a box
+    const float sl2 = p.scale * 1.4426950408889634f;
+    bool ok = true;
+    int gt = 0;  // key tiles of the CTA's stream so far
+    for (int n_item = 0; ok; ++n_item) {
+      ok = mbar_wait(&item_bar[n_item & 7], (uint32_t)(n_item >> 3) & 1u, abort_flag, p.error_out, ERR_ATT_ITEM);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const AttItem item = ring[n_item & 7];
+      if (item.n_tiles == 0) break;
+      const bool row_ok = hg < g && tq_row < item.n_tq;
+      const int pos_r = row_ok ? item.pos0 + tq_row : -1;  // -1: padding row, sees no key
+      const int lo_r = (p.window > 0) ? pos_r - p.window + 1 : 0;
+      float m_run = -INFINITY, l_run = 0.f;
+      for (int i = 0; i < item.n_tiles; ++i, ++gt) {
+        ok = mbar_wait(s_bar, (uint32_t)gt & 1u, abort_flag, p.error_out, ERR_ATT_S);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        float s[KEYS];
+#pragma unroll
+        for (int c = 0; c < KEYS / 32; ++c) tmem_load32(tmem_base + lane_base + S_COL + c * 32, s + c * 32);
+        tmem_load_wait();
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);
+        const int key0 = (item.kt_first + i) * KEYS;
+        const bool full_tile = (key0 + KEYS - 1 <= pos_r) && (key0 >= lo_r);
+        float mx = -INFINITY;
+        if (!full_tile) {
+#pragma unroll
+          for (int j = 0; j < KEYS; ++j) {
+            const int key = key0 + j;
+            s[j] = (key <= pos_r && key >= lo_r) ? s[j] : -INFINITY;
+          }
+        }
+        {
+          float m8[8];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) m8[c] = max3(s[c], s[c + 8], s[c + 16]);
+#pragma unroll
+          for (int j = 24; j + 16 <= KEYS; j += 16) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) m8[c] = max3(m8[c], s[j + c], s[j + c + 8]);
+          }
+#pragma unroll
+          for (int c = 0; c < 8; ++c) m8[c] = fmaxf(m8[c], s[KEYS - 8 + c]);
+          mx = fmaxf(max3(m8[0], m8[1], m8[2]), fmaxf(max3(m8[3], m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+        }
+        mx *= sl2;
+        const bool move = (mx > m_run + 8.0f) || (m_run == -INFINITY && mx > -INFINITY);
+        const float m_new = move ? mx : m_run;
+        const float base = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = move ? fast_exp2(m_run - base) : 1.0f;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t packed[KEYS / 2];
+#pragma unroll
+        for (int j = 0; j < KEYS; j += 2) {
+          const float p0 = fast_exp2(fmaf(s[j], sl2, -base)), p1 = fast_exp2(fmaf(s[j + 1], sl2, -base));
+          sum4[(j / 2) & 3] += p0 + p1;
+          __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
+          packed[j / 2] = *reinterpret_cast<uint32_t*>(&t);
+        }
+        l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+        m_run = m_new;
+        if (gt > 0) {
+          // the product of the key tile before (of this item, or the last of the item before) reads the P columns
+          ok = mbar_wait(o_bar, (uint32_t)(gt - 1) & 1u, abort_flag, p.error_out, ERR_ATT_O);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+#pragma unroll
+        for (int c = 0; c < KEYS / 64; ++c) tmem_store32(tmem_base + lane_base + P_COL + c * 32, packed + c * 32);
+        if (i > 0 && __any_sync(0xffffffffu, move)) {
+#pragma unroll
+          for (int c = 0; c < HD / 64; ++c) {
+            float o[64];
+            tmem_load32(tmem_base + lane_base + O_COL + c * 64, o);
+            tmem_load32(tmem_base + lane_base + O_COL + c * 64 + 32, o + 32);
+            tmem_load_wait();
+            uint32_t ou[64];
+#pragma unroll
+            for (int d = 0; d < 64; ++d) ou[d] = __float_as_uint(o[d] * alpha);
+            tmem_store32(tmem_base + lane_base + O_COL + c * 64, ou);
+            tmem_store32(tmem_base + lane_base + O_COL + c * 64 + 32, ou + 32);
+          }
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_bar);
+      }
+      if (!ok) break;
+      // ---- the rows of the item's output, normalised
+      ok = mbar_wait(o_bar, (uint32_t)(gt - 1) & 1u, abort_flag, p.error_out, ERR_ATT_O);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(item.tok_base + tq_row) * p.ld_out + (size_t)(item.kvh * g + hg) * HD);
+#pragma unroll
+      for (int b = 0; b < HD / 64; ++b) {
+        float o[64];
+        tmem_load32(tmem_base + lane_base + O_COL + b * 64, o);
+        tmem_load32(tmem_base + lane_base + O_COL + b * 64 + 32, o + 32);
+        tmem_load_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 t = __floats2bfloat162_rn(o[c * 8 + 2 * e] * inv, o[c * 8 + 2 * e + 1] * inv);
+              w[e] = *reinterpret_cast<uint32_t*>(&t);
+            }
+            dst[b * 8 + c] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      // (the output has left tensor memory; the next item's first product, which overwrites it, waits for
+      // probabilities that these threads write later)
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+  }
+  __syncwarp();
+  if (tid == 0) mbar_drain(done_bar, 0, p.error_out);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS_ATT) : "memory");
+  if (tid == 0) {  // the CTA that leaves last puts the counters back to zero for the next launch
+    __threadfence();
+    if (atomicAdd(&work[1], 1) == (int)gridDim.x - 1) {
+      work[0] = 0;
+      work[1] = 0;
+      __threadfence();
+    }
+  }
+}
+
 template <int HD>
 bool launch_att(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, dim3 grid, int max_blocks, cudaStream_t stream) {
   using L = AttLayout<HD>;
@@ -452,7 +885,47 @@ bool launch_att(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams
   return true;
 }
 
+template <int HD>
+bool launch_att_persistent(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, int n_seqs,
+                           int n_qtiles, int n_items, int* work, int n_sms, cudaStream_t stream) {
+  using L = AttLayout<HD>;
+  const size_t smem = L::Q_BYTES + 4 * L::KV_BYTES + 24 * sizeof(uint64_t) + 16 + 8 * sizeof(AttItem) + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(paged_attention_tc_persistent_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
+    attr_set = true;
+  }
+  const int grid = std::min(n_items, 2 * n_sms);
+  launch_kernel(paged_attention_tc_persistent_kernel<HD>, grid, ATT_PERSISTENT_THREADS, smem, stream, mq, mk, mv, p, n_seqs, n_qtiles, n_items, work);
+  return true;
+}
+
+// Two ints of device memory per process for the persistent kernel's work counters, zero between launches.
+int* att_work_counters() {
+  static int* w = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    if (cudaMalloc(&w, 2 * sizeof(int)) == cudaSuccess) cudaMemset(w, 0, 2 * sizeof(int));
+    else w = nullptr;
+  });
+  return w;
+}
+
+int att_sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
 }  // namespace
+
+static int g_att_persistent = 1;
+// 1 (the default): query tiles are taken from a counter by CTAs that stay (where the group allows);
+// 0: a CTA a query tile. For comparisons; the results are the same sums in the same order.
+extern "C" void llm_attention_tc_persistent(int on) { g_att_persistent = on; }
 
 // Whether the tcgen05 attention takes this geometry (else the caller uses the mma.sync kernel).
 extern "C" int llm_attention_tc_supported(int nq, int nkv, int hd, int page_size, long long ld_q, long long ld_out) {
@@ -470,7 +943,7 @@ extern "C" int llm_attention_tc_supported(int nq, int nkv, int hd, int page_size
 extern "C" int llm_paged_attention_tc(const void* q, long long ld_q, const void* kcache, const void* vcache, long long n_cache_pages,
                                       const int* seq_start, const int* seq_ntok, const int* seq_qoff, const int* block_table,
                                       int max_blocks, void* out, long long ld_out, int n_seqs, int max_new_tokens, int nq, int nkv,
-                                      int hd, int page_size, float scale, int window, cudaStream_t stream) {
+                                      int hd, int page_size, float scale, int window, int n_tokens, cudaStream_t stream) {
   if (n_seqs == 0 || max_new_tokens == 0) return LLM_OK;
   LLM_REQUIRE(llm_attention_tc_supported(nq, nkv, hd, page_size, ld_q, ld_out), "attention_tc: geometry not supported (nq=%d nkv=%d hd=%d page=%d)", nq, nkv, hd, page_size);
   auto al = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
@@ -489,6 +962,22 @@ extern "C" int llm_paged_attention_tc(const void* q, long long ld_q, const void*
   p.null_page = (int)(n_cache_pages - 1);
   LLM_REQUIRE(max_blocks <= 4096, "attention_tc: block tables wider than 4096 pages are not supported");
   const int g = nq / nkv, tq_cap = ROWS / g;
+  const int ptq = persistent_tq_cap(g);
+  if (g_att_persistent && ptq >= 8 && n_tokens > 0 && (ld_q % 8) == 0) {
+    // the persistent form: query rows by TMA (rows of q: the step's tokens), work items from a counter
+    int* work = att_work_counters();
+    LLM_REQUIRE(work != nullptr, "attention_tc: cannot allocate the work counters");
+    CUtensorMap mq;
+    LLM_REQUIRE(tensor_map_for(q, n_tokens, (long long)nq * hd, ld_q, ptq, &mq), "attention_tc: cuTensorMapEncodeTiled failed for q");
+    const int n_qtiles = (max_new_tokens + ptq - 1) / ptq;
+    const long long n_items = (long long)n_qtiles * n_seqs * nkv;
+    LLM_REQUIRE(n_items < (1LL << 30), "attention_tc: too many query tiles");
+    const bool ok = hd == 64 ? launch_att_persistent<64>(mq, mk, mv, p, n_seqs, n_qtiles, (int)n_items, work, att_sm_count(), stream)
+                             : launch_att_persistent<128>(mq, mk, mv, p, n_seqs, n_qtiles, (int)n_items, work, att_sm_count(), stream);
+    LLM_REQUIRE(ok, "attention_tc: cannot raise the shared memory limit");
+    LLM_CHECK_LAUNCH("paged_attention_tc");
+    return LLM_OK;
+  }
   dim3 grid(nkv, n_seqs, (max_new_tokens + tq_cap - 1) / tq_cap);
   bool attr_ok = true;
   if (hd == 64) attr_ok = launch_att<64>(mk, mv, p, grid, max_blocks, stream);

@@ -133,6 +133,7 @@ def run_attention(args) -> dict:
     B, ctx, new = args.batch, args.context, args.new
     if getattr(args, "kernel", "auto") == "mma":
         ops.tcgen05_attention = ops.tma_decode_attention = False
+    ops.lib("tensorcore").llm_attention_tc_persistent(1 if getattr(args, "query_tiles", "counter") == "counter" else 0)
     total = ctx + new
     blocks = (total + page - 1) // page
     layers = max(2, int(300e6 // max(B * total * nkv * hd * 4, 1)) + 1)  # caches of several "layers" in turn
@@ -247,6 +248,8 @@ def main(argv=None) -> int:
     a.add_argument("--page", type=int, default=16); a.add_argument("--reps", type=int, default=20)
     a.add_argument("--kernel", choices=["auto", "mma"], default="auto",
                    help="mma: the mma.sync kernels also where the tcgen05 / TMA kernels would run")
+    a.add_argument("--query-tiles", choices=["counter", "cta"], default="counter",
+                   help="prompt portions on tcgen05: CTAs that stay and take query tiles from a counter (the default), or a CTA a query tile")
     a.add_argument("--sequential", action="store_true", help="each request's pages lie in a row (default: scattered over the pool)")
     t = sub.add_parser("step")
     t.add_argument("--batch", type=int, default=8); t.add_argument("--context", type=int, default=2048)

@@ -681,7 +681,7 @@ class CudaOps:
                     _ptr(batch.seq_start), _ptr(batch.seq_ntok), _ptr(batch.seq_qoff), _ptr(block_table),
                     c_int(block_table.shape[1]), _ptr(out), c_longlong(out.stride(0)), c_int(batch.n_seqs),
                     c_int(batch.max_new_tokens), c_int(nq), c_int(nkv), c_int(hd), c_int(page), c_float(scale), c_int(window),
-                    _stream()), lib)
+                    c_int(q.shape[0]), _stream()), lib)
                 return out
             decode_only = batch.max_new_tokens == 1 and batch.n_tokens == batch.n_seqs
             use_tma = decode_only and self.tma_decode_attention and lib.llm_attention_decode_supported(

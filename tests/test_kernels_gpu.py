@@ -359,6 +359,41 @@ def test_paged_attention_tcgen05(ops, nq, nkv, window, hd, page):
         assert not torch.isnan(out.float()).any()
 
 
+@pytest.mark.parametrize("nq,nkv,hd,page,window", [(32, 8, 64, 16, 0), (24, 8, 128, 16, 0), (8, 2, 64, 32, 150), (6, 2, 128, 8, 0),
+                                                   (5, 1, 64, 16, 70), (7, 1, 64, 64, 0), (16, 1, 128, 16, 0)])
+def test_paged_attention_tcgen05_both_forms(ops, nq, nkv, hd, page, window):
+    """The CTAs that stay and take query tiles from a counter (query rows by TMA, a box a head; tiles of
+    a multiple of 8 tokens) against a CTA a query tile: the same sums in the same order for every
+    (token, head), so equal bit for bit; many more query tiles than CTAs, requests that end inside a
+    tile, portions that start in the middle of a context, groups that do not divide 128, and the same
+    launch three times (the work counters must be left at zero)."""
+    dt = torch.bfloat16
+    lib = ops.lib("tensorcore")
+    seq_lens = [1500, 1, 129, 700, 128, 40, 333, 2]
+    kc, vc, table, dense = _paged_setup(dt, nkv, hd, page, seq_lens, sum((L + page - 1) // page for L in seq_lens) + 3, seed=31)
+    scale = 1.0 / math.sqrt(hd)
+    for b in (Batch([(0, 1500), (0, 1), (0, 129), (0, 700), (0, 128), (0, 40), (0, 333), (0, 2)]),
+              Batch([(1200, 300), (0, 1), (100, 29), (310, 390), (127, 1), (7, 33), (300, 33), (1, 1)])):
+        q = rnd(b.n_tokens, nq * hd, dtype=dt, seed=32)
+        outs = []
+        for form in (1, 1, 1, 0):
+            lib.llm_attention_tc_persistent(form)
+            try:
+                out = torch.full((b.n_tokens, nq * hd), float("nan"), dtype=dt, device=DEV)
+                ops.paged_attention(q, kc, vc, b, table, out, nq, nkv, hd, scale, window)
+            finally:
+                lib.llm_attention_tc_persistent(1)
+            assert ops.tensor_core_error() == 0
+            outs.append(out)
+        assert not torch.isnan(outs[0].float()).any()
+        for o in outs[1:]:
+            assert torch.equal(outs[0], o)
+        for i in list(range(0, b.n_tokens, 97)) + [b.n_tokens - 1]:
+            s_, p_ = b.tokens[i]
+            ref = _attention_ref(q[i].cpu().view(nq, hd), dense[s_][0], dense[s_][1], p_, nq, nkv, hd, scale, window)
+            torch.testing.assert_close(outs[0][i].float().cpu(), ref, **tol(dt, 2))
+
+
 @pytest.mark.parametrize("cluster_merge", [True, False])
 @pytest.mark.parametrize("target_ctas", [1, 592, 100000])  # no split, the usual splits, a split every 64 keys
 @pytest.mark.parametrize("nq,nkv,hd,page,window", [(32, 8, 64, 16, 0), (8, 2, 64, 8, 0), (4, 4, 64, 32, 0), (16, 1, 64, 64, 0),
