@@ -98,6 +98,46 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Two float32 lanes in one 64-bit register pair, for the packed instructions of sm_100 (fma.rn.f32x2,
+// add.rn.f32x2: one issue slot for two results, each lane rounded as the scalar instruction rounds).
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// The probabilities of a row's scores of one key tile: p[j] = 2^(s[j] * sl2 - base) as bfloat16 pairs,
+// and their float32 sum (of the unrounded values; eight chains of additions joined in a fixed order).
+// The multiply-adds and the additions run two lanes an instruction.
+template <int KEYS>
+__device__ __forceinline__ float exp_row(const float* s, float sl2, float base, uint32_t* packed) {
+  const uint64_t sl2_2 = pack2(sl2, sl2), nbase2 = pack2(-base, -base);
+  uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};  // (0.f, 0.f) pairs
+#pragma unroll
+  for (int j = 0; j < KEYS; j += 2) {
+    float x0, x1;
+    unpack2(fma2(pack2(s[j], s[j + 1]), sl2_2, nbase2), x0, x1);
+    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+    sum2[(j / 2) & 3] = add2(sum2[(j / 2) & 3], pack2(p0, p1));
+    __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
+    packed[j / 2] = *reinterpret_cast<uint32_t*>(&t);
+  }
+  float a0, a1;
+  unpack2(add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3])), a0, a1);
+  return a0 + a1;
+}
+
 // tcgen05.mma with the A operand in tensor memory.
 __device__ __forceinline__ void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -359,16 +399,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)  // two CTAs per SM: at most 2
       const float m_new = move ? mx : m_run;
       const float base = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = move ? fast_exp2(m_run - base) : 1.0f;  // 0 when the row had seen no key yet
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};  // four chains of additions, joined at the end (a fixed order)
       uint32_t packed[KEYS / 2];
-#pragma unroll
-      for (int j = 0; j < KEYS; j += 2) {
-        const float p0 = fast_exp2(fmaf(s[j], sl2, -base)), p1 = fast_exp2(fmaf(s[j + 1], sl2, -base));
-        sum4[(j / 2) & 3] += p0 + p1;
-        __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
-        packed[j / 2] = *reinterpret_cast<uint32_t*>(&t);
-      }
-      l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      l_run = l_run * alpha + exp_row<KEYS>(s, sl2, base, packed);
       m_run = m_new;
       if (i > 0) {
         // The product P V of the tile before reads the P columns and adds into O: both are touched
@@ -784,16 +816,8 @@ __global__ void __launch_bounds__(ATT_PERSISTENT_THREADS, 2)
         const float m_new = move ? mx : m_run;
         const float base = (m_new == -INFINITY) ? 0.f : m_new;
         const float alpha = move ? fast_exp2(m_run - base) : 1.0f;
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t packed[KEYS / 2];
-#pragma unroll
-        for (int j = 0; j < KEYS; j += 2) {
-          const float p0 = fast_exp2(fmaf(s[j], sl2, -base)), p1 = fast_exp2(fmaf(s[j + 1], sl2, -base));
-          sum4[(j / 2) & 3] += p0 + p1;
-          __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
-          packed[j / 2] = *reinterpret_cast<uint32_t*>(&t);
-        }
-        l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+        l_run = l_run * alpha + exp_row<KEYS>(s, sl2, base, packed);
         m_run = m_new;
         if (gt > 0) {
           // the product of the key tile before (of this item, or the last of the item before) reads the P columns
