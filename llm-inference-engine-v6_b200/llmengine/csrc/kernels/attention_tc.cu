@@ -924,17 +924,6 @@ bool launch_att_persistent(const CUtensorMap& mq, const CUtensorMap& mk, const C
   return true;
 }
 
-// Two ints of device memory per process for the persistent kernel's work counters, zero between launches.
-int* att_work_counters() {
-  static int* w = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    if (cudaMalloc(&w, 2 * sizeof(int)) == cudaSuccess) cudaMemset(w, 0, 2 * sizeof(int));
-    else w = nullptr;
-  });
-  return w;
-}
-
 int att_sm_count() {
   static int n = 0;
   if (!n) {
@@ -963,11 +952,13 @@ extern "C" int llm_attention_tc_supported(int nq, int nkv, int hd, int page_size
 
 // q: rows of [nq*hd] bf16; caches [pages, nkv, page_size, hd] bf16 (n_cache_pages pages each, the LAST of
 // them the null page: finite values, never a request's);
-// seq_* and block_table as in the step's batch; out [n_tokens, nq*hd] bf16.
+// seq_* and block_table as in the step's batch; out [n_tokens, nq*hd] bf16. n_tokens: rows of q. work: two ints
+// that are zero between launches (the persistent form's counters: next query tile, CTAs that are done; the
+// kernel leaves them at zero), or null for the form with a CTA a query tile.
 extern "C" int llm_paged_attention_tc(const void* q, long long ld_q, const void* kcache, const void* vcache, long long n_cache_pages,
                                       const int* seq_start, const int* seq_ntok, const int* seq_qoff, const int* block_table,
                                       int max_blocks, void* out, long long ld_out, int n_seqs, int max_new_tokens, int nq, int nkv,
-                                      int hd, int page_size, float scale, int window, int n_tokens, cudaStream_t stream) {
+                                      int hd, int page_size, float scale, int window, int n_tokens, int* work, cudaStream_t stream) {
   if (n_seqs == 0 || max_new_tokens == 0) return LLM_OK;
   LLM_REQUIRE(llm_attention_tc_supported(nq, nkv, hd, page_size, ld_q, ld_out), "attention_tc: geometry not supported (nq=%d nkv=%d hd=%d page=%d)", nq, nkv, hd, page_size);
   auto al = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
@@ -987,10 +978,8 @@ extern "C" int llm_paged_attention_tc(const void* q, long long ld_q, const void*
   LLM_REQUIRE(max_blocks <= 4096, "attention_tc: block tables wider than 4096 pages are not supported");
   const int g = nq / nkv, tq_cap = ROWS / g;
   const int ptq = persistent_tq_cap(g);
-  if (g_att_persistent && ptq >= 8 && n_tokens > 0 && (ld_q % 8) == 0) {
+  if (g_att_persistent && ptq >= 8 && n_tokens > 0 && (ld_q % 8) == 0 && work != nullptr) {
     // the persistent form: query rows by TMA (rows of q: the step's tokens), work items from a counter
-    int* work = att_work_counters();
-    LLM_REQUIRE(work != nullptr, "attention_tc: cannot allocate the work counters");
     CUtensorMap mq;
     LLM_REQUIRE(tensor_map_for(q, n_tokens, (long long)nq * hd, ld_q, ptq, &mq), "attention_tc: cuTensorMapEncodeTiled failed for q");
     const int n_qtiles = (max_new_tokens + ptq - 1) / ptq;

@@ -227,6 +227,7 @@ class Engine:
         for ws in spaces:
             ws.zero("attention.split_counters")
             ws.zero("gemm.meet_counters")
+            ws.zero("attention.work_counters")
         from ..ops import KernelError
         what = getattr(self.ops, "ERROR_CODES", {}).get(code, "unknown code")
         raise KernelError(f"a tensor-core kernel gave up a bounded wait (code {code}: {what}); the step's results are void")

@@ -676,12 +676,13 @@ class CudaOps:
                     lib.llm_attention_tc_supported(c_int(nq), c_int(nkv), c_int(hd), c_int(page), c_longlong(q.stride(0)),
                                                    c_longlong(out.stride(0)))):
                 # prompt portions: tcgen05 kernel (128 rows per CTA, scores and output in tensor memory)
+                work = batch.ws.get_zeroed("attention.work_counters", (2,), torch.int32)  # left at zero by the kernel
                 self._check(lib.llm_paged_attention_tc(
                     _ptr(q), c_longlong(q.stride(0)), _ptr(kcache), _ptr(vcache), c_longlong(kcache.shape[0]),
                     _ptr(batch.seq_start), _ptr(batch.seq_ntok), _ptr(batch.seq_qoff), _ptr(block_table),
                     c_int(block_table.shape[1]), _ptr(out), c_longlong(out.stride(0)), c_int(batch.n_seqs),
                     c_int(batch.max_new_tokens), c_int(nq), c_int(nkv), c_int(hd), c_int(page), c_float(scale), c_int(window),
-                    c_int(q.shape[0]), _stream()), lib)
+                    c_int(q.shape[0]), _ptr(work), _stream()), lib)
                 return out
             decode_only = batch.max_new_tokens == 1 and batch.n_tokens == batch.n_seqs
             use_tma = decode_only and self.tma_decode_attention and lib.llm_attention_decode_supported(
