@@ -497,13 +497,23 @@ struct AttItem {
 // pattern's period), so a multiple of 8 tokens; 0: the group is too large for this form.
 __host__ __device__ inline int persistent_tq_cap(int g) { return (ROWS / g) / 8 * 8; }
 
+// Work item `it` of a step: the kv head runs fastest, then the query tiles of request 0 from its last
+// (which sees the most keys) to its first, then those of request 1, and so on. seq_first[s] is the
+// number of query tiles of the requests before s (seq_first[n_seqs]: of all), so that requests with a
+// single token beside a long prompt portion add one item a kv head each and no empty ones.
 template <int HD>
-__device__ __forceinline__ bool att_item(const AttnTcParams& p, int it, int n_seqs, int n_qtiles, AttItem* out) {
+__device__ __forceinline__ void att_item(const AttnTcParams& p, int it, int n_seqs, const int* seq_first, AttItem* out) {
   constexpr int KEYS = AttLayout<HD>::KEYS;
   const int g = p.nq / p.nkv, tq_cap = persistent_tq_cap(g);
-  const int kvh = it % p.nkv, r = it / p.nkv, seq = r % n_seqs, z = r / n_seqs;
-  const int q0 = (n_qtiles - 1 - z) * tq_cap, ntok = p.seq_ntok[seq];  // late query tiles see the most keys: they go first
-  if (q0 >= ntok) return false;
+  const int kvh = it % p.nkv, j = it / p.nkv;
+  int lo_s = 0, hi_s = n_seqs;  // the request whose tiles hold j: seq_first[lo_s] <= j < seq_first[lo_s + 1]
+  while (hi_s - lo_s > 1) {
+    const int mid = (lo_s + hi_s) >> 1;
+    if (seq_first[mid] <= j) lo_s = mid;
+    else hi_s = mid;
+  }
+  const int seq = lo_s, tiles = seq_first[seq + 1] - seq_first[seq];
+  const int q0 = (tiles - 1 - (j - seq_first[seq])) * tq_cap, ntok = p.seq_ntok[seq];
   out->seq = seq;
   out->kvh = kvh;
   out->n_tq = min(tq_cap, ntok - q0);
@@ -513,7 +523,6 @@ __device__ __forceinline__ bool att_item(const AttnTcParams& p, int it, int n_se
   const int lo = (p.window > 0) ? max(0, out->pos0 - p.window + 1) : 0;
   out->kt_first = lo / KEYS;
   out->n_tiles = out->hi / KEYS - out->kt_first + 1;
-  return true;
 }
 
 enum : int { ERR_ATT_ITEM = 14 };
@@ -523,8 +532,8 @@ constexpr int ATT_PERSISTENT_THREADS = 192;  // warps 0-3: softmax; warp 4: one 
 template <int HD>
 __global__ void __launch_bounds__(ATT_PERSISTENT_THREADS, 2)
     paged_attention_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                                         const __grid_constant__ CUtensorMap map_v, const AttnTcParams p, int n_seqs, int n_qtiles,
-                                         int n_items, int* __restrict__ work) {  // work[0]: next item, work[1]: CTAs that are done
+                                         const __grid_constant__ CUtensorMap map_v, const AttnTcParams p, int n_seqs,
+                                         int* __restrict__ work) {  // work[0]: next item, work[1]: CTAs that are done
   using L = AttLayout<HD>;
   constexpr int KEYS = L::KEYS, DBLK = L::DBLK, Q_BYTES = L::Q_BYTES, KV_BYTES = L::KV_BYTES;
   constexpr int S_COL = L::S_COL, P_COL = L::P_COL, O_COL = L::O_COL;
@@ -547,6 +556,7 @@ __global__ void __launch_bounds__(ATT_PERSISTENT_THREADS, 2)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(item_bar + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   AttItem* ring = reinterpret_cast<AttItem*>(tmem_slot + 4);  // [8]
+  int* seq_first = reinterpret_cast<int*>(ring + 8);          // [n_seqs + 1] query tiles of the requests before (used by warp 5 only)
 
   dep_launch();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -597,19 +607,32 @@ __global__ void __launch_bounds__(ATT_PERSISTENT_THREADS, 2)
     };
     int n_fetched = 0;
     bool ok = true;
-    auto fetch = [&]() -> Cur {  // the first key tile of the next item with work
+    int n_items = 0;
+    {  // the query tiles of every request, summed up (the batch arrays came with the step's host-to-device copy)
+      int run = 0;
+      for (int base = 0; base < n_seqs; base += 32) {
+        const int sq = base + lane;
+        const int cnt = sq < n_seqs ? (p.seq_ntok[sq] + tq_cap - 1) / tq_cap : 0;
+        int incl = cnt;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, incl, off);
+          if (lane >= off) incl += v;
+        }
+        if (sq < n_seqs) seq_first[sq] = run + incl - cnt;
+        run += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) seq_first[n_seqs] = run;
+      __syncwarp();
+      n_items = run * p.nkv;
+    }
+    auto fetch = [&]() -> Cur {  // the first key tile of the next item
       int slot = n_fetched & 7, n = 0;
       if (lane == 0) {
         AttItem item;
         item.n_tiles = 0;
-        for (;;) {
-          const int it = atomicAdd(&work[0], 1);
-          if (it >= n_items) {
-            item.n_tiles = 0;
-            break;
-          }
-          if (att_item<HD>(p, it, n_seqs, n_qtiles, &item)) break;
-        }
+        const int it = atomicAdd(&work[0], 1);
+        if (it < n_items) att_item<HD>(p, it, n_seqs, seq_first, &item);
         ring[slot] = item;
         n = item.n_tiles;
         __threadfence_block();
@@ -911,16 +934,16 @@ bool launch_att(const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams
 
 template <int HD>
 bool launch_att_persistent(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p, int n_seqs,
-                           int n_qtiles, int n_items, int* work, int n_sms, cudaStream_t stream) {
+                           long long max_items, int* work, int n_sms, cudaStream_t stream) {
   using L = AttLayout<HD>;
-  const size_t smem = L::Q_BYTES + 4 * L::KV_BYTES + 24 * sizeof(uint64_t) + 16 + 8 * sizeof(AttItem) + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
+  const size_t smem = L::Q_BYTES + 4 * L::KV_BYTES + 24 * sizeof(uint64_t) + 16 + 8 * sizeof(AttItem) + (size_t)(n_seqs + 1) * sizeof(int) + 1024;
+  static size_t attr_smem = 0;
+  if (smem > attr_smem) {
     if (cudaFuncSetAttribute(paged_attention_tc_persistent_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
-    attr_set = true;
+    attr_smem = smem;
   }
-  const int grid = std::min(n_items, 2 * n_sms);
-  launch_kernel(paged_attention_tc_persistent_kernel<HD>, grid, ATT_PERSISTENT_THREADS, smem, stream, mq, mk, mv, p, n_seqs, n_qtiles, n_items, work);
+  const int grid = (int)std::min<long long>(max_items, 2 * n_sms);  // (the step may hold fewer items than max_items: CTAs without one leave at once)
+  launch_kernel(paged_attention_tc_persistent_kernel<HD>, grid, ATT_PERSISTENT_THREADS, smem, stream, mq, mk, mv, p, n_seqs, work);
   return true;
 }
 
@@ -982,11 +1005,11 @@ extern "C" int llm_paged_attention_tc(const void* q, long long ld_q, const void*
     // the persistent form: query rows by TMA (rows of q: the step's tokens), work items from a counter
     CUtensorMap mq;
     LLM_REQUIRE(tensor_map_for(q, n_tokens, (long long)nq * hd, ld_q, ptq, &mq), "attention_tc: cuTensorMapEncodeTiled failed for q");
-    const int n_qtiles = (max_new_tokens + ptq - 1) / ptq;
-    const long long n_items = (long long)n_qtiles * n_seqs * nkv;
-    LLM_REQUIRE(n_items < (1LL << 30), "attention_tc: too many query tiles");
-    const bool ok = hd == 64 ? launch_att_persistent<64>(mq, mk, mv, p, n_seqs, n_qtiles, (int)n_items, work, att_sm_count(), stream)
-                             : launch_att_persistent<128>(mq, mk, mv, p, n_seqs, n_qtiles, (int)n_items, work, att_sm_count(), stream);
+    // at most: every token a query tile of its own, or every request as many as the longest portion
+    const long long max_items = std::min<long long>((long long)n_tokens, (long long)n_seqs * ((max_new_tokens + ptq - 1) / ptq)) * nkv;
+    LLM_REQUIRE(max_items < (1LL << 30) && n_seqs < 40000, "attention_tc: too many query tiles");
+    const bool ok = hd == 64 ? launch_att_persistent<64>(mq, mk, mv, p, n_seqs, max_items, work, att_sm_count(), stream)
+                             : launch_att_persistent<128>(mq, mk, mv, p, n_seqs, max_items, work, att_sm_count(), stream);
     LLM_REQUIRE(ok, "attention_tc: cannot raise the shared memory limit");
     LLM_CHECK_LAUNCH("paged_attention_tc");
     return LLM_OK;
