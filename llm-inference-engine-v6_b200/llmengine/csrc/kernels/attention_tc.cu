@@ -1001,7 +1001,7 @@ extern "C" int llm_paged_attention_tc(const void* q, long long ld_q, const void*
   LLM_REQUIRE(max_blocks <= 4096, "attention_tc: block tables wider than 4096 pages are not supported");
   const int g = nq / nkv, tq_cap = ROWS / g;
   const int ptq = persistent_tq_cap(g);
-  if (g_att_persistent && ptq >= 8 && n_tokens > 0 && (ld_q % 8) == 0 && work != nullptr) {
+  if (g_att_persistent && ptq >= 8 && n_tokens >= ptq && (ld_q % 8) == 0 && work != nullptr) {  // (a box of query rows is no taller than q)
     // the persistent form: query rows by TMA (rows of q: the step's tokens), work items from a counter
     CUtensorMap mq;
     LLM_REQUIRE(tensor_map_for(q, n_tokens, (long long)nq * hd, ld_q, ptq, &mq), "attention_tc: cuTensorMapEncodeTiled failed for q");
