@@ -4,10 +4,11 @@
     python -m llmengine.kernel_bench gemm_few --m 8 --n 2048 --k 8192 --mode residual
     python -m llmengine.kernel_bench attention --batch 8 --context 2048 --new 1
     python -m llmengine.kernel_bench attention --batch 1 --context 0 --new 2048
+    python -m llmengine.kernel_bench norm --rows 8 --dim 2048 --parts 16
     python -m llmengine.kernel_bench step --batch 8 --context 2048          (timeline of one decode step)
     python -m llmengine.kernel_bench step --batch 1 --context 2048 --prefill (timeline of one prompt step)
 
-Each of the first three launches ONE kind of kernel a few times on inputs that are larger than the L2 cache
+Each of these launches ONE kind of kernel a few times on inputs that are larger than the L2 cache
 (several copies of the operands are used in turn) and prints the mean device time per launch with
 the bytes and flops it implies. The sizes default to the Llama 3.2 1B geometry. Meant to be run
 alone or under a profiler with a small --reps.
@@ -161,6 +162,24 @@ def run_attention(args) -> dict:
             "head_dim": hd, "us": round(sec * 1e6, 2), "tflops": round(flops / sec / 1e12, 2), "kv_gbs": round(nbytes / sec / 1e9, 1)}
 
 
+def run_norm(args) -> dict:
+    """RMSNorm with the residual sum folded in: `rows` rows of `dim`, `parts` float32 partial sums to add
+    (0: the stream alone); bfloat16 out. Buffers rotate through more than the L2 cache."""
+    from .ops import get_ops
+    ops = get_ops()
+    dev = torch.device("cuda:0")
+    n, dim, parts = args.rows, args.dim, args.parts
+    per = n * dim * (4 * (2 + parts) + 2)  # bytes a launch touches: stream in and out, the parts, the result
+    sets = max(2, int(300e6 // per) + 1)
+    w = torch.ones(dim, device=dev)
+    hs = [torch.randn(n, dim, device=dev) for _ in range(sets)]
+    ds = [torch.randn(parts, n, dim, device=dev) if parts else None for _ in range(sets)]
+    outs = [torch.empty(n, dim, device=dev, dtype=torch.bfloat16) for _ in range(sets)]
+    sec = _time(lambda i: ops.rmsnorm(hs[i % sets], w, 1e-5, outs[i % sets], delta=ds[i % sets]), args.reps)
+    nbytes = n * dim * (4 * (1 + parts) + (4 if parts else 0) + 2)  # the stream is written back only when something was added
+    return {"kernel": "rmsnorm", "rows": n, "dim": dim, "parts": parts, "us": round(sec * 1e6, 2), "gbs": round(nbytes / sec / 1e9, 1)}
+
+
 def run_step_timeline(args) -> dict:
     import collections
     import tempfile
@@ -251,6 +270,10 @@ def main(argv=None) -> int:
     a.add_argument("--query-tiles", choices=["counter", "cta"], default="counter",
                    help="prompt portions on tcgen05: CTAs that stay and take query tiles from a counter (the default), or a CTA a query tile")
     a.add_argument("--sequential", action="store_true", help="each request's pages lie in a row (default: scattered over the pool)")
+    nm = sub.add_parser("norm")
+    nm.add_argument("--rows", type=int, default=8); nm.add_argument("--dim", type=int, default=2048)
+    nm.add_argument("--parts", type=int, default=16, help="float32 partial sums of the product before, added into the stream (0: none)")
+    nm.add_argument("--reps", type=int, default=20)
     t = sub.add_parser("step")
     t.add_argument("--batch", type=int, default=8); t.add_argument("--context", type=int, default=2048)
     t.add_argument("--prefill", action="store_true")
@@ -274,7 +297,7 @@ def main(argv=None) -> int:
         for k in kernels:
             print(f"{k['critical_us']:9.1f} us critical  x{k['launches']:4d}  mean {k['mean_duration_us']:8.2f} us  {k['kernel']}")
         return 0
-    print(json.dumps({"gemm": run_gemm, "gemm_few": run_gemm_few, "attention": run_attention}[args.what](args)))
+    print(json.dumps({"gemm": run_gemm, "gemm_few": run_gemm_few, "attention": run_attention, "norm": run_norm}[args.what](args)))
     return 0
 
 
