@@ -93,6 +93,26 @@ __global__ void __launch_bounds__(1024) rmsnorm_vec_kernel(float* __restrict__ h
   const float* dr = delta ? delta + (size_t)r * dim : nullptr;
   float4 x[R];
   float ss = 0.f;
+  if (R > 1 && dr && n_partials == 1) {
+    // many rows a launch (a prompt), one product to add: every load of the thread is asked for before
+    // any is used, so that a row costs one trip to memory, not one per quarter of it
+    float4 d[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      const int i = (threadIdx.x + k * blockDim.x) * 4;
+      x[k] = i < dim ? *reinterpret_cast<const float4*>(hr + i) : make_float4(0, 0, 0, 0);
+      d[k] = i < dim ? *reinterpret_cast<const float4*>(dr + i) : make_float4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      const int i = (threadIdx.x + k * blockDim.x) * 4;
+      x[k].x += d[k].x; x[k].y += d[k].y; x[k].z += d[k].z; x[k].w += d[k].w;
+      if (i < dim) {
+        if (write_back) *reinterpret_cast<float4*>(hr + i) = x[k];
+        ss += x[k].x * x[k].x + x[k].y * x[k].y + x[k].z * x[k].z + x[k].w * x[k].w;
+      }
+    }
+  } else
 #pragma unroll
   for (int k = 0; k < R; ++k) {
     const int i = (threadIdx.x + k * blockDim.x) * 4;
@@ -166,6 +186,9 @@ static void launch_rmsnorm(float* h, const float* delta, int n_partials, size_t 
   if (vec) {
     const int quads = dim / 4;
     int threads = quads <= 1024 ? ((quads + 31) / 32) * 32 : 1024;
+    // Many rows (a prompt): a quarter of the threads with four float4 each, so that every row of the
+    // launch is resident at once and all of its bytes are on their way together.
+    if (n_out_rows >= 512 && quads >= 256 && quads <= 4096) threads = ((quads / 4 + 31) / 32) * 32;
     const int per_thread = (quads + threads - 1) / threads;
     if (per_thread == 1)
       launch_kernel(rmsnorm_vec_kernel<TOut, 1>, n_out_rows, threads, 0, stream, h, delta, n_partials, partial_stride, w, rows, out, dim, eps, write_back);
